@@ -1,0 +1,171 @@
+/*
+ * mkb200.h - C ABI of the B200 decode megakernel library (libmkb200.so).
+ *
+ * The library replaces the compiled extension module the reference loads as
+ * `mk_llama` (megakernels/mk.py:5-9) and calls once per decoded token with 23
+ * tensors and 4 scalars (megakernels/demos/latency/mk.py:15-49; binding order
+ * demos/low-latency-llama/llama.cu:29-52).  Here the same argument set is one
+ * plain struct of device pointers and sizes; nothing in the signatures is a
+ * torch or C++ type, so any host language with a C FFI can bind it.
+ *
+ * All pointers are device pointers owned by the caller and must stay valid
+ * until the stream has executed the launch.  The library keeps no pointer
+ * after mkb_launch returns, except cached TMA descriptors keyed by the KV
+ * cache addresses and shape.
+ */
+#ifndef MKB200_H
+#define MKB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MKB_ABI_VERSION 1
+
+/* instruction encoding (megakernels/scheduler.py:13-14) */
+#define MKB_INTS_PER_INSTRUCTION 32
+#define MKB_TIMING_SLOTS 128
+#define MKB_STATUS_WORDS 16
+
+/* opcodes (megakernels/demos/latency/instructions.py:32-196;
+ * demos/low-latency-llama/llama.cuh:7-13) */
+enum {
+    MKB_OP_NOOP = 0,
+    MKB_OP_RMS_QKV_ROPE_APPEND = 1,
+    MKB_OP_PARTIAL_ATTENTION = 2,
+    MKB_OP_ATTENTION_REDUCTION = 3,
+    MKB_OP_O_PROJ_RESIDUAL = 4,
+    MKB_OP_RMS_UPGATE_SILU = 5,
+    MKB_OP_DOWN_PROJ_RESIDUAL = 6,
+    MKB_OP_RMS_LM_HEAD = 7,
+};
+
+/* return / status codes */
+enum {
+    MKB_OK = 0,
+    MKB_ERR_INVALID_ARGUMENT = 1, /* a shape/pointer check failed; nothing was launched */
+    MKB_ERR_CUDA = 2,             /* a CUDA runtime/driver call failed */
+    MKB_ERR_DEVICE_TIMEOUT = 3,   /* a device-side wait gave up; see MkbStatus */
+    MKB_ERR_BAD_OPCODE = 4,       /* the device met an opcode it does not know */
+    MKB_ERR_UNSUPPORTED = 5,      /* valid request this build cannot run */
+};
+
+/*
+ * The kernel's argument set.  Replaces `globals_t` of the reference
+ * (demos/low-latency-llama/llama.cuh:48-158) and the Python-side `Globals`
+ * (megakernels/instructions.py:10-69, demos/latency/instructions.py:9-29).
+ * Model dimensions are run-time values (the reference compiles them in,
+ * llama.cuh:15-26); under tensor parallelism they are the per-rank values.
+ */
+typedef struct MkbGlobals {
+    uint32_t abi_version; /* MKB_ABI_VERSION */
+    uint32_t struct_bytes; /* sizeof(MkbGlobals) as the caller sees it */
+
+    /* ---- virtual-machine state ---- */
+    int32_t *barriers;           /* [num_layers, barrier_ops, barrier_width] int32, zeroed per token */
+    const int32_t *instructions; /* [num_sms, queue_len, 32] int32 */
+    int32_t *timings;            /* [num_sms, queue_len, 128] int32 or NULL */
+    int32_t num_sms;             /* number of instruction queues == grid size */
+    int32_t queue_len;
+    int32_t barrier_ops;         /* 10 in the reference (latency/scheduler.py:59) */
+    int32_t barrier_width;       /* Hq + 2*Hkv */
+
+    /* ---- weights, bf16, row-major [.., out, in], stacked over layers ---- */
+    const void *qkv_weights;          /* [L, (Hq+2Hkv)*D, H] */
+    const void *attn_ln_weights;      /* [L, H] */
+    const void *o_proj_weights;       /* [L, H, Hq*D] */
+    const void *mlp_ln_weights;       /* [L, H] */
+    const void *up_proj_weights;      /* [L, I, H] */
+    const void *gate_proj_weights;    /* [L, I, H] */
+    const void *down_proj_weights;    /* [L, H, I] */
+    const void *lm_head_norm_weights; /* [H] */
+    const void *lm_head_weights;      /* [V, H] */
+
+    /* ---- KV cache, bf16 [L*B, T, Hkv, D] (latency/mk.py:12-13) ---- */
+    void *k_cache;
+    void *v_cache;
+
+    /* ---- RoPE tables, fp32 [>= pos_id+1, D], interleaved pair layout ---- */
+    const float *rope_cos;
+    const float *rope_sin;
+
+    /* ---- activations ---- */
+    void *hidden_states;            /* bf16 [H]        in/out: residual stream */
+    void *post_ln_rope_q;           /* bf16 [Hq*D] */
+    void *attn_out;                 /* bf16 [Hq*D] */
+    float *attn_lse_intermediates;  /* fp32 [Hq, max_partials] */
+    float *attn_out_intermediates;  /* fp32 [Hq, max_partials, D] */
+    void *silu_out;                 /* bf16 [I] */
+    void *logits;                   /* bf16 [V] */
+
+    /* ---- model dimensions ---- */
+    int32_t num_layers;
+    int32_t hidden_size;         /* H */
+    int32_t intermediate_size;   /* I */
+    int32_t head_dim;            /* D: 64 or 128 */
+    int32_t num_attention_heads; /* Hq */
+    int32_t num_kv_heads;        /* Hkv */
+    int32_t vocab_size;          /* V */
+    int32_t kv_max_len;          /* T */
+    int32_t kv_batch;            /* B (sequence 0 is decoded) */
+    int32_t max_partials;        /* second dimension of the attention intermediates */
+    int32_t matvec_reduction_size; /* input-column slice of o-proj / down-proj instructions */
+
+    /* ---- per-token scalars ---- */
+    int32_t pos_id;
+    float attn_scale;
+    float rms_norm_eps;
+    int32_t skip_attn_reduction;
+
+    /* ---- robustness ---- */
+    uint32_t wait_timeout_ms; /* device-side wait budget; 0 selects the default (2000 ms) */
+    int32_t *status;          /* MKB_STATUS_WORDS int32 written on device errors, or NULL to use
+                                 the library's own per-device buffer */
+} MkbGlobals;
+
+/* Device-side error record, MKB_STATUS_WORDS int32. */
+typedef struct MkbStatus {
+    int32_t code;       /* MKB_OK or the first error raised on the device */
+    int32_t sm;         /* queue index of the CTA that raised it */
+    int32_t instruction_index;
+    int32_t opcode;
+    int32_t role;       /* 0 loader, 1 consumer, 2 storer */
+    int32_t detail[4];  /* barrier coordinates and the observed / expected values */
+    int32_t reserved[7];
+} MkbStatus;
+
+/*
+ * Validate `g` on the host and enqueue one decode step (one token) on
+ * `cuda_stream` (a cudaStream_t; NULL = legacy default stream).  Asynchronous:
+ * returns after the launch is enqueued, as the reference call does
+ * (megakernels/demos/latency/mk.py:48).  Replaces `mk_llama(...)`.
+ */
+int mkb_launch(const MkbGlobals *g, void *cuda_stream);
+
+/*
+ * Synchronise `cuda_stream` and copy the device status record to `out`.
+ * Returns out->code (MKB_OK when the last launches ran clean).  The reference
+ * has no counterpart: its device waits are unbounded and a bad opcode traps
+ * (include/util.cuh:38).
+ */
+int mkb_sync_status(const MkbGlobals *g, void *cuda_stream, MkbStatus *out);
+
+/* Message of the last host-side error raised on the calling thread. */
+const char *mkb_last_error(void);
+
+/* Number of SMs of the current CUDA device (megakernels/utils.py:107-109). */
+int mkb_sm_count(void);
+
+/* Dynamic shared memory in bytes the kernel asks for, and its block size. */
+int mkb_smem_bytes(void);
+int mkb_block_threads(void);
+
+/* ABI version the library was built with. */
+int mkb_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MKB200_H */

@@ -1,0 +1,137 @@
+"""Token loops around the megakernel.
+
+Reference: megakernels/generators.py (``Generator.generate_with_eos`` :21-58,
+``MK_Generator`` :95-163).  The per-token host contract is unchanged: write the
+token embedding into ``globs.hidden_states``, zero the barriers, set
+``pos_id``, launch, read ``argmax(globs.logits)``.  Everything stays on the
+device and nothing synchronises inside the loop.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from megakernels_b200.mk import MK_Interpreter
+from megakernels_b200.model_types import BatchState
+from megakernels_b200.scheduler import Schedule
+
+
+class Generator:
+    def generate(
+        self,
+        output_tokens: Tensor,
+        prompt_len: int,
+        ntok: int,
+        ntok_already_generated: int = 1,
+    ):
+        raise NotImplementedError
+
+    def generate_with_eos(
+        self,
+        output_tokens: Tensor,
+        prompt_len: int,
+        ntok: int,
+        eos_token_check_interval: int,
+        eos_token_ids: list[int],
+    ):
+        """Generate in chunks, stopping at the first EOS token.
+
+        Returns ``(position of the first eos, number of tokens generated)``
+        (reference: megakernels/generators.py:21-58).
+        """
+        assert output_tokens.shape[0] == 1, "batch size must be 1"
+        eos = set(int(t) for t in eos_token_ids)
+        for done in range(1, ntok, eos_token_check_interval):
+            chunk = min(eos_token_check_interval, ntok - done)
+            self.generate(
+                output_tokens, prompt_len=prompt_len, ntok=chunk, ntok_already_generated=done
+            )
+            new = output_tokens[0, done : done + chunk].cpu().tolist()
+            for j, tok in enumerate(new):
+                if tok in eos:
+                    return done + j, done + chunk - 1
+        return ntok, ntok - 1
+
+
+class MK_Generator(Generator):
+    """Batch-1 greedy decoding, one megakernel launch per token."""
+
+    def __init__(
+        self,
+        model,
+        interpreter: MK_Interpreter,
+        schedule: Schedule,
+        barrier_fill_val: int = 0,
+        skip_mk: bool = False,
+        skip_rest: bool = False,
+    ):
+        self.model = model
+        self.interpreter = interpreter
+        self.schedule = schedule
+        self.barrier_fill_val = barrier_fill_val
+        self.skip_mk = skip_mk
+        self.skip_rest = skip_rest
+        self.last_call = None
+        self.fill()
+
+    def fill(self):
+        self.schedule.globs.barriers.fill_(self.barrier_fill_val)
+
+    def replace_with_noops(self):
+        self.schedule.globs.instructions.zero_()
+
+    def run(self, input_ids: Tensor, pos_id: int):
+        globs = self.schedule.globs
+        if not self.skip_rest:
+            post = self.model.model.embed_tokens(BatchState(input_ids=input_ids))
+            assert post.hidden_states is not None
+            globs.hidden_states[:] = post.hidden_states.reshape(-1)
+        self.fill()
+        globs.pos_id = pos_id
+        if not self.skip_mk:
+            self.last_call = self.interpreter.interpret(globs)
+        if self.skip_rest:
+            return input_ids
+        return torch.argmax(globs.logits, dim=-1)
+
+    def generate(
+        self,
+        output_tokens: Tensor,
+        prompt_len: int,
+        ntok: int,
+        ntok_already_generated: int = 1,
+    ):
+        """Fill ``output_tokens[:, already : already + ntok]`` greedily.
+
+        ``pos_id = prompt_len + ntok_already_generated + i - 1``
+        (reference: megakernels/generators.py:145-163).
+        """
+        for i in range(ntok):
+            in_pos = ntok_already_generated + i - 1
+            input_ids = output_tokens[:, in_pos : in_pos + 1]
+            pos_id = prompt_len + ntok_already_generated + i - 1
+            output_ids = self.run(input_ids, pos_id=pos_id)
+            output_tokens[:, in_pos + 1] = output_ids.reshape(-1)
+
+    def prefill(self, prompt_ids: Tensor) -> Tensor:
+        """Run the prompt through the decode kernel one token at a time.
+
+        The reference prefills with its torch model (scripts/generate.py:125-137);
+        here the KV cache is filled by the megakernel itself, so no second
+        implementation of the forward pass exists in the product.  Returns the
+        first generated token ``[1]``.
+        """
+        ids = prompt_ids.reshape(1, -1)
+        out = None
+        for pos in range(ids.shape[1]):
+            out = self.run(ids[:, pos : pos + 1], pos_id=pos)
+        return out.reshape(-1)
+
+    def check(self):
+        """Synchronise and raise if any device-side wait gave up."""
+        if self.last_call is None:
+            return None
+        import mk_llama  # the module get_mk_func imported
+
+        return mk_llama.sync_status(self.last_call)

@@ -1,0 +1,144 @@
+"""Generic instruction-set base: kernel globals and instruction encoding.
+
+Reference: megakernels/instructions.py.  ``BaseGlobals`` is the argument set
+of the megakernel (:10-69); ``Instruction.serialize`` defines the int32 word
+layout the device decodes (:83-119); ``NoOp`` is opcode 0 (:122-126).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, fields
+from typing import Any
+
+from torch import Tensor
+
+from megakernels_b200.model_types import DeviceType
+from megakernels_b200.utils import get_sm_count
+
+
+@dataclass
+class BaseGlobals:
+    # model parameters, stacked over layers
+    qkv_proj_weights: Tensor
+    attn_ln_weights: Tensor
+    o_proj_weights: Tensor
+    mlp_ln_weights: Tensor
+    up_proj_weights: Tensor
+    gate_proj_weights: Tensor
+    down_proj_weights: Tensor
+    lm_head_norm_weights: Tensor
+    lm_head_weights: Tensor
+    k_cache: Tensor
+    v_cache: Tensor
+
+    # shared by all layers
+    rope_cos: Tensor
+    rope_sin: Tensor
+
+    # model constants (per-rank values under tensor parallelism)
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_kv_heads: int
+    head_dim: int
+    hidden_size: int
+    intermediate_size: int
+    vocab_size: int
+
+    attn_scale: float
+    rms_norm_eps: float
+    device: DeviceType
+
+    hidden_states: Tensor
+    barriers: Tensor
+
+    pos_id: int
+
+    def __post_init__(self):
+        self.instructions: Tensor | None = None
+        self.timings: Tensor | None = None
+
+    def sm_count(self) -> int:
+        return get_sm_count(self.device)
+
+    def num_total_heads(self) -> int:
+        return self.num_attention_heads + self.num_kv_heads * 2
+
+    def diff(self, other: "BaseGlobals", skip_kv_cache: bool = False, verbose: bool = True):
+        """Compare every non-weight tensor of two globals.
+
+        Reference: megakernels/instructions.py:54-66.  Returns
+        ``{name: (max_abs_diff, mean_rel_diff)}`` in addition to printing.
+        """
+        out = {}
+        for f in fields(self):
+            a, b = getattr(self, f.name), getattr(other, f.name)
+            if (
+                not isinstance(a, Tensor)
+                or "weights" in f.name
+                or f.name in ("rope_cos", "rope_sin")
+                or (skip_kv_cache and "cache" in f.name)
+            ):
+                continue
+            _, adiff, rdiff = diff_tensors(a, b, f.name, verbose=verbose)
+            out[f.name] = (float(adiff.max()), float(rdiff.mean()))
+        return out
+
+
+def diff_tensors(a: Tensor, b: Tensor, name: str, verbose: bool = True):
+    """Reference: megakernels/instructions.py:72-80."""
+    a = a.float().cpu()
+    b = b.float().cpu()
+    diff = a - b
+    adiff = diff.abs()
+    rdiff = 2 * adiff / (a.abs() + b.abs() + 1e-6)
+    if verbose:
+        print(f"{name}: max adiff: {adiff.max()}, mean rdiff: {rdiff.mean()}")
+    return diff, adiff, rdiff
+
+
+@dataclass
+class Instruction:
+    @classmethod
+    def opcode(cls) -> int:
+        raise NotImplementedError
+
+    @classmethod
+    def prev_opcode(cls) -> int:
+        raise NotImplementedError
+
+    @classmethod
+    def tags(cls) -> dict[str, Any]:
+        return {}
+
+    def cost(self, globs) -> float:
+        return 0.0
+
+    def serialize(self) -> list[int]:
+        """Word layout: opcode, then the dataclass fields in declaration order.
+
+        Ints (and bools) take one word, ``None`` becomes 0, tuples and lists
+        are length-prefixed, and a field named ``global_idx`` is skipped
+        (reference: megakernels/instructions.py:97-119).
+        """
+        words = [self.opcode()]
+        for f in fields(self):
+            if f.name == "global_idx":
+                continue
+            v = getattr(self, f.name)
+            if isinstance(v, int):
+                words.append(int(v))
+            elif isinstance(v, (tuple, list)):
+                words.append(len(v))
+                words.extend(int(x) for x in v)
+            elif v is None:
+                words.append(0)
+            else:
+                raise ValueError(f"Unsupported field type: {v!r}")
+        return words
+
+
+@dataclass
+class NoOp(Instruction):
+    @classmethod
+    def opcode(cls) -> int:
+        return 0

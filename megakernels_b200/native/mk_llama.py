@@ -1,0 +1,302 @@
+"""Importable ``mk_llama`` module: a ctypes shim over ``libmkb200.so``.
+
+The reference loads its compiled kernel with ``sys.path.append(mk_dir); from
+mk_llama import mk_llama`` (megakernels/mk.py:5-9) and calls it with 23 tensors,
+4 scalars and ``stream=`` (megakernels/demos/latency/mk.py:15-49).  This module
+offers the same callable.  It only marshals pointers and sizes into the C
+struct of ``include/mkb200.h``; all work happens in the CUDA library, and a
+missing library is an ImportError, never a fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libmkb200.so"
+
+MKB_ABI_VERSION = 1
+MKB_STATUS_WORDS = 16
+
+ERROR_NAMES = {
+    0: "MKB_OK",
+    1: "MKB_ERR_INVALID_ARGUMENT",
+    2: "MKB_ERR_CUDA",
+    3: "MKB_ERR_DEVICE_TIMEOUT",
+    4: "MKB_ERR_BAD_OPCODE",
+    5: "MKB_ERR_UNSUPPORTED",
+}
+
+
+class MkbGlobals(ctypes.Structure):
+    _fields_ = [
+        ("abi_version", ctypes.c_uint32),
+        ("struct_bytes", ctypes.c_uint32),
+        ("barriers", ctypes.c_void_p),
+        ("instructions", ctypes.c_void_p),
+        ("timings", ctypes.c_void_p),
+        ("num_sms", ctypes.c_int32),
+        ("queue_len", ctypes.c_int32),
+        ("barrier_ops", ctypes.c_int32),
+        ("barrier_width", ctypes.c_int32),
+        ("qkv_weights", ctypes.c_void_p),
+        ("attn_ln_weights", ctypes.c_void_p),
+        ("o_proj_weights", ctypes.c_void_p),
+        ("mlp_ln_weights", ctypes.c_void_p),
+        ("up_proj_weights", ctypes.c_void_p),
+        ("gate_proj_weights", ctypes.c_void_p),
+        ("down_proj_weights", ctypes.c_void_p),
+        ("lm_head_norm_weights", ctypes.c_void_p),
+        ("lm_head_weights", ctypes.c_void_p),
+        ("k_cache", ctypes.c_void_p),
+        ("v_cache", ctypes.c_void_p),
+        ("rope_cos", ctypes.c_void_p),
+        ("rope_sin", ctypes.c_void_p),
+        ("hidden_states", ctypes.c_void_p),
+        ("post_ln_rope_q", ctypes.c_void_p),
+        ("attn_out", ctypes.c_void_p),
+        ("attn_lse_intermediates", ctypes.c_void_p),
+        ("attn_out_intermediates", ctypes.c_void_p),
+        ("silu_out", ctypes.c_void_p),
+        ("logits", ctypes.c_void_p),
+        ("num_layers", ctypes.c_int32),
+        ("hidden_size", ctypes.c_int32),
+        ("intermediate_size", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("num_attention_heads", ctypes.c_int32),
+        ("num_kv_heads", ctypes.c_int32),
+        ("vocab_size", ctypes.c_int32),
+        ("kv_max_len", ctypes.c_int32),
+        ("kv_batch", ctypes.c_int32),
+        ("max_partials", ctypes.c_int32),
+        ("matvec_reduction_size", ctypes.c_int32),
+        ("pos_id", ctypes.c_int32),
+        ("attn_scale", ctypes.c_float),
+        ("rms_norm_eps", ctypes.c_float),
+        ("skip_attn_reduction", ctypes.c_int32),
+        ("wait_timeout_ms", ctypes.c_uint32),
+        ("status", ctypes.c_void_p),
+    ]
+
+
+class MkbStatus(ctypes.Structure):
+    _fields_ = [
+        ("code", ctypes.c_int32),
+        ("sm", ctypes.c_int32),
+        ("instruction_index", ctypes.c_int32),
+        ("opcode", ctypes.c_int32),
+        ("role", ctypes.c_int32),
+        ("detail", ctypes.c_int32 * 4),
+        ("reserved", ctypes.c_int32 * 7),
+    ]
+
+
+class MegakernelError(RuntimeError):
+    def __init__(self, code: int, message: str, status: "MkbStatus | None" = None):
+        super().__init__(f"{ERROR_NAMES.get(code, code)}: {message}")
+        self.code = code
+        self.status = status
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """Load ``libmkb200.so``; raise ImportError with build instructions if absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; "
+            "g.build()'` (or `make -C megakernels_b200/csrc`). There is no CPU fallback."
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.mkb_launch.argtypes = [ctypes.POINTER(MkbGlobals), ctypes.c_void_p]
+    lib.mkb_launch.restype = ctypes.c_int
+    lib.mkb_sync_status.argtypes = [
+        ctypes.POINTER(MkbGlobals),
+        ctypes.c_void_p,
+        ctypes.POINTER(MkbStatus),
+    ]
+    lib.mkb_sync_status.restype = ctypes.c_int
+    lib.mkb_last_error.restype = ctypes.c_char_p
+    for name in ("mkb_sm_count", "mkb_smem_bytes", "mkb_block_threads", "mkb_abi_version"):
+        getattr(lib, name).restype = ctypes.c_int
+    if lib.mkb_abi_version() != MKB_ABI_VERSION:
+        raise ImportError(
+            f"libmkb200.so has ABI {lib.mkb_abi_version()}, this shim expects {MKB_ABI_VERSION}"
+        )
+    _lib = lib
+    return lib
+
+
+def _check_tensor(name, t, dtype, ndim=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must live on a CUDA device")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if ndim is not None and t.ndim != ndim:
+        raise ValueError(f"{name} must have {ndim} dimensions, got {tuple(t.shape)}")
+    return t.data_ptr()
+
+
+def pack_globals(
+    barriers,
+    instructions,
+    timings,
+    qkv_weights,
+    attn_ln_weights,
+    o_proj_weights,
+    mlp_ln_weights,
+    up_proj_weights,
+    gate_proj_weights,
+    down_proj_weights,
+    lm_head_norm_weights,
+    lm_head_weights,
+    k_cache,
+    v_cache,
+    rope_cos,
+    rope_sin,
+    hidden_states,
+    post_ln_rope_q,
+    attn_out,
+    attn_lse_intermediates,
+    attn_out_intermediates,
+    silu_out,
+    logits,
+    pos_id,
+    attn_scale,
+    rms_norm_eps,
+    skip_attn_reduction,
+    matvec_reduction_size=None,
+    wait_timeout_ms=0,
+    status=None,
+) -> MkbGlobals:
+    """Fill the C struct from tensors; every dimension is read off the shapes."""
+    bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
+    g = MkbGlobals()
+    g.abi_version = MKB_ABI_VERSION
+    g.struct_bytes = ctypes.sizeof(MkbGlobals)
+    g.barriers = _check_tensor("barriers", barriers, i32, 3)
+    g.instructions = _check_tensor("instructions", instructions, i32, 3)
+    g.timings = _check_tensor("timings", timings, i32, 3) if timings is not None else None
+    g.num_sms, g.queue_len = instructions.shape[0], instructions.shape[1]
+    if instructions.shape[2] != 32:
+        raise ValueError("instructions must be [num_sms, queue_len, 32]")
+    g.barrier_ops, g.barrier_width = barriers.shape[1], barriers.shape[2]
+
+    g.qkv_weights = _check_tensor("qkv_weights", qkv_weights, bf16, 3)
+    g.attn_ln_weights = _check_tensor("attn_ln_weights", attn_ln_weights, bf16, 2)
+    g.o_proj_weights = _check_tensor("o_proj_weights", o_proj_weights, bf16, 3)
+    g.mlp_ln_weights = _check_tensor("mlp_ln_weights", mlp_ln_weights, bf16, 2)
+    g.up_proj_weights = _check_tensor("up_proj_weights", up_proj_weights, bf16, 3)
+    g.gate_proj_weights = _check_tensor("gate_proj_weights", gate_proj_weights, bf16, 3)
+    g.down_proj_weights = _check_tensor("down_proj_weights", down_proj_weights, bf16, 3)
+    g.lm_head_norm_weights = _check_tensor("lm_head_norm_weights", lm_head_norm_weights, bf16, 1)
+    g.lm_head_weights = _check_tensor("lm_head_weights", lm_head_weights, bf16, 2)
+    g.k_cache = _check_tensor("k_cache", k_cache, bf16, 4)
+    g.v_cache = _check_tensor("v_cache", v_cache, bf16, 4)
+    if k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    g.rope_cos = _check_tensor("rope_cos", rope_cos, f32, 2)
+    g.rope_sin = _check_tensor("rope_sin", rope_sin, f32, 2)
+    g.hidden_states = _check_tensor("hidden_states", hidden_states, bf16)
+    g.post_ln_rope_q = _check_tensor("post_ln_rope_q", post_ln_rope_q, bf16)
+    g.attn_out = _check_tensor("attn_out", attn_out, bf16)
+    g.attn_lse_intermediates = _check_tensor(
+        "attn_lse_intermediates", attn_lse_intermediates, f32, 2
+    )
+    g.attn_out_intermediates = _check_tensor(
+        "attn_out_intermediates", attn_out_intermediates, f32, 3
+    )
+    g.silu_out = _check_tensor("silu_out", silu_out, bf16)
+    g.logits = _check_tensor("logits", logits, bf16)
+
+    L, qkv_rows, H = qkv_weights.shape
+    LB, T, Hkv, D = k_cache.shape
+    Hq = attn_lse_intermediates.shape[0]
+    g.num_layers = L
+    g.hidden_size = H
+    g.intermediate_size = up_proj_weights.shape[1]
+    g.head_dim = D
+    g.num_attention_heads = Hq
+    g.num_kv_heads = Hkv
+    g.vocab_size = lm_head_weights.shape[0]
+    g.kv_max_len = T
+    g.kv_batch = LB // L
+    g.max_partials = attn_lse_intermediates.shape[1]
+    if qkv_rows != (Hq + 2 * Hkv) * D:
+        raise ValueError(
+            f"qkv rows {qkv_rows} != (Hq + 2*Hkv)*D = {(Hq + 2 * Hkv) * D}"
+        )
+    if rope_cos.shape[1] != D or rope_sin.shape != rope_cos.shape:
+        raise ValueError("rope tables must be [positions, head_dim]")
+    if rope_cos.shape[0] <= int(pos_id):
+        raise ValueError(f"rope tables have {rope_cos.shape[0]} rows, pos_id is {pos_id}")
+    if matvec_reduction_size is None:
+        for r in (2048, 1024, 512):
+            if (Hq * D) % r == 0 and g.intermediate_size % r == 0:
+                matvec_reduction_size = r
+                break
+        else:
+            raise ValueError("cannot derive matvec_reduction_size from the shapes")
+    g.matvec_reduction_size = int(matvec_reduction_size)
+    g.pos_id = int(pos_id)
+    g.attn_scale = float(attn_scale)
+    g.rms_norm_eps = float(rms_norm_eps)
+    g.skip_attn_reduction = int(bool(skip_attn_reduction))
+    g.wait_timeout_ms = int(wait_timeout_ms)
+    g.status = _check_tensor("status", status, i32) if status is not None else None
+    return g
+
+
+def _stream_handle(stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    if isinstance(stream, int):
+        return stream
+    return int(stream.cuda_stream)
+
+
+def mk_llama(*args, stream=None, matvec_reduction_size=None, wait_timeout_ms=0, status=None):
+    """Enqueue one decode step; positional arguments as in the reference call.
+
+    ``(barriers, instructions, timings, qkv_w, attn_ln_w, o_w, mlp_ln_w, up_w,
+    gate_w, down_w, lm_head_norm_w, lm_head_w, k_cache4d, v_cache4d, rope_cos,
+    rope_sin, hidden_states, post_ln_rope_q, attn_out, attn_lse_intermediates,
+    attn_out_intermediates, silu_out, logits, pos_id, attn_scale, rms_norm_eps,
+    skip_attn_reduction, stream=...)``.  Asynchronous; raises
+    ``MegakernelError`` when host-side validation rejects the arguments.
+    """
+    if len(args) != 27:
+        raise TypeError(f"mk_llama expects 27 positional arguments, got {len(args)}")
+    lib = load_library()
+    g = pack_globals(
+        *args,
+        matvec_reduction_size=matvec_reduction_size,
+        wait_timeout_ms=wait_timeout_ms,
+        status=status,
+    )
+    rc = lib.mkb_launch(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
+    if rc != 0:
+        raise MegakernelError(rc, lib.mkb_last_error().decode())
+    return g
+
+
+def sync_status(g: MkbGlobals, stream=None) -> MkbStatus:
+    """Synchronise the stream and return the device status; raise on device errors."""
+    lib = load_library()
+    st = MkbStatus()
+    rc = lib.mkb_sync_status(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)), ctypes.byref(st))
+    if rc != 0:
+        msg = lib.mkb_last_error().decode()
+        raise MegakernelError(rc, msg, st)
+    return st
