@@ -152,6 +152,14 @@ int mkb_launch(const MkbGlobals *g, void *cuda_stream);
  */
 int mkb_sync_status(const MkbGlobals *g, void *cuda_stream, MkbStatus *out);
 
+/*
+ * Check a HOST copy of the instruction tensor ([num_sms, queue_len, 32] int32)
+ * against the shapes in `g`: every layer, block range, head and partial index
+ * must stay inside its tensor.  Call once per schedule, before the first launch.
+ * The reference has no counterpart (a bad schedule hangs or traps its kernel).
+ */
+int mkb_validate_instructions(const MkbGlobals *g, const int32_t *host_instructions);
+
 /* Message of the last host-side error raised on the calling thread. */
 const char *mkb_last_error(void);
 

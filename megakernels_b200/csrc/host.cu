@@ -1,0 +1,377 @@
+// C ABI of libmkb200.so (declared in include/mkb200.h): host-side validation,
+// TMA descriptor cache, launch and status read-back.  Replaces the pybind11
+// glue of the reference (demos/low-latency-llama/llama.cu:26-53), which builds
+// its descriptors on every call inside ThunderKittens' bind_kernel.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "mk_common.cuh"
+
+namespace mkb {
+__global__ void megakernel(const __grid_constant__ KParams p);
+}
+
+using namespace mkb;
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define MKB_CUDA(call)                                                                   \
+    do {                                                                                 \
+        cudaError_t e_ = (call);                                                         \
+        if (e_ != cudaSuccess)                                                           \
+            return fail(MKB_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_));   \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct KvMapKey {
+    const void* ptr;
+    int D, Hkv, T, LB;
+    bool operator==(const KvMapKey& o) const {
+        return ptr == o.ptr && D == o.D && Hkv == o.Hkv && T == o.T && LB == o.LB;
+    }
+};
+struct KvMapEntry {
+    KvMapKey key;
+    CUtensorMap map;
+};
+
+struct DeviceState {
+    bool attr_set = false;
+    int sm_count = 0;
+    int* status = nullptr;  // library-owned status record
+    std::vector<KvMapEntry> maps;
+};
+
+std::mutex g_mutex;
+DeviceState g_devices[64];
+EncodeTiledFn g_encode = nullptr;
+
+int get_encode_fn() {
+    if (g_encode) return MKB_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    MKB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
+        return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return MKB_OK;
+}
+
+// 4-D view [D, Hkv, T, L*B] of a KV cache; one box is TS positions of one head.
+int kv_tensor_map(DeviceState& ds, const void* ptr, int D, int Hkv, int T, int LB, CUtensorMap* out) {
+    KvMapKey key{ptr, D, Hkv, T, LB};
+    for (auto& e : ds.maps)
+        if (e.key == key) {
+            *out = e.map;
+            return MKB_OK;
+        }
+    int rc = get_encode_fn();
+    if (rc) return rc;
+    const int ts = (kStageBytes / 4) / D;
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)T, (cuuint64_t)LB};
+    cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)Hkv * D * 2, (cuuint64_t)T * Hkv * D * 2};
+    cuuint32_t box[4] = {(cuuint32_t)D, 1, (cuuint32_t)ts, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap m;
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    if (ds.maps.size() >= 64) ds.maps.erase(ds.maps.begin());
+    ds.maps.push_back({key, m});
+    *out = m;
+    return MKB_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate(const MkbGlobals* g) {
+    if (!g) return fail(MKB_ERR_INVALID_ARGUMENT, "globals pointer is NULL");
+    if (g->abi_version != MKB_ABI_VERSION)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "ABI version %u, library has %d", g->abi_version,
+                    MKB_ABI_VERSION);
+    if (g->struct_bytes != sizeof(MkbGlobals))
+        return fail(MKB_ERR_INVALID_ARGUMENT, "struct_bytes %u != %zu", g->struct_bytes,
+                    sizeof(MkbGlobals));
+    const struct {
+        const void* p;
+        const char* name;
+    } ptrs[] = {
+        {g->barriers, "barriers"},
+        {g->instructions, "instructions"},
+        {g->qkv_weights, "qkv_weights"},
+        {g->attn_ln_weights, "attn_ln_weights"},
+        {g->o_proj_weights, "o_proj_weights"},
+        {g->mlp_ln_weights, "mlp_ln_weights"},
+        {g->up_proj_weights, "up_proj_weights"},
+        {g->gate_proj_weights, "gate_proj_weights"},
+        {g->down_proj_weights, "down_proj_weights"},
+        {g->lm_head_norm_weights, "lm_head_norm_weights"},
+        {g->lm_head_weights, "lm_head_weights"},
+        {g->k_cache, "k_cache"},
+        {g->v_cache, "v_cache"},
+        {g->rope_cos, "rope_cos"},
+        {g->rope_sin, "rope_sin"},
+        {g->hidden_states, "hidden_states"},
+        {g->post_ln_rope_q, "post_ln_rope_q"},
+        {g->attn_out, "attn_out"},
+        {g->attn_lse_intermediates, "attn_lse_intermediates"},
+        {g->attn_out_intermediates, "attn_out_intermediates"},
+        {g->silu_out, "silu_out"},
+        {g->logits, "logits"},
+    };
+    for (const auto& e : ptrs) {
+        if (!e.p) return fail(MKB_ERR_INVALID_ARGUMENT, "%s is NULL", e.name);
+        if (!aligned16(e.p))
+            return fail(MKB_ERR_INVALID_ARGUMENT, "%s must be 16-byte aligned", e.name);
+    }
+    const int H = g->hidden_size, I = g->intermediate_size, D = g->head_dim, R = g->matvec_reduction_size;
+    const int Hq = g->num_attention_heads, Hkv = g->num_kv_heads;
+    if (g->num_layers < 1 || g->queue_len < 1 || g->num_sms < 1)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "num_layers, queue_len and num_sms must be positive");
+    if (H != 2048 && H != 4096 && H != 8192)
+        return fail(MKB_ERR_UNSUPPORTED, "hidden_size %d: supported are 2048, 4096, 8192", H);
+    if (D != 64 && D != 128) return fail(MKB_ERR_UNSUPPORTED, "head_dim %d: supported are 64, 128", D);
+    if (Hkv < 1 || Hq % Hkv != 0) return fail(MKB_ERR_INVALID_ARGUMENT, "Hq %d not a multiple of Hkv %d", Hq, Hkv);
+    const int gqa = Hq / Hkv;
+    if (!(gqa == 4 || (gqa == 8 && D == 128)))
+        return fail(MKB_ERR_UNSUPPORTED, "GQA ratio %d with head_dim %d is not supported", gqa, D);
+    if (Hq % 4 != 0) return fail(MKB_ERR_UNSUPPORTED, "Hq %d must be a multiple of 4", Hq);
+    if (R != 512 && R != 1024 && R != 2048)
+        return fail(MKB_ERR_UNSUPPORTED, "matvec_reduction_size %d: supported are 512, 1024, 2048", R);
+    if ((Hq * D) % R != 0 || I % R != 0)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "o-proj inputs %d and intermediate %d must be multiples of %d", Hq * D, I, R);
+    if (I % 16 != 0 || g->vocab_size % 16 != 0)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "intermediate and vocab sizes must be multiples of 16");
+    if (g->barrier_width < Hq + 2 * Hkv || g->barrier_width < I / R || g->barrier_ops < 6)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "barriers tensor too small: ops %d width %d", g->barrier_ops, g->barrier_width);
+    if (g->kv_batch < 1 || g->kv_max_len < 1)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "KV cache needs batch >= 1 and length >= 1");
+    if (g->pos_id < 0 || g->pos_id >= g->kv_max_len)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "pos_id %d outside the KV cache length %d", g->pos_id, g->kv_max_len);
+    if (g->max_partials < 1) return fail(MKB_ERR_INVALID_ARGUMENT, "max_partials must be >= 1");
+    return MKB_OK;
+}
+
+int device_state(DeviceState** out) {
+    int dev = 0;
+    MKB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MKB_ERR_UNSUPPORTED, "device index %d", dev);
+    DeviceState& ds = g_devices[dev];
+    if (!ds.attr_set) {
+        cudaDeviceProp prop;
+        MKB_CUDA(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major < 10)
+            return fail(MKB_ERR_UNSUPPORTED, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
+        ds.sm_count = prop.multiProcessorCount;
+        MKB_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc));
+        MKB_CUDA(cudaMalloc(&ds.status, MKB_STATUS_WORDS * sizeof(int)));
+        MKB_CUDA(cudaMemset(ds.status, 0, MKB_STATUS_WORDS * sizeof(int)));
+        ds.attr_set = true;
+    }
+    *out = &ds;
+    return MKB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
+    int rc = validate(g);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* ds = nullptr;
+    rc = device_state(&ds);
+    if (rc) return rc;
+    if (g->num_sms > ds->sm_count)
+        return fail(MKB_ERR_INVALID_ARGUMENT,
+                    "%d instruction queues but the device has %d SMs: all CTAs must be co-resident",
+                    g->num_sms, ds->sm_count);
+
+    KParams p;
+    memset(&p, 0, sizeof(p));
+    p.barriers = g->barriers;
+    p.instructions = g->instructions;
+    p.timings = g->timings;
+    p.status = g->status ? g->status : ds->status;
+    p.queue_len = g->queue_len;
+    p.barrier_ops = g->barrier_ops;
+    p.barrier_width = g->barrier_width;
+    p.qkv_w = (const __nv_bfloat16*)g->qkv_weights;
+    p.attn_ln_w = (const __nv_bfloat16*)g->attn_ln_weights;
+    p.o_w = (const __nv_bfloat16*)g->o_proj_weights;
+    p.mlp_ln_w = (const __nv_bfloat16*)g->mlp_ln_weights;
+    p.up_w = (const __nv_bfloat16*)g->up_proj_weights;
+    p.gate_w = (const __nv_bfloat16*)g->gate_proj_weights;
+    p.down_w = (const __nv_bfloat16*)g->down_proj_weights;
+    p.lm_norm_w = (const __nv_bfloat16*)g->lm_head_norm_weights;
+    p.lm_head_w = (const __nv_bfloat16*)g->lm_head_weights;
+    p.k_cache = (__nv_bfloat16*)g->k_cache;
+    p.v_cache = (__nv_bfloat16*)g->v_cache;
+    p.rope_cos = g->rope_cos;
+    p.rope_sin = g->rope_sin;
+    p.hidden = (__nv_bfloat16*)g->hidden_states;
+    p.q_rope = (__nv_bfloat16*)g->post_ln_rope_q;
+    p.attn_out = (__nv_bfloat16*)g->attn_out;
+    p.silu_out = (__nv_bfloat16*)g->silu_out;
+    p.logits = (__nv_bfloat16*)g->logits;
+    p.attn_lse = g->attn_lse_intermediates;
+    p.attn_o = g->attn_out_intermediates;
+    p.L = g->num_layers;
+    p.H = g->hidden_size;
+    p.I = g->intermediate_size;
+    p.D = g->head_dim;
+    p.Hq = g->num_attention_heads;
+    p.Hkv = g->num_kv_heads;
+    p.V = g->vocab_size;
+    p.T = g->kv_max_len;
+    p.B = g->kv_batch;
+    p.max_partials = g->max_partials;
+    p.R = g->matvec_reduction_size;
+    p.qkv_rows = (p.Hq + 2 * p.Hkv) * p.D;
+    p.o_in = p.Hq * p.D;
+    p.pos_id = g->pos_id;
+    p.attn_scale_log2e = g->attn_scale * 1.4426950408889634f;
+    p.rms_eps = g->rms_norm_eps;
+    p.skip_attn_reduction = g->skip_attn_reduction;
+    p.thr_qkv_waits_down = (p.H / 16) * (p.I / p.R);
+    p.thr_attn_waits_qkv = p.D / 16;
+    p.thr_oproj_waits_attn = p.Hq;
+    p.thr_upgate_waits_oproj = (p.H / 16) * (p.o_in / p.R);
+    p.thr_down_waits_upgate = p.R / 16;
+    const unsigned ms = g->wait_timeout_ms ? g->wait_timeout_ms : 2000u;
+    p.timeout_ns = (unsigned long long)ms * 1000000ull;
+
+    rc = kv_tensor_map(*ds, g->k_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.k_map);
+    if (rc) return rc;
+    rc = kv_tensor_map(*ds, g->v_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.v_map);
+    if (rc) return rc;
+
+    megakernel<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
+    MKB_CUDA(cudaGetLastError());
+    return MKB_OK;
+}
+
+int mkb_sync_status(const MkbGlobals* g, void* cuda_stream, MkbStatus* out) {
+    if (!out) return fail(MKB_ERR_INVALID_ARGUMENT, "status output pointer is NULL");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    MKB_CUDA(cudaStreamSynchronize((cudaStream_t)cuda_stream));
+    int* st = (g && g->status) ? g->status : ds->status;
+    int words[MKB_STATUS_WORDS];
+    MKB_CUDA(cudaMemcpy(words, st, sizeof(words), cudaMemcpyDeviceToHost));
+    memcpy(out, words, sizeof(MkbStatus));
+    if (words[0] != MKB_OK || words[kStatusAbortWord] != 0) {
+        MKB_CUDA(cudaMemset(st, 0, sizeof(words)));  // re-arm for the next launch
+        static const char* roles[] = {"loader", "consumer", "storer"};
+        const char* role = (out->role >= 0 && out->role < 3) ? roles[out->role] : "?";
+        return fail(out->code ? out->code : MKB_ERR_DEVICE_TIMEOUT,
+                    "device error %d on queue %d, instruction %d (opcode %d, %s): detail %d %d %d %d",
+                    out->code, out->sm, out->instruction_index, out->opcode, role, out->detail[0],
+                    out->detail[1], out->detail[2], out->detail[3]);
+    }
+    return MKB_OK;
+}
+
+// Host-side check of an instruction tensor (a HOST copy, [num_sms, queue_len, 32]):
+// every index an instruction carries must stay inside the tensors of `g`.
+int mkb_validate_instructions(const MkbGlobals* g, const int32_t* host_instructions) {
+    int rc = validate(g);
+    if (rc) return rc;
+    if (!host_instructions) return fail(MKB_ERR_INVALID_ARGUMENT, "host_instructions is NULL");
+    const int L = g->num_layers, H = g->hidden_size, I = g->intermediate_size, D = g->head_dim;
+    const int Hq = g->num_attention_heads, Hkv = g->num_kv_heads, R = g->matvec_reduction_size;
+    const int qkv_blocks = (Hq + 2 * Hkv) * D / 16;
+    for (int sm = 0; sm < g->num_sms; ++sm) {
+        for (int i = 0; i < g->queue_len; ++i) {
+            const int32_t* w = host_instructions + ((size_t)sm * g->queue_len + i) * MKB_INTS_PER_INSTRUCTION;
+            auto bad = [&](const char* what) {
+                return fail(MKB_ERR_INVALID_ARGUMENT, "queue %d instruction %d (opcode %d): %s", sm, i, w[0], what);
+            };
+            auto range_ok = [](int s, int e, int n) { return 0 <= s && s <= e && e <= n; };
+            switch (w[0]) {
+                case MKB_OP_NOOP:
+                    break;
+                case MKB_OP_RMS_QKV_ROPE_APPEND:
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (!range_ok(w[2], w[3], qkv_blocks)) return bad("block range outside the QKV rows");
+                    break;
+                case MKB_OP_PARTIAL_ATTENTION:
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (w[2] < 0 || w[2] >= Hkv) return bad("KV head out of range");
+                    if (w[3] < 1 || w[4] < 0 || w[4] >= w[3]) return bad("partial index outside num_partials");
+                    if (!g->skip_attn_reduction && w[4] >= g->max_partials) return bad("partial index beyond max_partials");
+                    if (g->skip_attn_reduction && w[3] != 1) return bad("skip_attn_reduction needs num_partials == 1");
+                    break;
+                case MKB_OP_ATTENTION_REDUCTION: {
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (w[2] < 0 || w[2] + 4 > Hq) return bad("head range outside the Q heads");
+                    const int n = w[5];
+                    if (n < 1 || n > 25) return bad("reduction list length must be 1..25");
+                    for (int j = 0; j < n; ++j)
+                        if (w[6 + j] < 0 || w[6 + j] >= g->max_partials) return bad("reduction index beyond max_partials");
+                    if (!w[4] && (w[6 + n] < 0 || w[6 + n] >= g->max_partials)) return bad("output partial index beyond max_partials");
+                } break;
+                case MKB_OP_O_PROJ_RESIDUAL:
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (!range_ok(w[2], w[3], H / 16)) return bad("block range outside the hidden rows");
+                    if (w[4] < 0 || w[4] >= Hq * D / R) return bad("reduction block out of range");
+                    break;
+                case MKB_OP_RMS_UPGATE_SILU:
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (w[2] < 0 || w[2] > MKB_INTS_PER_INSTRUCTION - 3) return bad("block list too long");
+                    for (int j = 0; j < w[2]; ++j)
+                        if (w[3 + j] < 0 || w[3 + j] >= I / 16) return bad("block outside the intermediate rows");
+                    break;
+                case MKB_OP_DOWN_PROJ_RESIDUAL:
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (!range_ok(w[2], w[3], H / 16)) return bad("block range outside the hidden rows");
+                    if (w[4] < 0 || w[4] >= I / R) return bad("reduction block out of range");
+                    break;
+                case MKB_OP_RMS_LM_HEAD:
+                    if (!range_ok(w[1], w[2], g->vocab_size / 16)) return bad("block range outside the vocabulary");
+                    break;
+                default:
+                    return bad("unknown opcode");
+            }
+        }
+    }
+    return MKB_OK;
+}
+
+const char* mkb_last_error(void) { return g_error; }
+
+int mkb_sm_count(void) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    return n;
+}
+
+int mkb_smem_bytes(void) { return kSmemAlloc; }
+int mkb_block_threads(void) { return kBlockThreads; }
+int mkb_abi_version(void) { return MKB_ABI_VERSION; }
+
+}  // extern "C"

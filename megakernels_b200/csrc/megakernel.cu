@@ -1,0 +1,1123 @@
+// The persistent decode megakernel: one CTA per SM interprets its instruction
+// queue.  Replaces the reference's `mk` kernel template and its seven op
+// structs (include/megakernel.cuh:166-171; demos/low-latency-llama/*.cu) with
+// shape-generic, hand-written sm_100a code:
+//
+//   loader warp   - walks the queue ahead of everybody else and streams every
+//                   weight block (cp.async.bulk) and KV tile (cp.async.bulk.tensor)
+//                   into a ring of 32 KiB stages; it never looks at a barrier,
+//                   because weights and old KV positions depend on nothing.
+//   16 consumer   - wait for the instruction's global barrier, load (and
+//   warps           RMS-normalise) the activation vector into registers, then
+//                   multiply ring stages against it with fp32 FMAs; each warp
+//                   owns a column slice, rows are reduced with warp shuffles.
+//   storer warp   - sums the per-warp partials of a 16-row block, applies the
+//                   op's epilogue (RoPE + KV append, SiLU*up, residual add,
+//                   logits) and signals the next op's barrier counter.
+#include "mk_common.cuh"
+
+namespace mkb {
+
+// --------------------------------------------------------------------------- //
+// control / error reporting
+// --------------------------------------------------------------------------- //
+struct Ctx {
+    const KParams* p;
+    uint32_t base;            // shared-window address of the aligned smem base
+    volatile int* cta_abort;  // generic pointer to the CTA-wide abort word
+    int instr;                // instruction index being executed (for reports)
+    int opcode;
+    int role;
+
+    __device__ __forceinline__ uint32_t full_bar(int slot) const { return base + kSmemBars + slot * 8; }
+    __device__ __forceinline__ uint32_t empty_bar(int slot) const {
+        return base + kSmemBars + (kNumStages + slot) * 8;
+    }
+    __device__ __forceinline__ uint32_t out_full_bar(int slot) const {
+        return base + kSmemBars + (2 * kNumStages + slot) * 8;
+    }
+    __device__ __forceinline__ uint32_t out_empty_bar(int slot) const {
+        return base + kSmemBars + (2 * kNumStages + kOutSlots + slot) * 8;
+    }
+    __device__ __forceinline__ uint32_t stage_addr(int slot) const {
+        return base + kSmemRing + slot * kStageBytes;
+    }
+};
+
+__device__ __noinline__ void report_error(const Ctx& c, int code, int d0, int d1, int d2, int d3) {
+    int* st = c.p->status;
+    if (atomicCAS(&st[0], 0, code) == 0) {
+        st[1] = blockIdx.x;
+        st[2] = c.instr;
+        st[3] = c.opcode;
+        st[4] = c.role;
+        st[5] = d0;
+        st[6] = d1;
+        st[7] = d2;
+        st[8] = d3;
+        __threadfence();
+    }
+    atomicExch(&st[kStatusAbortWord], 1);
+    *c.cta_abort = 1;
+}
+
+__device__ __forceinline__ bool global_abort(const Ctx& c) {
+    return *reinterpret_cast<volatile int*>(&c.p->status[kStatusAbortWord]) != 0;
+}
+
+// Bounded mbarrier wait.  Returns false when the CTA is aborting or the budget ran out.
+__device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t parity,
+                                            bool honour_abort) {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 127u) == 0) {
+            if (honour_abort && *c.cta_abort) return false;
+            unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > 2 * c.p->timeout_ns) {
+                // twice the counter budget: when a global counter is stuck, the report
+                // should come from the wait on that counter, not from its bystanders
+                report_error(c, MKB_ERR_DEVICE_TIMEOUT, -1, (int)bar, (int)parity, 0);
+                return false;
+            }
+            if (honour_abort && (spins & 2047u) == 0 && global_abort(c)) {
+                *c.cta_abort = 1;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(c, bar, parity, true);
+}
+
+// Warp-collective bounded wait: lane 0 runs the bounded loop, then EVERY lane
+// observes the completed phase itself.  The second step is not optional: data
+// written by TMA (or by other warps before their arrive) is only guaranteed
+// visible to a thread that performed the acquiring try_wait itself; lanes that
+// merely learn of the completion through a shuffle were seen reading stale
+// shared memory.  Returns false (uniformly) if the wait was abandoned.
+__device__ __forceinline__ bool warp_mbar_wait(const Ctx& c, uint32_t bar, uint32_t parity,
+                                               bool skip, int lane) {
+    int ok = 1;
+    if (!skip && lane == 0) ok = mbar_wait(c, bar, parity) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (skip || !ok) return false;
+    for (int k = 0; k < 4096 && !mbar_try_wait(bar, parity); ++k) {
+    }
+    return true;
+}
+
+// Bounded wait for `*addr >= threshold` with acquire semantics.
+__device__ __noinline__ bool wait_counter(const Ctx& c, const int* addr, int threshold, int layer,
+                                          int row, int slot) {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        int v = ld_acquire_gpu(addr);
+        if (v >= threshold) return true;
+        if ((++spins & 63u) == 0) {
+            if (*c.cta_abort) return false;
+            if (global_abort(c)) {
+                *c.cta_abort = 1;
+                return false;
+            }
+            unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > c.p->timeout_ns) {
+                report_error(c, MKB_ERR_DEVICE_TIMEOUT, layer, row, slot, v);
+                return false;
+            }
+        }
+        __nanosleep(20);
+    }
+}
+
+__device__ __forceinline__ int* bar_addr(const KParams& p, int layer, int row, int slot) {
+    return p.barriers + ((size_t)layer * p.barrier_ops + row) * p.barrier_width + slot;
+}
+
+// --------------------------------------------------------------------------- //
+// matvec geometry: how a 16-row x KC block is cut into ring stages and threads
+// --------------------------------------------------------------------------- //
+template <int KC>
+struct MV {
+    static constexpr int CHUNKS = KC / 8;                      // 16-byte chunks per row
+    static constexpr int CPT = CHUNKS > 512 ? CHUNKS / 512 : 1;  // chunks per thread
+    static constexpr int TPR = CHUNKS / CPT;                   // threads covering one row
+    static constexpr int G = kConsumerThreads / TPR;           // row groups
+    static constexpr int NR = (kStageBytes / (KC * 2)) > 16 ? 16 : (kStageBytes / (KC * 2));
+    static constexpr int SPB = kBlockRows / NR;                // stages per block
+    static constexpr int RPT = NR / G;                         // rows per thread per stage
+    static constexpr int NACC = kBlockRows / G;                // accumulators per thread
+    static constexpr int WPG = TPR / 32;                       // warps per group = partials per row
+    static constexpr int STAGE_TX = NR * KC * 2;
+};
+
+__host__ __device__ inline int stage_rows_for(int kc) {
+    int nr = kStageBytes / (kc * 2);
+    return nr > 16 ? 16 : nr;
+}
+__host__ __device__ inline int partials_per_row_for(int kc) {
+    int chunks = kc / 8;
+    return (chunks > 512 ? 512 : chunks) / 32;
+}
+
+// Sum N per-lane values across the warp so that lane `l` ends with the total
+// of element `l / (32 / N)`; costs N shuffles instead of 5 * N.
+template <int N>
+__device__ __forceinline__ float warp_transpose_reduce(float (&v)[N], int lane) {
+    static_assert(N == 1 || N == 2 || N == 4 || N == 8 || N == 16 || N == 32, "");
+    int o = 16;
+#pragma unroll
+    for (int n = N / 2; n >= 1; n >>= 1) {
+        const bool upper = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < n; ++i) {
+            float send = upper ? v[i] : v[i + n];
+            float keep = upper ? v[i + n] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+        o >>= 1;
+    }
+    float r = v[0];
+#pragma unroll
+    for (; o >= 1; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
+}
+
+// --------------------------------------------------------------------------- //
+// loader
+// --------------------------------------------------------------------------- //
+struct LoaderState {
+    uint32_t stage = 0;  // running stage counter over the whole queue
+    uint64_t policy;
+    bool dead = false;
+};
+
+__device__ __forceinline__ bool loader_acquire(const Ctx& c, LoaderState& ls, int& slot) {
+    slot = ls.stage % kNumStages;
+    uint32_t phase = (ls.stage / kNumStages) & 1u;
+    if (!mbar_wait(c, c.empty_bar(slot), phase ^ 1u)) {
+        ls.dead = true;
+        return false;
+    }
+    return true;
+}
+
+// stream one 16-row block: rows contiguous in memory when ld == kc
+__device__ __forceinline__ void loader_block(const Ctx& c, LoaderState& ls,
+                                             const __nv_bfloat16* src, int ld, int kc) {
+    const int nr = stage_rows_for(kc);
+    const uint32_t row_bytes = (uint32_t)kc * 2u;
+    for (int r0 = 0; r0 < kBlockRows && !ls.dead; r0 += nr) {
+        int slot;
+        if (!loader_acquire(c, ls, slot)) return;
+        const uint32_t bar = c.full_bar(slot);
+        const uint32_t dst = c.stage_addr(slot);
+        mbar_expect_tx(bar, row_bytes * nr);
+        const __nv_bfloat16* s = src + (size_t)r0 * ld;
+        if (ld == kc) {
+            tma_bulk_g2s(dst, s, row_bytes * nr, bar, ls.policy);
+        } else {
+            for (int r = 0; r < nr; ++r)
+                tma_bulk_g2s(dst + r * row_bytes, s + (size_t)r * ld, row_bytes, bar, ls.policy);
+        }
+        ls.stage++;
+    }
+}
+
+// split-KV geometry shared by loader and consumers
+struct AttnRange {
+    int t0;         // first position of this partial
+    int t_old_end;  // end of the positions that were in the cache before this token
+    int has_cur;    // the token being decoded falls into this partial
+    int n_stages;
+};
+__device__ __forceinline__ AttnRange attn_range(const KParams& p, int num_partials, int partial_idx) {
+    const int seq_len = p.pos_id + 1;
+    const int total_blocks = (seq_len + 15) / 16;
+    const int per = (total_blocks + num_partials - 1) / num_partials;
+    const int b0 = partial_idx * per;
+    const int b1 = min(b0 + per, total_blocks);
+    AttnRange r;
+    r.t0 = b0 * 16;
+    const int t1 = min(b1 * 16, seq_len);
+    r.has_cur = (p.pos_id >= r.t0 && p.pos_id < t1) ? 1 : 0;
+    r.t_old_end = r.has_cur ? p.pos_id : t1;
+    const int n_old = max(0, r.t_old_end - r.t0);
+    const int ts = (kStageBytes / 4) / p.D;  // positions per stage: K and V halves of 16 KiB
+    r.n_stages = (n_old + ts - 1) / ts;
+    return r;
+}
+
+__device__ void loader_main(Ctx c) {
+    const KParams& p = *c.p;
+    LoaderState ls;
+    ls.policy = l2_policy_evict_first();
+    const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
+    c.role = kRoleLoader;
+    for (int i = 0; i < p.queue_len && !ls.dead; ++i) {
+        const int* w = queue + i * MKB_INTS_PER_INSTRUCTION;
+        if (i + 1 < p.queue_len) prefetch_l1(w + MKB_INTS_PER_INSTRUCTION);
+        if (i + 2 < p.queue_len) prefetch_l1(w + 2 * MKB_INTS_PER_INSTRUCTION);
+        const int op = __ldg(w);
+        c.instr = i;
+        c.opcode = op;
+        if (*c.cta_abort) break;
+        switch (op) {
+            case MKB_OP_RMS_QKV_ROPE_APPEND: {
+                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
+                const __nv_bfloat16* base = p.qkv_w + (size_t)layer * p.qkv_rows * p.H;
+                for (int b = sb; b < eb; ++b)
+                    loader_block(c, ls, base + (size_t)b * kBlockRows * p.H, p.H, p.H);
+            } break;
+            case MKB_OP_O_PROJ_RESIDUAL: {
+                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3), rb = __ldg(w + 4);
+                const __nv_bfloat16* base = p.o_w + (size_t)layer * p.H * p.o_in + (size_t)rb * p.R;
+                for (int b = sb; b < eb; ++b)
+                    loader_block(c, ls, base + (size_t)b * kBlockRows * p.o_in, p.o_in, p.R);
+            } break;
+            case MKB_OP_RMS_UPGATE_SILU: {
+                const int layer = __ldg(w + 1), n = __ldg(w + 2);
+                const __nv_bfloat16* up = p.up_w + (size_t)layer * p.I * p.H;
+                const __nv_bfloat16* gate = p.gate_w + (size_t)layer * p.I * p.H;
+                for (int j = 0; j < n; ++j) {
+                    const size_t off = (size_t)__ldg(w + 3 + j) * kBlockRows * p.H;
+                    loader_block(c, ls, up + off, p.H, p.H);
+                    loader_block(c, ls, gate + off, p.H, p.H);
+                }
+            } break;
+            case MKB_OP_DOWN_PROJ_RESIDUAL: {
+                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3), rb = __ldg(w + 4);
+                const __nv_bfloat16* base = p.down_w + (size_t)layer * p.H * p.I + (size_t)rb * p.R;
+                for (int b = sb; b < eb; ++b)
+                    loader_block(c, ls, base + (size_t)b * kBlockRows * p.I, p.I, p.R);
+            } break;
+            case MKB_OP_RMS_LM_HEAD: {
+                const int sb = __ldg(w + 1), eb = __ldg(w + 2);
+                for (int b = sb; b < eb; ++b)
+                    loader_block(c, ls, p.lm_head_w + (size_t)b * kBlockRows * p.H, p.H, p.H);
+            } break;
+            case MKB_OP_PARTIAL_ATTENTION: {
+                const int layer = __ldg(w + 1), kvh = __ldg(w + 2), np = __ldg(w + 3), pi = __ldg(w + 4);
+                const AttnRange r = attn_range(p, np, pi);
+                const int ts = (kStageBytes / 4) / p.D;
+                for (int s = 0; s < r.n_stages && !ls.dead; ++s) {
+                    int slot;
+                    if (!loader_acquire(c, ls, slot)) break;
+                    const uint32_t bar = c.full_bar(slot);
+                    const uint32_t dst = c.stage_addr(slot);
+                    mbar_expect_tx(bar, kStageBytes);
+                    const int t = r.t0 + s * ts;
+                    tma_tile4_g2s(dst, &p.k_map, 0, kvh, t, layer * p.B, bar, ls.policy);
+                    tma_tile4_g2s(dst + kStageBytes / 2, &p.v_map, 0, kvh, t, layer * p.B, bar, ls.policy);
+                    ls.stage++;
+                }
+            } break;
+            default:
+                break;  // NoOp, AttentionReduction: nothing to stream
+        }
+    }
+    // hand the number of issued stages to the exit path
+    reinterpret_cast<volatile int*>(c.cta_abort)[1] = (int)ls.stage;
+}
+
+// --------------------------------------------------------------------------- //
+// consumers: matvec
+// --------------------------------------------------------------------------- //
+struct ConsumerState {
+    uint32_t stage = 0;  // running ring stage counter (mirrors the loader's)
+    uint32_t out = 0;    // running output-slot counter (mirrors the storer's)
+    uint32_t nverdict = 0;  // verdicts broadcast so far (selects one of two smem words)
+    bool dead = false;   // a wait of this warp failed: finish the instruction without waiting
+};
+
+// The 512 consumer threads must leave the instruction loop together (they share
+// a named barrier), so the decision to stop is taken by thread 0 only, written
+// to one of two alternating shared words and read by everyone after a barrier.
+__device__ __forceinline__ volatile int* verdict_word(const Ctx& c, ConsumerState& cs) {
+    return c.cta_abort + 2 + (cs.nverdict++ & 1u);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+    f[0] = bf16_lo(w.x); f[1] = bf16_hi(w.x);
+    f[2] = bf16_lo(w.y); f[3] = bf16_hi(w.y);
+    f[4] = bf16_lo(w.z); f[5] = bf16_hi(w.z);
+    f[6] = bf16_lo(w.w); f[7] = bf16_hi(w.w);
+}
+
+__device__ __forceinline__ float dot8(const uint4& w, const float* a, float acc) {
+    acc = fmaf(bf16_lo(w.x), a[0], acc);
+    acc = fmaf(bf16_hi(w.x), a[1], acc);
+    acc = fmaf(bf16_lo(w.y), a[2], acc);
+    acc = fmaf(bf16_hi(w.y), a[3], acc);
+    acc = fmaf(bf16_lo(w.z), a[4], acc);
+    acc = fmaf(bf16_hi(w.z), a[5], acc);
+    acc = fmaf(bf16_lo(w.w), a[6], acc);
+    acc = fmaf(bf16_hi(w.w), a[7], acc);
+    return acc;
+}
+
+// wait for ring stage `cs.stage` (lane 0 polls, result broadcast to the warp)
+__device__ __forceinline__ void consumer_wait_stage(const Ctx& c, ConsumerState& cs, int lane,
+                                                    int& slot) {
+    slot = cs.stage % kNumStages;
+    const uint32_t phase = (cs.stage / kNumStages) & 1u;
+    if (!warp_mbar_wait(c, c.full_bar(slot), phase, cs.dead, lane)) cs.dead = true;
+}
+__device__ __forceinline__ void consumer_release_stage(const Ctx& c, ConsumerState& cs, int lane,
+                                                       int slot) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(c.empty_bar(slot));
+    cs.stage++;
+}
+
+// Multiply `nblocks` consecutive ring blocks (16 rows x KC) against the
+// activation registers and hand each block's per-warp partial sums to the storer.
+template <int KC>
+__device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, int nblocks,
+                                               const float (&act)[MV<KC>::CPT * 8]) {
+    using M = MV<KC>;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int grp = tid / M::TPR;
+    const int col = tid % M::TPR;
+    const int wi = col >> 5;  // warp index inside its row group
+
+    for (int b = 0; b < nblocks; ++b) {
+        float acc[M::NACC];
+#pragma unroll
+        for (int i = 0; i < M::NACC; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int st = 0; st < M::SPB; ++st) {
+            int slot;
+            consumer_wait_stage(c, cs, lane, slot);
+            const uint32_t sbase = c.stage_addr(slot) + (uint32_t)grp * (KC * 2) + (uint32_t)col * 16;
+#pragma unroll
+            for (int j = 0; j < M::RPT; ++j) {
+#pragma unroll
+                for (int cc = 0; cc < M::CPT; ++cc) {
+                    const uint4 w = lds_v4(sbase + (uint32_t)(j * M::G) * (KC * 2) + cc * 512 * 16);
+                    acc[st * M::RPT + j] = dot8(w, &act[cc * 8], acc[st * M::RPT + j]);
+                }
+            }
+            consumer_release_stage(c, cs, lane, slot);
+        }
+        // acc[i] belongs to block row grp + i * G
+        const float total = warp_transpose_reduce<M::NACC>(acc, lane);
+        const int oslot = cs.out % kOutSlots;
+        const uint32_t ophase = (cs.out / kOutSlots) & 1u;
+        if (!warp_mbar_wait(c, c.out_empty_bar(oslot), ophase ^ 1u, cs.dead, lane)) cs.dead = true;
+        constexpr int LPE = 32 / M::NACC;  // lanes holding the same element
+        if ((lane % LPE) == 0) {
+            const int row = grp + (lane / LPE) * M::G;
+            float* out = reinterpret_cast<float*>(__cvta_shared_to_generic(
+                c.base + kSmemOut + (oslot * kOutSlotFloats + row * 16 + wi) * 4));
+            *out = total;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.out_full_bar(oslot));
+        cs.out++;
+    }
+}
+
+// Load this thread's slice of a bf16 activation vector (fp32 registers).
+template <int KC>
+__device__ __forceinline__ void load_activation(const __nv_bfloat16* vec,
+                                                float (&act)[MV<KC>::CPT * 8]) {
+    using M = MV<KC>;
+    const int col = threadIdx.x % M::TPR;
+#pragma unroll
+    for (int cc = 0; cc < M::CPT; ++cc) {
+        const uint4 v = ld_cg_v4(vec + (size_t)(col + cc * 512) * 8);
+        float f[8];
+        unpack8(v, f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) act[cc * 8 + k] = f[k];
+    }
+}
+
+// RMSNorm of the hidden state into registers.  Mirrors the reference's
+// arithmetic: fp32 statistics, bf16 round of x * rstd, then times the bf16
+// weight, rounded to bf16 (python_vm.py:50-56).
+template <int KC>
+__device__ __forceinline__ void rms_activation(const Ctx& c, const __nv_bfloat16* norm_w,
+                                               float (&act)[MV<KC>::CPT * 8]) {
+    using M = MV<KC>;
+    const KParams& p = *c.p;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int col = tid % M::TPR;
+    float wgt[M::CPT * 8];
+#pragma unroll
+    for (int cc = 0; cc < M::CPT; ++cc) {
+        const uint4 v = ld_nc_v4(norm_w + (size_t)(col + cc * 512) * 8);
+        float f[8];
+        unpack8(v, f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) wgt[cc * 8 + k] = f[k];
+    }
+    load_activation<KC>(p.hidden, act);
+    float ss = 0.f;
+    if (tid < M::TPR) {
+#pragma unroll
+        for (int k = 0; k < M::CPT * 8; ++k) ss = fmaf(act[k], act[k], ss);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float* red = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemRed));
+    if (lane == 0) red[warp] = ss;
+    consumer_sync();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < kConsumerWarps; ++k) tot += red[k];
+    const float rstd = rsqrtf(tot / (float)KC + p.rms_eps);
+#pragma unroll
+    for (int k = 0; k < M::CPT * 8; ++k) act[k] = bf16_round(wgt[k] * bf16_round(act[k] * rstd));
+}
+
+// Consumer thread 0 waits for a counter; the verdict reaches all 512 consumer
+// threads through shared memory so that they leave the instruction together.
+__device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerState& cs, int layer,
+                                                       int row, int slot, int threshold,
+                                                       bool needed) {
+    volatile int* verdict = verdict_word(c, cs);
+    if (threadIdx.x == 0) {
+        bool ok = !*c.cta_abort;
+        if (ok && needed) ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
+        *verdict = ok ? 1 : 0;
+    }
+    consumer_sync();
+    return *verdict != 0;
+}
+
+template <int KC>
+__device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
+                                                    const __nv_bfloat16* norm_w, int nblocks,
+                                                    int wait_layer, int wait_row, int threshold,
+                                                    bool needed) {
+    if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
+    float act[MV<KC>::CPT * 8];
+    rms_activation<KC>(c, norm_w, act);
+    consume_blocks<KC>(c, cs, nblocks, act);
+    return true;
+}
+
+template <int KC>
+__device__ __forceinline__ bool consumer_plain_matvec(const Ctx& c, ConsumerState& cs,
+                                                      const __nv_bfloat16* vec, int nblocks,
+                                                      int wait_layer, int wait_row, int wait_slot,
+                                                      int threshold) {
+    if (!consumers_wait_counter(c, cs, wait_layer, wait_row, wait_slot, threshold, true)) return false;
+    float act[MV<KC>::CPT * 8];
+    load_activation<KC>(vec, act);
+    consume_blocks<KC>(c, cs, nblocks, act);
+    return true;
+}
+
+// --------------------------------------------------------------------------- //
+// consumers: attention
+// --------------------------------------------------------------------------- //
+// Online-softmax state of one warp for GQA heads, DPL = D / 32 dims per lane.
+template <int GQA, int DPL>
+struct AttnAcc {
+    float m[GQA];       // running max (log2 domain)
+    float l[GQA];       // running denominator
+    float o[GQA][DPL];  // running numerator, this lane's dims
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+            m[h] = -INFINITY;
+            l[h] = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[h][i] = 0.f;
+        }
+    }
+};
+
+template <int DPL>
+__device__ __forceinline__ void load_row_smem(uint32_t addr, float (&f)[DPL]) {
+    if constexpr (DPL == 4) {
+        const uint2 w = lds_v2(addr);
+        f[0] = bf16_lo(w.x); f[1] = bf16_hi(w.x); f[2] = bf16_lo(w.y); f[3] = bf16_hi(w.y);
+    } else {
+        const uint32_t w = lds_u32(addr);
+        f[0] = bf16_lo(w); f[1] = bf16_hi(w);
+    }
+}
+template <int DPL>
+__device__ __forceinline__ void load_row_gmem(const __nv_bfloat16* ptr, float (&f)[DPL]) {
+    if constexpr (DPL == 4) {
+        const uint2 w = ld_cg_v2(ptr);
+        f[0] = bf16_lo(w.x); f[1] = bf16_hi(w.x); f[2] = bf16_lo(w.y); f[3] = bf16_hi(w.y);
+    } else {
+        const uint32_t w = ld_cg_u32(ptr);
+        f[0] = bf16_lo(w); f[1] = bf16_hi(w);
+    }
+}
+
+// Fold NP positions (scores already reduced: every lane holds s[j][h]) into acc.
+template <int GQA, int DPL, int NP>
+__device__ __forceinline__ void attn_fold(AttnAcc<GQA, DPL>& a, const float (&s)[NP][GQA],
+                                          const float (&v)[NP][DPL]) {
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+        float mx = a.m[h];
+#pragma unroll
+        for (int j = 0; j < NP; ++j) mx = fmaxf(mx, s[j][h]);
+        const float ms = (mx == -INFINITY) ? 0.f : mx;
+        const float alpha = exp2f(a.m[h] - ms);
+        a.m[h] = mx;
+        float lsum = a.l[h] * alpha;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) a.o[h][i] *= alpha;
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+            const float pj = exp2f(s[j][h] - ms);
+            lsum += pj;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) a.o[h][i] = fmaf(pj, v[j][i], a.o[h][i]);
+        }
+        a.l[h] = lsum;
+    }
+}
+
+template <int D, int GQA>
+__device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w) {
+    constexpr int DPL = D / 32;
+    constexpr int TS = (kStageBytes / 4) / D;      // positions per stage
+    constexpr int NPW = TS / kConsumerWarps;       // positions per warp per stage
+    constexpr int HP = kAttnHeadsPerPass;
+    const KParams& p = *c.p;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int layer = __ldg(w + 1), kvh = __ldg(w + 2), np = __ldg(w + 3), pi = __ldg(w + 4);
+    const AttnRange r = attn_range(p, np, pi);
+
+    // barrier: the GQA query heads, then this KV head's K and V blocks
+    {
+        volatile int* verdict = verdict_word(c, cs);
+        if (tid == 0) {
+            bool ok = !*c.cta_abort;
+            const int row = MKB_OP_RMS_QKV_ROPE_APPEND - 1;
+            for (int h = 0; h < GQA && ok; ++h)
+                ok = wait_counter(c, bar_addr(p, layer, row, kvh * GQA + h), p.thr_attn_waits_qkv, layer, row, kvh * GQA + h);
+            if (ok) ok = wait_counter(c, bar_addr(p, layer, row, p.Hq + kvh), p.thr_attn_waits_qkv, layer, row, p.Hq + kvh);
+            if (ok) ok = wait_counter(c, bar_addr(p, layer, row, p.Hq + p.Hkv + kvh), p.thr_attn_waits_qkv, layer, row, p.Hq + p.Hkv + kvh);
+            *verdict = ok ? 1 : 0;
+        }
+        consumer_sync();
+        if (*verdict == 0) return false;
+    }
+
+    // q for the GQA heads, pre-scaled into the log2 domain
+    float q[GQA][DPL];
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+        load_row_gmem<DPL>(p.q_rope + (size_t)(kvh * GQA + h) * D + lane * DPL, q[h]);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) q[h][i] *= p.attn_scale_log2e;
+    }
+
+    AttnAcc<GQA, DPL> acc;
+    acc.init();
+
+    for (int s = 0; s < r.n_stages; ++s) {
+        int slot;
+        consumer_wait_stage(c, cs, lane, slot);
+        const uint32_t kbase = c.stage_addr(slot);
+        const uint32_t vbase = kbase + kStageBytes / 2;
+        const int tbase = r.t0 + s * TS;
+        if (tbase + warp < r.t_old_end) {  // this warp has at least one valid position
+            float part[NPW * GQA];
+            float vv[NPW][DPL];
+#pragma unroll
+            for (int j = 0; j < NPW; ++j) {
+                const int pos_in_stage = warp + j * kConsumerWarps;
+                float kk[DPL];
+                load_row_smem<DPL>(kbase + (uint32_t)pos_in_stage * (D * 2) + lane * (DPL * 2), kk);
+                load_row_smem<DPL>(vbase + (uint32_t)pos_in_stage * (D * 2) + lane * (DPL * 2), vv[j]);
+#pragma unroll
+                for (int h = 0; h < GQA; ++h) {
+                    float d = 0.f;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) d = fmaf(q[h][i], kk[i], d);
+                    part[j * GQA + h] = d;
+                }
+            }
+            // lane l now gets the full dot product of element l / (32 / N)
+            constexpr int N = NPW * GQA;
+            static_assert(N <= 32, "scores per warp per stage must fit one warp");
+            const float mine = warp_transpose_reduce<N>(part, lane);
+            float s_all[NPW][GQA];
+#pragma unroll
+            for (int j = 0; j < NPW; ++j) {
+                const bool valid = (tbase + warp + j * kConsumerWarps) < r.t_old_end;
+#pragma unroll
+                for (int h = 0; h < GQA; ++h) {
+                    const float sv = __shfl_sync(0xffffffffu, mine, (j * GQA + h) * (32 / N));
+                    s_all[j][h] = valid ? sv : -INFINITY;
+                }
+            }
+            attn_fold<GQA, DPL, NPW>(acc, s_all, vv);
+        }
+        consumer_release_stage(c, cs, lane, slot);
+    }
+
+    // the token being decoded: its K/V were appended by another SM in this launch,
+    // so read them straight from global memory (after the barrier above)
+    if (warp == 0 && r.has_cur) {
+        const size_t off = (((size_t)layer * p.B) * p.T + p.pos_id) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
+        float kk[DPL];
+        float vv[1][DPL];
+        load_row_gmem<DPL>(p.k_cache + off, kk);
+        load_row_gmem<DPL>(p.v_cache + off, vv[0]);
+        float s1[1][GQA];
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) d = fmaf(q[h][i], kk[i], d);
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            s1[0][h] = d;
+        }
+        attn_fold<GQA, DPL, 1>(acc, s1, vv);
+    }
+
+    // merge the 16 warps pairwise through shared memory, HP heads per pass
+    float* scratch = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemAttn));
+#pragma unroll
+    for (int pass = 0; pass < GQA / HP; ++pass) {
+        for (int half = kConsumerWarps / 2; half >= 1; half >>= 1) {
+            if (warp >= half && warp < 2 * half) {
+                float* slot = scratch + (warp - half) * kAttnSlotFloats;
+#pragma unroll
+                for (int hh = 0; hh < HP; ++hh) {
+                    const int h = pass * HP + hh;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) slot[hh * 132 + lane * DPL + i] = acc.o[h][i];
+                    if (lane == 0) {
+                        slot[hh * 132 + 128] = acc.m[h];
+                        slot[hh * 132 + 129] = acc.l[h];
+                    }
+                }
+            }
+            consumer_sync();
+            if (warp < half) {
+                const float* slot = scratch + warp * kAttnSlotFloats;
+#pragma unroll
+                for (int hh = 0; hh < HP; ++hh) {
+                    const int h = pass * HP + hh;
+                    const float m2 = slot[hh * 132 + 128], l2 = slot[hh * 132 + 129];
+                    const float mx = fmaxf(acc.m[h], m2);
+                    const float ms = (mx == -INFINITY) ? 0.f : mx;
+                    const float a1 = exp2f(acc.m[h] - ms), a2 = exp2f(m2 - ms);
+                    acc.m[h] = mx;
+                    acc.l[h] = acc.l[h] * a1 + l2 * a2;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i)
+                        acc.o[h][i] = acc.o[h][i] * a1 + slot[hh * 132 + lane * DPL + i] * a2;
+                }
+            }
+            consumer_sync();
+        }
+    }
+
+    if (warp == 0 && !cs.dead) {
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+            const int head = kvh * GQA + h;
+            const float inv = acc.l[h] > 0.f ? 1.f / acc.l[h] : 0.f;
+            if (p.skip_attn_reduction) {
+                __nv_bfloat16* dst = p.attn_out + (size_t)head * D + lane * DPL;
+                if constexpr (DPL == 4) {
+                    uint2 v;
+                    v.x = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
+                    v.y = pack_bf16x2(acc.o[h][2] * inv, acc.o[h][3] * inv);
+                    *reinterpret_cast<uint2*>(dst) = v;
+                } else {
+                    *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
+                }
+            } else {
+                float* dst = p.attn_o + ((size_t)head * p.max_partials + pi) * D + lane * DPL;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) dst[i] = acc.o[h][i] * inv;
+                if (lane == 0)
+                    p.attn_lse[(size_t)head * p.max_partials + pi] =
+                        acc.l[h] > 0.f ? acc.m[h] + log2f(acc.l[h]) : -INFINITY;
+            }
+        }
+        __syncwarp();
+        if (p.skip_attn_reduction) {
+            if (lane == 0) {
+                __threadfence();
+                red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);
+            }
+        } else {
+            if (lane == 0) __threadfence();
+            __syncwarp();
+            if (lane < GQA)
+                red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, kvh * GQA + lane), 1);
+        }
+    }
+    return true;
+}
+
+// AttentionReduction: merge `n` partial (O, LSE) pairs for 4 consecutive heads.
+template <int D>
+__device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const int* w) {
+    constexpr int DPL = D / 32;
+    const KParams& p = *c.p;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int layer = __ldg(w + 1), h0 = __ldg(w + 2), num_partials = __ldg(w + 3);
+    const int is_terminal = __ldg(w + 4), n = __ldg(w + 5);
+    const int out_idx = __ldg(w + 6 + n);
+    volatile int* verdict = verdict_word(c, cs);
+    if (tid == 0) {
+        bool ok = !*c.cta_abort;
+        const int row = MKB_OP_PARTIAL_ATTENTION - 1;
+        for (int h = 0; h < 4 && ok; ++h)
+            ok = wait_counter(c, bar_addr(p, layer, row, h0 + h), num_partials, layer, row, h0 + h);
+        *verdict = ok ? 1 : 0;
+    }
+    consumer_sync();
+    if (*verdict == 0) return false;
+    if (warp >= 4) return true;
+
+    const int head = h0 + warp;
+    int idx = 0;
+    float lse = -INFINITY;
+    if (lane < n) {
+        idx = __ldg(w + 6 + lane);
+        lse = ld_cg_f32(p.attn_lse + (size_t)head * p.max_partials + idx);
+    }
+    float mx = lse;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
+    const float wgt = exp2f(lse - ms);
+    float denom = wgt;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    float o_acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o_acc[i] = 0.f;
+    for (int j = 0; j < n; ++j) {
+        const float wj = __shfl_sync(0xffffffffu, wgt, j);
+        const int ij = __shfl_sync(0xffffffffu, idx, j);
+        const float* src = p.attn_o + ((size_t)head * p.max_partials + ij) * D + lane * DPL;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o_acc[i] = fmaf(wj, ld_cg_f32(src + i), o_acc[i]);
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    if (is_terminal) {
+        __nv_bfloat16* dst = p.attn_out + (size_t)head * D + lane * DPL;
+        if constexpr (DPL == 4) {
+            uint2 v;
+            v.x = pack_bf16x2(o_acc[0] * inv, o_acc[1] * inv);
+            v.y = pack_bf16x2(o_acc[2] * inv, o_acc[3] * inv);
+            *reinterpret_cast<uint2*>(dst) = v;
+        } else {
+            *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(o_acc[0] * inv, o_acc[1] * inv);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence();
+            red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), 1);
+        }
+    } else {
+        float* dst = p.attn_o + ((size_t)head * p.max_partials + out_idx) * D + lane * DPL;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) dst[i] = o_acc[i] * inv;
+        if (lane == 0)
+            p.attn_lse[(size_t)head * p.max_partials + out_idx] =
+                denom > 0.f ? mx + log2f(denom) : -INFINITY;
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence();
+            red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, head), 1);
+        }
+    }
+    return true;
+}
+
+// --------------------------------------------------------------------------- //
+// consumer dispatch
+// --------------------------------------------------------------------------- //
+template <int KH>
+__device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
+    const KParams& p = *c.p;
+    switch (op) {
+        case MKB_OP_RMS_QKV_ROPE_APPEND: {
+            const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
+            return consumer_rms_matvec<KH>(c, cs, p.attn_ln_w + (size_t)layer * p.H, eb - sb,
+                                           layer - 1, MKB_OP_DOWN_PROJ_RESIDUAL - 1,
+                                           p.thr_qkv_waits_down, layer > 0);
+        }
+        case MKB_OP_RMS_UPGATE_SILU: {
+            const int layer = __ldg(w + 1), n = __ldg(w + 2);
+            return consumer_rms_matvec<KH>(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
+                                           MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true);
+        }
+        default: {  // MKB_OP_RMS_LM_HEAD
+            const int sb = __ldg(w + 1), eb = __ldg(w + 2);
+            return consumer_rms_matvec<KH>(c, cs, p.lm_norm_w, eb - sb, p.L - 1,
+                                           MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true);
+        }
+    }
+}
+
+template <int KR>
+__device__ bool consumer_residual_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
+    const KParams& p = *c.p;
+    const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3), rb = __ldg(w + 4);
+    if (op == MKB_OP_O_PROJ_RESIDUAL)
+        return consumer_plain_matvec<KR>(c, cs, p.attn_out + (size_t)rb * p.R, eb - sb, layer,
+                                         MKB_OP_ATTENTION_REDUCTION - 1, 0, p.thr_oproj_waits_attn);
+    return consumer_plain_matvec<KR>(c, cs, p.silu_out + (size_t)rb * p.R, eb - sb, layer,
+                                     MKB_OP_RMS_UPGATE_SILU - 1, rb, p.thr_down_waits_upgate);
+}
+
+__device__ void consumer_main(Ctx c) {
+    const KParams& p = *c.p;
+    ConsumerState cs;
+    const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
+    c.role = kRoleConsumer;
+    for (int i = 0; i < p.queue_len; ++i) {
+        const int* w = queue + i * MKB_INTS_PER_INSTRUCTION;
+        const int op = __ldg(w);
+        c.instr = i;
+        c.opcode = op;
+        bool ok = true;
+        switch (op) {
+            case MKB_OP_NOOP:
+                break;
+            case MKB_OP_RMS_QKV_ROPE_APPEND:
+            case MKB_OP_RMS_UPGATE_SILU:
+            case MKB_OP_RMS_LM_HEAD:
+                if (p.H == 2048) ok = consumer_rms_op<2048>(c, cs, op, w);
+                else if (p.H == 4096) ok = consumer_rms_op<4096>(c, cs, op, w);
+                else ok = consumer_rms_op<8192>(c, cs, op, w);
+                break;
+            case MKB_OP_O_PROJ_RESIDUAL:
+            case MKB_OP_DOWN_PROJ_RESIDUAL:
+                if (p.R == 2048) ok = consumer_residual_op<2048>(c, cs, op, w);
+                else if (p.R == 1024) ok = consumer_residual_op<1024>(c, cs, op, w);
+                else ok = consumer_residual_op<512>(c, cs, op, w);
+                break;
+            case MKB_OP_PARTIAL_ATTENTION: {
+                const int gqa = p.Hq / p.Hkv;
+                if (p.D == 64) ok = consumer_attention<64, 4>(c, cs, w);
+                else if (gqa == 4) ok = consumer_attention<128, 4>(c, cs, w);
+                else ok = consumer_attention<128, 8>(c, cs, w);
+            } break;
+            case MKB_OP_ATTENTION_REDUCTION:
+                if (p.D == 64) ok = consumer_attn_reduction<64>(c, cs, w);
+                else ok = consumer_attn_reduction<128>(c, cs, w);
+                break;
+            default:
+                if (threadIdx.x == 0) report_error(c, MKB_ERR_BAD_OPCODE, op, 0, 0, 0);
+                ok = false;
+                break;
+        }
+        if (!ok) break;  // `ok` is uniform over the 512 consumer threads
+    }
+}
+
+// --------------------------------------------------------------------------- //
+// storer
+// --------------------------------------------------------------------------- //
+struct StorerState {
+    uint32_t out = 0;
+    bool dead = false;
+    int* pending_addr = nullptr;  // barrier counter with unsignalled arrivals
+    int pending = 0;
+};
+
+// sum the per-warp partials of the next finished block; lane r < 16 gets row r
+__device__ __forceinline__ float storer_take_block(const Ctx& c, StorerState& ss, int lane,
+                                                   int partials) {
+    const int oslot = ss.out % kOutSlots;
+    const uint32_t ophase = (ss.out / kOutSlots) & 1u;
+    if (!warp_mbar_wait(c, c.out_full_bar(oslot), ophase, ss.dead, lane)) ss.dead = true;
+    // lane = row + 16 * half: each half sums every other partial
+    const int row = lane & 15, half = lane >> 4;
+    const uint32_t src = c.base + kSmemOut + (oslot * kOutSlotFloats + row * 16) * 4;
+    float v = 0.f;
+    for (int k = half; k < partials; k += 2) v += __uint_as_float(lds_u32(src + k * 4));
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(c.out_empty_bar(oslot));
+    ss.out++;
+    return v;
+}
+
+__device__ __forceinline__ void storer_flush(StorerState& ss, int lane) {
+    __syncwarp();
+    if (ss.pending > 0 && lane == 0) {
+        __threadfence();
+        red_release_gpu_add(ss.pending_addr, ss.pending);
+    }
+    ss.pending = 0;
+    ss.pending_addr = nullptr;
+}
+__device__ __forceinline__ void storer_signal(StorerState& ss, int lane, int* addr, int count) {
+    if (ss.pending_addr != addr) {
+        storer_flush(ss, lane);
+        ss.pending_addr = addr;
+    }
+    ss.pending += count;
+}
+
+__device__ void storer_main(Ctx c) {
+    const KParams& p = *c.p;
+    StorerState ss;
+    const int lane = threadIdx.x & 31;
+    const int row = lane & 15;
+    const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
+    c.role = kRoleStorer;
+    const int kh_partials = partials_per_row_for(p.H);
+    const int kr_partials = partials_per_row_for(p.R);
+    const int k_start = p.Hq * p.D, v_start = (p.Hq + p.Hkv) * p.D;
+
+    for (int i = 0; i < p.queue_len; ++i) {
+        const int* w = queue + i * MKB_INTS_PER_INSTRUCTION;
+        const int op = __ldg(w);
+        c.instr = i;
+        c.opcode = op;
+        int stop = 0;
+        if (lane == 0) stop = (*c.cta_abort != 0) || ss.dead;
+        if (__shfl_sync(0xffffffffu, stop, 0)) break;
+        switch (op) {
+            case MKB_OP_RMS_QKV_ROPE_APPEND: {
+                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
+                for (int b = sb; b < eb; ++b) {
+                    float v = bf16_round(storer_take_block(c, ss, lane, kh_partials));
+                    const int start = b * kBlockRows;
+                    if (start < v_start) {
+                        const int seg = start % p.D;
+                        const float cs_ = __ldg(p.rope_cos + (size_t)p.pos_id * p.D + seg + row);
+                        const float sn = __ldg(p.rope_sin + (size_t)p.pos_id * p.D + seg + row);
+                        const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                        const float rot = (row & 1) ? other : -other;
+                        v = v * cs_ + rot * sn;
+                    }
+                    const float hi = __shfl_down_sync(0xffffffffu, v, 1);
+                    __nv_bfloat16* dst;
+                    if (start < k_start) {
+                        dst = p.q_rope + start;
+                    } else {
+                        const size_t tok = (((size_t)layer * p.B) * p.T + p.pos_id) * p.Hkv * p.D;
+                        dst = (start < v_start) ? p.k_cache + tok + (start - k_start)
+                                                : p.v_cache + tok + (start - v_start);
+                    }
+                    if (lane < 16 && (lane & 1) == 0)
+                        *reinterpret_cast<uint32_t*>(dst + row) = pack_bf16x2(v, hi);
+                    storer_signal(ss, lane, bar_addr(p, layer, op - 1, start / p.D), 1);
+                }
+                storer_flush(ss, lane);
+            } break;
+            case MKB_OP_O_PROJ_RESIDUAL:
+            case MKB_OP_DOWN_PROJ_RESIDUAL: {
+                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
+                for (int b = sb; b < eb; ++b) {
+                    const float v = storer_take_block(c, ss, lane, kr_partials);
+                    const float hi = __shfl_down_sync(0xffffffffu, v, 1);
+                    if (lane < 16 && (lane & 1) == 0)
+                        red_add_bf16x2(p.hidden + b * kBlockRows + row, pack_bf16x2(v, hi));
+                }
+                storer_signal(ss, lane, bar_addr(p, layer, op - 1, 0), eb - sb);
+                storer_flush(ss, lane);
+            } break;
+            case MKB_OP_RMS_UPGATE_SILU: {
+                const int layer = __ldg(w + 1), n = __ldg(w + 2);
+                for (int j = 0; j < n; ++j) {
+                    const int b = __ldg(w + 3 + j);
+                    const float up = bf16_round(storer_take_block(c, ss, lane, kh_partials));
+                    const float gate = bf16_round(storer_take_block(c, ss, lane, kh_partials));
+                    const float act = bf16_round(gate / (1.f + __expf(-gate)));
+                    const float v = act * up;
+                    const float hi = __shfl_down_sync(0xffffffffu, v, 1);
+                    if (lane < 16 && (lane & 1) == 0)
+                        *reinterpret_cast<uint32_t*>(p.silu_out + b * kBlockRows + row) = pack_bf16x2(v, hi);
+                    storer_signal(ss, lane, bar_addr(p, layer, op - 1, b * kBlockRows / p.R), 1);
+                }
+                storer_flush(ss, lane);
+            } break;
+            case MKB_OP_RMS_LM_HEAD: {
+                const int sb = __ldg(w + 1), eb = __ldg(w + 2);
+                for (int b = sb; b < eb; ++b) {
+                    const float v = storer_take_block(c, ss, lane, kh_partials);
+                    const float hi = __shfl_down_sync(0xffffffffu, v, 1);
+                    if (lane < 16 && (lane & 1) == 0)
+                        *reinterpret_cast<uint32_t*>(p.logits + b * kBlockRows + row) = pack_bf16x2(v, hi);
+                }
+            } break;
+            default:
+                break;
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- //
+// kernel
+// --------------------------------------------------------------------------- //
+__global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_constant__ KParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - raw);
+
+    Ctx c;
+    c.p = &p;
+    c.base = base;
+    c.cta_abort = reinterpret_cast<volatile int*>(gbase + kSmemCtl);
+    c.instr = -1;
+    c.opcode = -1;
+    c.role = -1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kNumStages; ++s) {
+            mbar_init(c.full_bar(s), 1);
+            mbar_init(c.empty_bar(s), kConsumerWarps);
+        }
+        for (int s = 0; s < kOutSlots; ++s) {
+            mbar_init(c.out_full_bar(s), kConsumerWarps);
+            mbar_init(c.out_empty_bar(s), 1);
+        }
+        for (int k = 0; k < 8; ++k) c.cta_abort[k] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5;
+    if (warp < kConsumerWarps) {
+        consumer_main(c);
+    } else if (warp == kLoaderWarp) {
+        if ((threadIdx.x & 31) == 0) loader_main(c);
+    } else {
+        storer_main(c);
+    }
+    __syncthreads();
+
+    // No bulk copy may still be in flight when the CTA's shared memory goes away:
+    // wait (bounded) for every stage the loader issued most recently.
+    if (warp == kLoaderWarp && (threadIdx.x & 31) == 0) {
+        const uint32_t issued = (uint32_t)c.cta_abort[1];
+        const uint32_t first = issued > (uint32_t)kNumStages ? issued - kNumStages : 0u;
+        c.role = kRoleLoader;
+        for (uint32_t s = first; s < issued; ++s) {
+            const uint32_t bar = c.full_bar(s % kNumStages);
+            const uint32_t parity = (s / kNumStages) & 1u;
+            if (!mbar_try_wait(bar, parity)) mbar_wait_slow(c, bar, parity, false);
+        }
+    }
+}
+
+}  // namespace mkb

@@ -1,0 +1,223 @@
+// Shared definitions of the decode megakernel: geometry, kernel parameters and
+// the PTX wrappers (mbarrier, bulk-copy TMA, release/acquire global counters).
+//
+// Design (replaces include/megakernel.cuh, include/controller/*, include/util.cuh
+// and include/config.cuh of the reference):
+//   * one persistent CTA per SM, each walking its own instruction queue;
+//   * 16 consumer warps + 1 loader warp + 1 storer warp, every role decodes the
+//     instruction words itself, so there is no controller warp and no page
+//     allocator: the weight ring is one continuous sequence of 32 KiB stages
+//     that runs across instruction boundaries, which lets the loader stream the
+//     next instruction's weights while the consumers still wait on a barrier;
+//   * counters in HBM (`barriers[layer][opcode-1][slot]`) order instructions of
+//     different SMs: producers `red.release.gpu`, waiters `ld.acquire.gpu`;
+//   * every wait is bounded and reports into a status record instead of hanging.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mkb200.h"
+
+namespace mkb {
+
+// ---- geometry ------------------------------------------------------------ //
+constexpr int kConsumerWarps = 16;
+constexpr int kConsumerThreads = kConsumerWarps * 32;  // 512
+constexpr int kLoaderWarp = kConsumerWarps;            // warp 16
+constexpr int kStorerWarp = kConsumerWarps + 1;        // warp 17
+constexpr int kBlockThreads = (kConsumerWarps + 2) * 32;  // 576
+
+constexpr int kStageBytes = 32768;  // one ring stage
+constexpr int kNumStages = 6;       // 192 KiB of weights / KV in flight per SM
+constexpr int kOutSlots = 4;        // ring of per-block partial sums, consumer -> storer
+constexpr int kOutSlotFloats = 16 * 16;  // [row][partial]
+constexpr int kBlockRows = 16;      // output rows per matvec block
+
+// attention: cross-warp merge scratch, 8 slots x 4 heads x (D + m + l)
+constexpr int kAttnHeadsPerPass = 4;
+constexpr int kAttnSlotFloats = kAttnHeadsPerPass * (128 + 4);
+constexpr int kAttnScratchFloats = 8 * kAttnSlotFloats;
+
+// shared-memory map (byte offsets from the 1024-aligned base)
+constexpr int kSmemRing = 0;
+constexpr int kSmemOut = kSmemRing + kNumStages * kStageBytes;
+constexpr int kSmemAttn = kSmemOut + kOutSlots * kOutSlotFloats * 4;
+constexpr int kSmemRed = kSmemAttn + kAttnScratchFloats * 4;  // 32 floats
+constexpr int kSmemBars = kSmemRed + 32 * 4;                   // mbarriers, 8 B each
+constexpr int kNumMbars = 2 * kNumStages + 2 * kOutSlots;
+constexpr int kSmemCtl = kSmemBars + kNumMbars * 8;            // 8 ints of control words
+constexpr int kSmemTotal = kSmemCtl + 8 * 4;
+constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack to align the base
+
+enum Role { kRoleLoader = 0, kRoleConsumer = 1, kRoleStorer = 2 };
+
+// status record layout (int32 words), mirrors MkbStatus; word 15 is the abort flag
+constexpr int kStatusAbortWord = 15;
+
+// ---- kernel parameters ---------------------------------------------------- //
+struct KParams {
+    // vm
+    int* barriers;
+    const int* instructions;
+    int* timings;
+    int* status;
+    int queue_len, barrier_ops, barrier_width;
+    // weights
+    const __nv_bfloat16 *qkv_w, *attn_ln_w, *o_w, *mlp_ln_w, *up_w, *gate_w, *down_w, *lm_norm_w,
+        *lm_head_w;
+    __nv_bfloat16 *k_cache, *v_cache;
+    const float *rope_cos, *rope_sin;
+    __nv_bfloat16 *hidden, *q_rope, *attn_out, *silu_out, *logits;
+    float *attn_lse, *attn_o;
+    // dims
+    int L, H, I, D, Hq, Hkv, V, T, B, max_partials, R;
+    int qkv_rows;  // (Hq + 2 Hkv) * D
+    int o_in;      // Hq * D
+    // per token
+    int pos_id;
+    float attn_scale_log2e;  // attn_scale * log2(e)
+    float rms_eps;
+    int skip_attn_reduction;
+    // barrier thresholds, derived on the host from the shapes
+    int thr_qkv_waits_down;     // (H/16) * (I/R)
+    int thr_attn_waits_qkv;     // D/16
+    int thr_oproj_waits_attn;   // Hq
+    int thr_upgate_waits_oproj; // (H/16) * (o_in/R)
+    int thr_down_waits_upgate;  // R/16
+    unsigned long long timeout_ns;
+    // TMA descriptors of the KV cache, 4-D [D, Hkv, T, L*B], box {D, 1, TS, 1}
+    CUtensorMap k_map, v_map;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------- //
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// contiguous global -> shared bulk copy (TMA engine), completes on an mbarrier
+__device__ __forceinline__ void tma_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+// 4-D tiled tensor copy global -> shared
+__device__ __forceinline__ void tma_tile4_g2s(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                              int c2, int c3, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        ".L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_l1(const void* p) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ld_cg_v2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_cg_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void red_add_bf16x2(void* p, uint32_t packed) {
+    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(p), "r"(packed) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ float bf16_round(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+}  // namespace mkb
