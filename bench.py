@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--sched", default="wave")
     ap.add_argument("--attn-partitions", type=int, default=0, help="0 = pick from the length")
     ap.add_argument("--no-coalesce-o-proj", action="store_true")
+    ap.add_argument("--barrier-fill", type=int, default=0,
+                    help="experiment: preset all barrier counters (waits pass at once; results are garbage)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -260,7 +262,9 @@ def build_engine(args, device):
     schedule = make_schedule_builder("latency", options).build(model)
     schedule.globs.pos_id = prefill
     tensorize_instructions(schedule.globs, assign_to_sms(args.sched, schedule=schedule))
-    generator = MK_Generator(model, make_mk_interpreter("latency"), schedule)
+    generator = MK_Generator(
+        model, make_mk_interpreter("latency"), schedule, barrier_fill_val=args.barrier_fill
+    )
     info = dict(attn_partitions=n_part, queue_len=int(schedule.globs.instructions.shape[1]),
                 instructions=len(schedule.get_linear_instructions()))
     return cfg, prefill, model, schedule, generator, info
@@ -304,7 +308,7 @@ def run_ours(args):
     for i in range(K):
         # the body of MK_Generator.run, with events around the kernel launch
         globs.hidden_states[:] = embed[ids_dev[W + i]].reshape(-1)
-        globs.barriers.zero_()
+        gen.fill()
         globs.pos_id = prefill + W + i
         e0, e1 = launch_events[i]
         e0.record()

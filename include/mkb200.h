@@ -42,6 +42,23 @@ enum {
     MKB_OP_RMS_LM_HEAD = 7,
 };
 
+/* MkbGlobals.flags */
+#define MKB_FLAG_RECORD_TIMINGS 1u /* write per-instruction event times (ns) into `timings` */
+
+/* timing slots inside one instruction's 128-int row (low 32 bits of %globaltimer, ns);
+ * the reference records clock64 deltas at ids of its own (include/util.cuh:214-246) */
+enum {
+    MKB_T_CONSUMER_START = 0,      /* consumers reach the instruction */
+    MKB_T_CONSUMER_WAIT_DONE = 1,  /* its global barrier is satisfied */
+    MKB_T_CONSUMER_ACT_READY = 2,  /* activation vector (and RMSNorm) in registers */
+    MKB_T_CONSUMER_FIRST_STAGE = 3,/* first ring stage of the instruction has arrived */
+    MKB_T_CONSUMER_DONE = 4,       /* last block handed to the storer */
+    MKB_T_LOADER_START = 8,        /* loader reaches the instruction */
+    MKB_T_LOADER_DONE = 9,         /* last stage of the instruction issued */
+    MKB_T_STORER_START = 16,       /* storer reaches the instruction */
+    MKB_T_STORER_DONE = 17,        /* last barrier signal of the instruction sent */
+};
+
 /* return / status codes */
 enum {
     MKB_OK = 0,
@@ -119,7 +136,8 @@ typedef struct MkbGlobals {
     float rms_norm_eps;
     int32_t skip_attn_reduction;
 
-    /* ---- robustness ---- */
+    /* ---- options ---- */
+    uint32_t flags;           /* MKB_FLAG_* */
     uint32_t wait_timeout_ms; /* device-side wait budget; 0 selects the default (2000 ms) */
     int32_t *status;          /* MKB_STATUS_WORDS int32 written on device errors, or NULL to use
                                  the library's own per-device buffer */

@@ -4,6 +4,7 @@
 // its descriptors on every call inside ThunderKittens' bind_kernel.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -40,7 +41,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-struct KvMapKey {
+struct KvMapKey {  // also used for weight maps: (ptr, K, R, rows, L)
     const void* ptr;
     int D, Hkv, T, LB;
     bool operator==(const KvMapKey& o) const {
@@ -58,6 +59,16 @@ struct DeviceState {
     int* status = nullptr;  // library-owned status record
     std::vector<KvMapEntry> maps;
 };
+
+// L2 look-ahead of the loader in 32 KiB stages per SM; MKB_L2_WINDOW_KB overrides (0 disables).
+int l2_window_from_env() {
+    const char* e = getenv("MKB_L2_WINDOW_KB");
+    int kb = e ? atoi(e) : 512;
+    if (kb < 0) kb = 0;
+    if (kb > 4096) kb = 4096;
+    return kb == 0 ? 0 : kNumStages + kb * 1024 / kStageBytes;
+}
+const int g_l2_window_stages = l2_window_from_env();
 
 std::mutex g_mutex;
 DeviceState g_devices[64];
@@ -96,6 +107,35 @@ int kv_tensor_map(DeviceState& ds, const void* ptr, int D, int Hkv, int T, int L
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    if (ds.maps.size() >= 64) ds.maps.erase(ds.maps.begin());
+    ds.maps.push_back({key, m});
+    *out = m;
+    return MKB_OK;
+}
+
+// 4-D view [256, K/256, rows, L] of a stacked weight [L, rows, K]; one box is one ring
+// stage of an R-column slice: {256, R/256, rows per stage, 1}.
+int weight_tensor_map(DeviceState& ds, const void* ptr, int K, int R, int rows, int L, CUtensorMap* out) {
+    KvMapKey key{ptr, -K, R, rows, L};
+    for (auto& e : ds.maps)
+        if (e.key == key) {
+            *out = e.map;
+            return MKB_OK;
+        }
+    int rc = get_encode_fn();
+    if (rc) return rc;
+    const int nr = stage_rows_for(R);
+    cuuint64_t dims[4] = {256, (cuuint64_t)K / 256, (cuuint64_t)rows, (cuuint64_t)L};
+    cuuint64_t strides[3] = {512, (cuuint64_t)K * 2, (cuuint64_t)rows * K * 2};
+    cuuint32_t box[4] = {256, (cuuint32_t)R / 256, (cuuint32_t)nr, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap m;
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
     if (ds.maps.size() >= 64) ds.maps.erase(ds.maps.begin());
     ds.maps.push_back({key, m});
     *out = m;
@@ -212,7 +252,9 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     memset(&p, 0, sizeof(p));
     p.barriers = g->barriers;
     p.instructions = g->instructions;
-    p.timings = g->timings;
+    p.timings = (g->flags & MKB_FLAG_RECORD_TIMINGS) ? g->timings : nullptr;
+    if ((g->flags & MKB_FLAG_RECORD_TIMINGS) && !g->timings)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "MKB_FLAG_RECORD_TIMINGS needs a timings tensor");
     p.status = g->status ? g->status : ds->status;
     p.queue_len = g->queue_len;
     p.barrier_ops = g->barrier_ops;
@@ -261,11 +303,21 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     p.thr_down_waits_upgate = p.R / 16;
     const unsigned ms = g->wait_timeout_ms ? g->wait_timeout_ms : 2000u;
     p.timeout_ns = (unsigned long long)ms * 1000000ull;
+    p.l2_window_stages = g_l2_window_stages;
 
     rc = kv_tensor_map(*ds, g->k_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.k_map);
     if (rc) return rc;
     rc = kv_tensor_map(*ds, g->v_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.v_map);
     if (rc) return rc;
+
+    if (p.o_in != p.R) {
+        rc = weight_tensor_map(*ds, g->o_proj_weights, p.o_in, p.R, p.H, p.L, &p.o_map);
+        if (rc) return rc;
+    }
+    if (p.I != p.R) {
+        rc = weight_tensor_map(*ds, g->down_proj_weights, p.I, p.R, p.H, p.L, &p.down_map);
+        if (rc) return rc;
+    }
 
     megakernel<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     MKB_CUDA(cudaGetLastError());

@@ -44,6 +44,14 @@ struct Ctx {
     }
 };
 
+// one thread per role stamps event times (ns) into the instruction's timing row
+__device__ __forceinline__ void rec(const Ctx& c, int slot) {
+    int* t = c.p->timings;
+    if (t != nullptr && c.instr >= 0)
+        t[((size_t)blockIdx.x * c.p->queue_len + c.instr) * MKB_TIMING_SLOTS + slot] =
+            (int)(uint32_t)globaltimer_ns();
+}
+
 __device__ __noinline__ void report_error(const Ctx& c, int code, int d0, int d1, int d2, int d3) {
     int* st = c.p->status;
     if (atomicCAS(&st[0], 0, code) == 0) {
@@ -159,14 +167,6 @@ struct MV {
     static constexpr int STAGE_TX = NR * KC * 2;
 };
 
-__host__ __device__ inline int stage_rows_for(int kc) {
-    int nr = kStageBytes / (kc * 2);
-    return nr > 16 ? 16 : nr;
-}
-__host__ __device__ inline int partials_per_row_for(int kc) {
-    int chunks = kc / 8;
-    return (chunks > 512 ? 512 : chunks) / 32;
-}
 
 // Sum N per-lane values across the warp so that lane `l` ends with the total
 // of element `l / (32 / N)`; costs N shuffles instead of 5 * N.
@@ -194,44 +194,6 @@ __device__ __forceinline__ float warp_transpose_reduce(float (&v)[N], int lane) 
 // --------------------------------------------------------------------------- //
 // loader
 // --------------------------------------------------------------------------- //
-struct LoaderState {
-    uint32_t stage = 0;  // running stage counter over the whole queue
-    uint64_t policy;
-    bool dead = false;
-};
-
-__device__ __forceinline__ bool loader_acquire(const Ctx& c, LoaderState& ls, int& slot) {
-    slot = ls.stage % kNumStages;
-    uint32_t phase = (ls.stage / kNumStages) & 1u;
-    if (!mbar_wait(c, c.empty_bar(slot), phase ^ 1u)) {
-        ls.dead = true;
-        return false;
-    }
-    return true;
-}
-
-// stream one 16-row block: rows contiguous in memory when ld == kc
-__device__ __forceinline__ void loader_block(const Ctx& c, LoaderState& ls,
-                                             const __nv_bfloat16* src, int ld, int kc) {
-    const int nr = stage_rows_for(kc);
-    const uint32_t row_bytes = (uint32_t)kc * 2u;
-    for (int r0 = 0; r0 < kBlockRows && !ls.dead; r0 += nr) {
-        int slot;
-        if (!loader_acquire(c, ls, slot)) return;
-        const uint32_t bar = c.full_bar(slot);
-        const uint32_t dst = c.stage_addr(slot);
-        mbar_expect_tx(bar, row_bytes * nr);
-        const __nv_bfloat16* s = src + (size_t)r0 * ld;
-        if (ld == kc) {
-            tma_bulk_g2s(dst, s, row_bytes * nr, bar, ls.policy);
-        } else {
-            for (int r = 0; r < nr; ++r)
-                tma_bulk_g2s(dst + r * row_bytes, s + (size_t)r * ld, row_bytes, bar, ls.policy);
-        }
-        ls.stage++;
-    }
-}
-
 // split-KV geometry shared by loader and consumers
 struct AttnRange {
     int t0;         // first position of this partial
@@ -256,86 +218,228 @@ __device__ __forceinline__ AttnRange attn_range(const KParams& p, int num_partia
     return r;
 }
 
-__device__ void loader_main(Ctx c) {
-    const KParams& p = *c.p;
-    LoaderState ls;
-    ls.policy = l2_policy_evict_first();
-    const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
-    c.role = kRoleLoader;
-    for (int i = 0; i < p.queue_len && !ls.dead; ++i) {
-        const int* w = queue + i * MKB_INTS_PER_INSTRUCTION;
-        if (i + 1 < p.queue_len) prefetch_l1(w + MKB_INTS_PER_INSTRUCTION);
-        if (i + 2 < p.queue_len) prefetch_l1(w + 2 * MKB_INTS_PER_INSTRUCTION);
-        const int op = __ldg(w);
-        c.instr = i;
-        c.opcode = op;
-        if (*c.cta_abort) break;
+// One ring stage worth of work for the loader.
+struct StageDesc {
+    const __nv_bfloat16* src;  // contiguous weights: first row of the stage
+    int ld, kc, nr;            // row stride (elements), row length, rows in the stage
+    int kind;                  // kStageContig, kStageStrided or kStageAttn
+    const CUtensorMap* map;    // strided weights: 4-D view [256, K/256, rows, L]
+    int c1, c2, c3;            // ... and its coordinates (column chunk, row, layer)
+    int kvh, t, lb;            // K/V tile coordinates
+};
+enum { kStageContig = 0, kStageStrided = 1, kStageAttn = 2 };
+
+// Walks the instruction queue and yields its ring stages in consumption order.
+// The loader keeps two of these: one for the stages it copies into the ring and
+// one that runs ahead of it and only pulls the same bytes into L2.
+struct StreamCursor {
+    int i = -1;  // instruction index
+    int op = 0;
+    int b = 0, eb = 0;  // block (or KV stage) counter within the instruction
+    int r0 = 0;         // row offset inside the current 16-row block
+    int sb = 0;         // first block index of a range instruction
+    const __nv_bfloat16* base = nullptr;
+    const __nv_bfloat16* base2 = nullptr;  // gate matrix of the up/gate op
+    const int* w = nullptr;
+    int ld = 0, kc = 0, nr = 0;
+    int kvh = 0, t0 = 0, lb = 0, ts = 0;
+    const CUtensorMap* map = nullptr;  // set for column-sliced matrices (o-proj, down-proj)
+    int map_c1 = 0, map_layer = 0;
+
+    __device__ __forceinline__ void set_matrix(const __nv_bfloat16* m, int ld_, int kc_) {
+        base = m;
+        ld = ld_;
+        kc = kc_;
+        nr = stage_rows_for(kc_);
+    }
+
+    // decode instruction `i`; leaves b == eb when it streams nothing
+    __device__ void decode(const KParams& p, const int* queue) {
+        w = queue + i * MKB_INTS_PER_INSTRUCTION;
+        op = __ldg(w);
+        b = eb = 0;
+        r0 = 0;
+        map = nullptr;
         switch (op) {
-            case MKB_OP_RMS_QKV_ROPE_APPEND: {
-                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
-                const __nv_bfloat16* base = p.qkv_w + (size_t)layer * p.qkv_rows * p.H;
-                for (int b = sb; b < eb; ++b)
-                    loader_block(c, ls, base + (size_t)b * kBlockRows * p.H, p.H, p.H);
-            } break;
-            case MKB_OP_O_PROJ_RESIDUAL: {
-                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3), rb = __ldg(w + 4);
-                const __nv_bfloat16* base = p.o_w + (size_t)layer * p.H * p.o_in + (size_t)rb * p.R;
-                for (int b = sb; b < eb; ++b)
-                    loader_block(c, ls, base + (size_t)b * kBlockRows * p.o_in, p.o_in, p.R);
-            } break;
+            case MKB_OP_RMS_QKV_ROPE_APPEND:
+                sb = __ldg(w + 2);
+                eb = __ldg(w + 3) - sb;
+                set_matrix(p.qkv_w + (size_t)__ldg(w + 1) * p.qkv_rows * p.H, p.H, p.H);
+                break;
+            case MKB_OP_O_PROJ_RESIDUAL:
+                sb = __ldg(w + 2);
+                eb = __ldg(w + 3) - sb;
+                set_matrix(p.o_w + (size_t)__ldg(w + 1) * p.H * p.o_in + (size_t)__ldg(w + 4) * p.R,
+                           p.o_in, p.R);
+                if (p.o_in != p.R) {
+                    map = &p.o_map;
+                    map_c1 = __ldg(w + 4) * (p.R / 256);
+                    map_layer = __ldg(w + 1);
+                }
+                break;
             case MKB_OP_RMS_UPGATE_SILU: {
-                const int layer = __ldg(w + 1), n = __ldg(w + 2);
-                const __nv_bfloat16* up = p.up_w + (size_t)layer * p.I * p.H;
-                const __nv_bfloat16* gate = p.gate_w + (size_t)layer * p.I * p.H;
-                for (int j = 0; j < n; ++j) {
-                    const size_t off = (size_t)__ldg(w + 3 + j) * kBlockRows * p.H;
-                    loader_block(c, ls, up + off, p.H, p.H);
-                    loader_block(c, ls, gate + off, p.H, p.H);
+                const size_t off = (size_t)__ldg(w + 1) * p.I * p.H;
+                eb = 2 * __ldg(w + 2);
+                set_matrix(p.up_w + off, p.H, p.H);
+                base2 = p.gate_w + off;
+            } break;
+            case MKB_OP_DOWN_PROJ_RESIDUAL:
+                sb = __ldg(w + 2);
+                eb = __ldg(w + 3) - sb;
+                set_matrix(p.down_w + (size_t)__ldg(w + 1) * p.H * p.I + (size_t)__ldg(w + 4) * p.R,
+                           p.I, p.R);
+                if (p.I != p.R) {
+                    map = &p.down_map;
+                    map_c1 = __ldg(w + 4) * (p.R / 256);
+                    map_layer = __ldg(w + 1);
                 }
-            } break;
-            case MKB_OP_DOWN_PROJ_RESIDUAL: {
-                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3), rb = __ldg(w + 4);
-                const __nv_bfloat16* base = p.down_w + (size_t)layer * p.H * p.I + (size_t)rb * p.R;
-                for (int b = sb; b < eb; ++b)
-                    loader_block(c, ls, base + (size_t)b * kBlockRows * p.I, p.I, p.R);
-            } break;
-            case MKB_OP_RMS_LM_HEAD: {
-                const int sb = __ldg(w + 1), eb = __ldg(w + 2);
-                for (int b = sb; b < eb; ++b)
-                    loader_block(c, ls, p.lm_head_w + (size_t)b * kBlockRows * p.H, p.H, p.H);
-            } break;
+                break;
+            case MKB_OP_RMS_LM_HEAD:
+                sb = __ldg(w + 1);
+                eb = __ldg(w + 2) - sb;
+                set_matrix(p.lm_head_w, p.H, p.H);
+                break;
             case MKB_OP_PARTIAL_ATTENTION: {
-                const int layer = __ldg(w + 1), kvh = __ldg(w + 2), np = __ldg(w + 3), pi = __ldg(w + 4);
-                const AttnRange r = attn_range(p, np, pi);
-                const int ts = (kStageBytes / 4) / p.D;
-                for (int s = 0; s < r.n_stages && !ls.dead; ++s) {
-                    int slot;
-                    if (!loader_acquire(c, ls, slot)) break;
-                    const uint32_t bar = c.full_bar(slot);
-                    const uint32_t dst = c.stage_addr(slot);
-                    mbar_expect_tx(bar, kStageBytes);
-                    const int t = r.t0 + s * ts;
-                    tma_tile4_g2s(dst, &p.k_map, 0, kvh, t, layer * p.B, bar, ls.policy);
-                    tma_tile4_g2s(dst + kStageBytes / 2, &p.v_map, 0, kvh, t, layer * p.B, bar, ls.policy);
-                    ls.stage++;
-                }
+                const AttnRange r = attn_range(p, __ldg(w + 3), __ldg(w + 4));
+                kvh = __ldg(w + 2);
+                lb = __ldg(w + 1) * p.B;
+                t0 = r.t0;
+                ts = (kStageBytes / 4) / p.D;
+                eb = r.n_stages;
             } break;
             default:
-                break;  // NoOp, AttentionReduction: nothing to stream
+                break;
         }
     }
+
+    // next stage of the stream; false when the queue is exhausted
+    __device__ bool next(const KParams& p, const int* queue, StageDesc& d) {
+        while (b >= eb) {
+            if (++i >= p.queue_len) return false;
+            decode(p, queue);
+        }
+        if (op == MKB_OP_PARTIAL_ATTENTION) {
+            d.kind = kStageAttn;
+            d.kvh = kvh;
+            d.t = t0 + b * ts;
+            d.lb = lb;
+            ++b;
+            return true;
+        }
+        int blk;
+        const __nv_bfloat16* m = base;
+        if (op == MKB_OP_RMS_UPGATE_SILU) {
+            blk = __ldg(w + 3 + (b >> 1));
+            if (b & 1) m = base2;
+        } else {
+            blk = sb + b;
+        }
+        d.kind = map ? kStageStrided : kStageContig;
+        d.src = m + ((size_t)blk * kBlockRows + r0) * ld;
+        d.ld = ld;
+        d.kc = kc;
+        d.nr = nr;
+        d.map = map;
+        d.c1 = map_c1;
+        d.c2 = blk * kBlockRows + r0;
+        d.c3 = map_layer;
+        r0 += nr;
+        if (r0 >= kBlockRows) {
+            r0 = 0;
+            ++b;
+        }
+        return true;
+    }
+};
+
+__device__ __forceinline__ void prefetch_l2_bulk(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2_tile4(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map),
+                 "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
+__device__ void loader_main(Ctx c) {
+    const KParams& p = *c.p;
+    const uint64_t policy = l2_policy_evict_first();
+    const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
+    c.role = kRoleLoader;
+
+    StreamCursor issue, ahead;  // `ahead` is never behind `issue`
+    StageDesc d, da;
+    uint32_t stage = 0;       // stages copied into the ring so far
+    uint32_t ahead_stage = 0; // stages the look-ahead cursor has passed
+    bool ahead_more = true;
+    int last_instr = -1;
+    bool have = issue.next(p, queue, d);
+    while (have) {
+        if (issue.i != last_instr) {
+            if (last_instr >= 0) rec(c, MKB_T_LOADER_DONE);
+            last_instr = issue.i;
+            c.instr = issue.i;
+            c.opcode = issue.op;
+            rec(c, MKB_T_LOADER_START);
+            if (issue.i + 2 < p.queue_len) prefetch_l1(queue + (issue.i + 2) * MKB_INTS_PER_INSTRUCTION);
+            if (*c.cta_abort) break;
+        }
+        const int slot = stage % kNumStages;
+        const uint32_t parity = ((stage / kNumStages) & 1u) ^ 1u;
+        if (!mbar_try_wait(c.empty_bar(slot), parity)) {
+            // ring full: use the time to pull upcoming weights into L2, where the
+            // stalls of this SM's consumers cannot stop HBM from streaming
+            if (ahead_more && (int)(ahead_stage - stage) < p.l2_window_stages) {
+                if (ahead_stage < stage + kNumStages) {
+                    // skip what the ring already holds or is about to receive
+                    ahead_more = ahead.next(p, queue, da);
+                    ++ahead_stage;
+                    continue;
+                }
+                ahead_more = ahead.next(p, queue, da);
+                if (ahead_more) {
+                    ++ahead_stage;
+                    if (da.kind == kStageContig)
+                        prefetch_l2_bulk(da.src, (uint32_t)da.kc * 2u * da.nr);
+                    else if (da.kind == kStageStrided)
+                        prefetch_l2_tile4(da.map, 0, da.c1, da.c2, da.c3);
+                }
+                continue;
+            }
+            if (!mbar_wait_slow(c, c.empty_bar(slot), parity, true)) break;
+        }
+        const uint32_t bar = c.full_bar(slot);
+        const uint32_t dst = c.stage_addr(slot);
+        if (d.kind == kStageAttn) {
+            mbar_expect_tx(bar, kStageBytes);
+            tma_tile4_g2s(dst, &p.k_map, 0, d.kvh, d.t, d.lb, bar, policy);
+            tma_tile4_g2s(dst + kStageBytes / 2, &p.v_map, 0, d.kvh, d.t, d.lb, bar, policy);
+        } else {
+            const uint32_t bytes = (uint32_t)d.kc * 2u * d.nr;
+            mbar_expect_tx(bar, bytes);
+            if (d.kind == kStageContig)
+                tma_bulk_g2s(dst, d.src, bytes, bar, policy);
+            else  // one tiled copy brings nr rows x kc columns of a column-sliced matrix
+                tma_tile4_g2s(dst, d.map, 0, d.c1, d.c2, d.c3, bar, policy);
+        }
+        ++stage;
+        have = issue.next(p, queue, d);
+    }
+    if (last_instr >= 0) rec(c, MKB_T_LOADER_DONE);
     // hand the number of issued stages to the exit path
-    reinterpret_cast<volatile int*>(c.cta_abort)[1] = (int)ls.stage;
+    reinterpret_cast<volatile int*>(c.cta_abort)[1] = (int)stage;
 }
 
 // --------------------------------------------------------------------------- //
 // consumers: matvec
 // --------------------------------------------------------------------------- //
 struct ConsumerState {
-    uint32_t stage = 0;  // running ring stage counter (mirrors the loader's)
-    uint32_t out = 0;    // running output-slot counter (mirrors the storer's)
+    uint32_t slot = 0;    // ring slot of the next stage (mirrors the loader's sequence)
+    uint32_t phase = 0;   // parity of that slot's current use
+    uint32_t oslot = 0;   // output-ring slot of the next block (mirrors the storer's)
+    uint32_t ophase = 0;
     uint32_t nverdict = 0;  // verdicts broadcast so far (selects one of two smem words)
-    bool dead = false;   // a wait of this warp failed: finish the instruction without waiting
+    bool dead = false;   // a wait of this thread failed: finish the instruction without waiting
 };
 
 // The 512 consumer threads must leave the instruction loop together (they share
@@ -364,18 +468,22 @@ __device__ __forceinline__ float dot8(const uint4& w, const float* a, float acc)
     return acc;
 }
 
-// wait for ring stage `cs.stage` (lane 0 polls, result broadcast to the warp)
-__device__ __forceinline__ void consumer_wait_stage(const Ctx& c, ConsumerState& cs, int lane,
-                                                    int& slot) {
-    slot = cs.stage % kNumStages;
-    const uint32_t phase = (cs.stage / kNumStages) & 1u;
-    if (!warp_mbar_wait(c, c.full_bar(slot), phase, cs.dead, lane)) cs.dead = true;
+// Wait for the ring stage at cs.slot.  Every lane performs the acquiring
+// try_wait itself (see warp_mbar_wait for why); the bounded slow path is rare.
+__device__ __forceinline__ uint32_t consumer_wait_stage(const Ctx& c, ConsumerState& cs) {
+    const uint32_t bar = c.full_bar(cs.slot);
+    if (!cs.dead && !mbar_try_wait(bar, cs.phase)) {
+        if (!mbar_wait_slow(c, bar, cs.phase, true)) cs.dead = true;
+    }
+    return c.stage_addr(cs.slot);
 }
-__device__ __forceinline__ void consumer_release_stage(const Ctx& c, ConsumerState& cs, int lane,
-                                                       int slot) {
+__device__ __forceinline__ void consumer_release_stage(const Ctx& c, ConsumerState& cs, int lane) {
     __syncwarp();
-    if (lane == 0) mbar_arrive(c.empty_bar(slot));
-    cs.stage++;
+    if (lane == 0) mbar_arrive(c.empty_bar(cs.slot));
+    if (++cs.slot == kNumStages) {
+        cs.slot = 0;
+        cs.phase ^= 1u;
+    }
 }
 
 // Multiply `nblocks` consecutive ring blocks (16 rows x KC) against the
@@ -390,15 +498,15 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
     const int col = tid % M::TPR;
     const int wi = col >> 5;  // warp index inside its row group
 
+    const uint32_t thread_off = (uint32_t)grp * (KC * 2) + (uint32_t)col * 16;
     for (int b = 0; b < nblocks; ++b) {
         float acc[M::NACC];
 #pragma unroll
         for (int i = 0; i < M::NACC; ++i) acc[i] = 0.f;
 #pragma unroll
         for (int st = 0; st < M::SPB; ++st) {
-            int slot;
-            consumer_wait_stage(c, cs, lane, slot);
-            const uint32_t sbase = c.stage_addr(slot) + (uint32_t)grp * (KC * 2) + (uint32_t)col * 16;
+            const uint32_t sbase = consumer_wait_stage(c, cs) + thread_off;
+            if (st == 0 && b == 0 && tid == 0) rec(c, MKB_T_CONSUMER_FIRST_STAGE);
 #pragma unroll
             for (int j = 0; j < M::RPT; ++j) {
 #pragma unroll
@@ -407,23 +515,27 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
                     acc[st * M::RPT + j] = dot8(w, &act[cc * 8], acc[st * M::RPT + j]);
                 }
             }
-            consumer_release_stage(c, cs, lane, slot);
+            consumer_release_stage(c, cs, lane);
         }
         // acc[i] belongs to block row grp + i * G
         const float total = warp_transpose_reduce<M::NACC>(acc, lane);
-        const int oslot = cs.out % kOutSlots;
-        const uint32_t ophase = (cs.out / kOutSlots) & 1u;
-        if (!warp_mbar_wait(c, c.out_empty_bar(oslot), ophase ^ 1u, cs.dead, lane)) cs.dead = true;
+        const uint32_t obar = c.out_empty_bar(cs.oslot);
+        if (!cs.dead && !mbar_try_wait(obar, cs.ophase ^ 1u)) {
+            if (!mbar_wait_slow(c, obar, cs.ophase ^ 1u, true)) cs.dead = true;
+        }
         constexpr int LPE = 32 / M::NACC;  // lanes holding the same element
         if ((lane % LPE) == 0) {
             const int row = grp + (lane / LPE) * M::G;
             float* out = reinterpret_cast<float*>(__cvta_shared_to_generic(
-                c.base + kSmemOut + (oslot * kOutSlotFloats + row * 16 + wi) * 4));
+                c.base + kSmemOut + (cs.oslot * kOutSlotFloats + row * 16 + wi) * 4));
             *out = total;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(c.out_full_bar(oslot));
-        cs.out++;
+        if (lane == 0) mbar_arrive(c.out_full_bar(cs.oslot));
+        if (++cs.oslot == kOutSlots) {
+            cs.oslot = 0;
+            cs.ophase ^= 1u;
+        }
     }
 }
 
@@ -490,6 +602,7 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     if (threadIdx.x == 0) {
         bool ok = !*c.cta_abort;
         if (ok && needed) ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
+        rec(c, MKB_T_CONSUMER_WAIT_DONE);
         *verdict = ok ? 1 : 0;
     }
     consumer_sync();
@@ -504,6 +617,7 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
     if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
     float act[MV<KC>::CPT * 8];
     rms_activation<KC>(c, norm_w, act);
+    if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks<KC>(c, cs, nblocks, act);
     return true;
 }
@@ -516,6 +630,7 @@ __device__ __forceinline__ bool consumer_plain_matvec(const Ctx& c, ConsumerStat
     if (!consumers_wait_counter(c, cs, wait_layer, wait_row, wait_slot, threshold, true)) return false;
     float act[MV<KC>::CPT * 8];
     load_activation<KC>(vec, act);
+    if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks<KC>(c, cs, nblocks, act);
     return true;
 }
@@ -608,6 +723,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
                 ok = wait_counter(c, bar_addr(p, layer, row, kvh * GQA + h), p.thr_attn_waits_qkv, layer, row, kvh * GQA + h);
             if (ok) ok = wait_counter(c, bar_addr(p, layer, row, p.Hq + kvh), p.thr_attn_waits_qkv, layer, row, p.Hq + kvh);
             if (ok) ok = wait_counter(c, bar_addr(p, layer, row, p.Hq + p.Hkv + kvh), p.thr_attn_waits_qkv, layer, row, p.Hq + p.Hkv + kvh);
+            rec(c, MKB_T_CONSUMER_WAIT_DONE);
             *verdict = ok ? 1 : 0;
         }
         consumer_sync();
@@ -623,13 +739,22 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         for (int i = 0; i < DPL; ++i) q[h][i] *= p.attn_scale_log2e;
     }
 
+    // the token being decoded: its K/V were appended by another SM in this launch,
+    // so warp 0 reads them straight from global memory (issued now, used last)
+    float k_cur[DPL], v_cur[1][DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) k_cur[i] = v_cur[0][i] = 0.f;
+    if (warp == 0 && r.has_cur) {
+        const size_t off = (((size_t)layer * p.B) * p.T + p.pos_id) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
+        load_row_gmem<DPL>(p.k_cache + off, k_cur);
+        load_row_gmem<DPL>(p.v_cache + off, v_cur[0]);
+    }
+
     AttnAcc<GQA, DPL> acc;
     acc.init();
 
     for (int s = 0; s < r.n_stages; ++s) {
-        int slot;
-        consumer_wait_stage(c, cs, lane, slot);
-        const uint32_t kbase = c.stage_addr(slot);
+        const uint32_t kbase = consumer_wait_stage(c, cs);
         const uint32_t vbase = kbase + kStageBytes / 2;
         const int tbase = r.t0 + s * TS;
         if (tbase + warp < r.t_old_end) {  // this warp has at least one valid position
@@ -665,28 +790,21 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
             }
             attn_fold<GQA, DPL, NPW>(acc, s_all, vv);
         }
-        consumer_release_stage(c, cs, lane, slot);
+        consumer_release_stage(c, cs, lane);
     }
 
-    // the token being decoded: its K/V were appended by another SM in this launch,
-    // so read them straight from global memory (after the barrier above)
     if (warp == 0 && r.has_cur) {
-        const size_t off = (((size_t)layer * p.B) * p.T + p.pos_id) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
-        float kk[DPL];
-        float vv[1][DPL];
-        load_row_gmem<DPL>(p.k_cache + off, kk);
-        load_row_gmem<DPL>(p.v_cache + off, vv[0]);
         float s1[1][GQA];
 #pragma unroll
         for (int h = 0; h < GQA; ++h) {
             float d = 0.f;
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) d = fmaf(q[h][i], kk[i], d);
+            for (int i = 0; i < DPL; ++i) d = fmaf(q[h][i], k_cur[i], d);
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
             s1[0][h] = d;
         }
-        attn_fold<GQA, DPL, 1>(acc, s1, vv);
+        attn_fold<GQA, DPL, 1>(acc, s1, v_cur);
     }
 
     // merge the 16 warps pairwise through shared memory, HP heads per pass
@@ -754,13 +872,9 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         }
         __syncwarp();
         if (p.skip_attn_reduction) {
-            if (lane == 0) {
-                __threadfence();
+            if (lane == 0)
                 red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);
-            }
         } else {
-            if (lane == 0) __threadfence();
-            __syncwarp();
             if (lane < GQA)
                 red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, kvh * GQA + lane), 1);
         }
@@ -783,6 +897,7 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
         const int row = MKB_OP_PARTIAL_ATTENTION - 1;
         for (int h = 0; h < 4 && ok; ++h)
             ok = wait_counter(c, bar_addr(p, layer, row, h0 + h), num_partials, layer, row, h0 + h);
+        rec(c, MKB_T_CONSUMER_WAIT_DONE);
         *verdict = ok ? 1 : 0;
     }
     consumer_sync();
@@ -807,12 +922,30 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
     float o_acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) o_acc[i] = 0.f;
-    for (int j = 0; j < n; ++j) {
-        const float wj = __shfl_sync(0xffffffffu, wgt, j);
-        const int ij = __shfl_sync(0xffffffffu, idx, j);
-        const float* src = p.attn_o + ((size_t)head * p.max_partials + ij) * D + lane * DPL;
+    // batches of 8 partials: issue all loads of a batch, then accumulate, so the
+    // L2 round trips overlap instead of adding up
+    for (int j0 = 0; j0 < n; j0 += 8) {
+        float part[8][DPL];
+        float wj[8];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) o_acc[i] = fmaf(wj, ld_cg_f32(src + i), o_acc[i]);
+        for (int jj = 0; jj < 8; ++jj) {
+            const int j = j0 + jj;
+            const int ij = __shfl_sync(0xffffffffu, idx, j & 31);
+            wj[jj] = (j < n) ? __shfl_sync(0xffffffffu, wgt, j & 31) : 0.f;
+            const float* src = p.attn_o + ((size_t)head * p.max_partials + (j < n ? ij : 0)) * D + lane * DPL;
+            if constexpr (DPL == 4) {
+                const uint4 v = ld_cg_v4(src);
+                part[jj][0] = __uint_as_float(v.x); part[jj][1] = __uint_as_float(v.y);
+                part[jj][2] = __uint_as_float(v.z); part[jj][3] = __uint_as_float(v.w);
+            } else {
+                const uint2 v = ld_cg_v2(src);
+                part[jj][0] = __uint_as_float(v.x); part[jj][1] = __uint_as_float(v.y);
+            }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o_acc[i] = fmaf(wj[jj], part[jj][i], o_acc[i]);
     }
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
     if (is_terminal) {
@@ -826,10 +959,7 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
             *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(o_acc[0] * inv, o_acc[1] * inv);
         }
         __syncwarp();
-        if (lane == 0) {
-            __threadfence();
-            red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), 1);
-        }
+        if (lane == 0) red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), 1);
     } else {
         float* dst = p.attn_o + ((size_t)head * p.max_partials + out_idx) * D + lane * DPL;
 #pragma unroll
@@ -838,10 +968,7 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
             p.attn_lse[(size_t)head * p.max_partials + out_idx] =
                 denom > 0.f ? mx + log2f(denom) : -INFINITY;
         __syncwarp();
-        if (lane == 0) {
-            __threadfence();
-            red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, head), 1);
-        }
+        if (lane == 0) red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, head), 1);
     }
     return true;
 }
@@ -894,6 +1021,7 @@ __device__ void consumer_main(Ctx c) {
         c.instr = i;
         c.opcode = op;
         bool ok = true;
+        if (threadIdx.x == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_CONSUMER_START);
         switch (op) {
             case MKB_OP_NOOP:
                 break;
@@ -925,6 +1053,7 @@ __device__ void consumer_main(Ctx c) {
                 ok = false;
                 break;
         }
+        if (threadIdx.x == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_CONSUMER_DONE);
         if (!ok) break;  // `ok` is uniform over the 512 consumer threads
     }
 }
@@ -933,18 +1062,22 @@ __device__ void consumer_main(Ctx c) {
 // storer
 // --------------------------------------------------------------------------- //
 struct StorerState {
-    uint32_t out = 0;
+    uint32_t oslot = 0, ophase = 0;
     bool dead = false;
-    int* pending_addr = nullptr;  // barrier counter with unsignalled arrivals
-    int pending = 0;
+    // barrier arrivals not yet signalled: entry k lives in lane k
+    int* my_addr = nullptr;
+    int my_count = 0;
+    int n_entries = 0;
 };
 
 // sum the per-warp partials of the next finished block; lane r < 16 gets row r
 __device__ __forceinline__ float storer_take_block(const Ctx& c, StorerState& ss, int lane,
                                                    int partials) {
-    const int oslot = ss.out % kOutSlots;
-    const uint32_t ophase = (ss.out / kOutSlots) & 1u;
-    if (!warp_mbar_wait(c, c.out_full_bar(oslot), ophase, ss.dead, lane)) ss.dead = true;
+    const int oslot = ss.oslot;
+    const uint32_t obar = c.out_full_bar(oslot);
+    if (!ss.dead && !mbar_try_wait(obar, ss.ophase)) {
+        if (!mbar_wait_slow(c, obar, ss.ophase, true)) ss.dead = true;
+    }
     // lane = row + 16 * half: each half sums every other partial
     const int row = lane & 15, half = lane >> 4;
     const uint32_t src = c.base + kSmemOut + (oslot * kOutSlotFloats + row * 16) * 4;
@@ -953,25 +1086,35 @@ __device__ __forceinline__ float storer_take_block(const Ctx& c, StorerState& ss
     v += __shfl_xor_sync(0xffffffffu, v, 16);
     __syncwarp();
     if (lane == 0) mbar_arrive(c.out_empty_bar(oslot));
-    ss.out++;
+    if (++ss.oslot == kOutSlots) {
+        ss.oslot = 0;
+        ss.ophase ^= 1u;
+    }
     return v;
 }
 
+// Publish every pending arrival with ONE warp-wide `red.release.gpu`: the
+// release orders all global writes this warp made before the __syncwarp, so a
+// whole instruction's signals cost a single fence.
 __device__ __forceinline__ void storer_flush(StorerState& ss, int lane) {
     __syncwarp();
-    if (ss.pending > 0 && lane == 0) {
-        __threadfence();
-        red_release_gpu_add(ss.pending_addr, ss.pending);
-    }
-    ss.pending = 0;
-    ss.pending_addr = nullptr;
+    if (lane < ss.n_entries && ss.my_count > 0) red_release_gpu_add(ss.my_addr, ss.my_count);
+    ss.my_count = 0;
+    ss.my_addr = nullptr;
+    ss.n_entries = 0;
 }
 __device__ __forceinline__ void storer_signal(StorerState& ss, int lane, int* addr, int count) {
-    if (ss.pending_addr != addr) {
-        storer_flush(ss, lane);
-        ss.pending_addr = addr;
+    const unsigned hit = __ballot_sync(0xffffffffu, lane < ss.n_entries && ss.my_addr == addr);
+    if (hit) {
+        if (lane == __ffs(hit) - 1) ss.my_count += count;
+        return;
     }
-    ss.pending += count;
+    if (ss.n_entries == 32) storer_flush(ss, lane);
+    if (lane == ss.n_entries) {
+        ss.my_addr = addr;
+        ss.my_count = count;
+    }
+    ss.n_entries++;
 }
 
 __device__ void storer_main(Ctx c) {
@@ -990,9 +1133,9 @@ __device__ void storer_main(Ctx c) {
         const int op = __ldg(w);
         c.instr = i;
         c.opcode = op;
-        int stop = 0;
-        if (lane == 0) stop = (*c.cta_abort != 0) || ss.dead;
-        if (__shfl_sync(0xffffffffu, stop, 0)) break;
+        const int stop = (*c.cta_abort != 0) || ss.dead;
+        if (__any_sync(0xffffffffu, stop)) break;
+        if (lane == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_STORER_START);
         switch (op) {
             case MKB_OP_RMS_QKV_ROPE_APPEND: {
                 const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
@@ -1061,6 +1204,7 @@ __device__ void storer_main(Ctx c) {
             default:
                 break;
         }
+        if (lane == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_STORER_DONE);
     }
 }
 

@@ -20,6 +20,7 @@ LIB_PATH = _HERE / "libmkb200.so"
 
 MKB_ABI_VERSION = 1
 MKB_STATUS_WORDS = 16
+MKB_FLAG_RECORD_TIMINGS = 1
 
 ERROR_NAMES = {
     0: "MKB_OK",
@@ -77,6 +78,7 @@ class MkbGlobals(ctypes.Structure):
         ("attn_scale", ctypes.c_float),
         ("rms_norm_eps", ctypes.c_float),
         ("skip_attn_reduction", ctypes.c_int32),
+        ("flags", ctypes.c_uint32),
         ("wait_timeout_ms", ctypes.c_uint32),
         ("status", ctypes.c_void_p),
     ]
@@ -179,6 +181,7 @@ def pack_globals(
     matvec_reduction_size=None,
     wait_timeout_ms=0,
     status=None,
+    record_timings=False,
 ) -> MkbGlobals:
     """Fill the C struct from tensors; every dimension is read off the shapes."""
     bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
@@ -253,6 +256,9 @@ def pack_globals(
     g.attn_scale = float(attn_scale)
     g.rms_norm_eps = float(rms_norm_eps)
     g.skip_attn_reduction = int(bool(skip_attn_reduction))
+    g.flags = MKB_FLAG_RECORD_TIMINGS if record_timings else 0
+    if record_timings and timings is None:
+        raise ValueError("record_timings needs the timings tensor")
     g.wait_timeout_ms = int(wait_timeout_ms)
     g.status = _check_tensor("status", status, i32) if status is not None else None
     return g
@@ -266,7 +272,14 @@ def _stream_handle(stream) -> int:
     return int(stream.cuda_stream)
 
 
-def mk_llama(*args, stream=None, matvec_reduction_size=None, wait_timeout_ms=0, status=None):
+def mk_llama(
+    *args,
+    stream=None,
+    matvec_reduction_size=None,
+    wait_timeout_ms=0,
+    status=None,
+    record_timings=False,
+):
     """Enqueue one decode step; positional arguments as in the reference call.
 
     ``(barriers, instructions, timings, qkv_w, attn_ln_w, o_w, mlp_ln_w, up_w,
@@ -284,6 +297,7 @@ def mk_llama(*args, stream=None, matvec_reduction_size=None, wait_timeout_ms=0, 
         matvec_reduction_size=matvec_reduction_size,
         wait_timeout_ms=wait_timeout_ms,
         status=status,
+        record_timings=record_timings,
     )
     rc = lib.mkb_launch(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
     if rc != 0:
