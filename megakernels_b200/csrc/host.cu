@@ -64,6 +64,7 @@ struct DeviceState {
 int l2_window_from_env() {
     const char* e = getenv("MKB_L2_WINDOW_KB");
     int kb = e ? atoi(e) : 512;
+    if (kb == -1) return -12345;  // experiment: consumers skip the math
     if (kb < 0) kb = 0;
     if (kb > 4096) kb = 4096;
     return kb == 0 ? 0 : kNumStages + kb * 1024 / kStageBytes;

@@ -507,6 +507,7 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
         for (int st = 0; st < M::SPB; ++st) {
             const uint32_t sbase = consumer_wait_stage(c, cs) + thread_off;
             if (st == 0 && b == 0 && tid == 0) rec(c, MKB_T_CONSUMER_FIRST_STAGE);
+            if (c.p->l2_window_stages != -12345) {
 #pragma unroll
             for (int j = 0; j < M::RPT; ++j) {
 #pragma unroll
@@ -514,6 +515,7 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
                     const uint4 w = lds_v4(sbase + (uint32_t)(j * M::G) * (KC * 2) + cc * 512 * 16);
                     acc[st * M::RPT + j] = dot8(w, &act[cc * 8], acc[st * M::RPT + j]);
                 }
+            }
             }
             consumer_release_stage(c, cs, lane);
         }
@@ -739,6 +741,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         for (int i = 0; i < DPL; ++i) q[h][i] *= p.attn_scale_log2e;
     }
 
+    if (tid == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     // the token being decoded: its K/V were appended by another SM in this launch,
     // so warp 0 reads them straight from global memory (issued now, used last)
     float k_cur[DPL], v_cur[1][DPL];
@@ -790,8 +793,10 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
             }
             attn_fold<GQA, DPL, NPW>(acc, s_all, vv);
         }
-        consumer_release_stage(c, cs, lane);
+        // the last KV stage stays ours: its 32 KiB become the merge scratch below
+        if (s + 1 < r.n_stages) consumer_release_stage(c, cs, lane);
     }
+    if (tid == 0) rec(c, 5);
 
     if (warp == 0 && r.has_cur) {
         float s1[1][GQA];
@@ -807,70 +812,93 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         attn_fold<GQA, DPL, 1>(acc, s1, v_cur);
     }
 
-    // merge the 16 warps pairwise through shared memory, HP heads per pass
-    float* scratch = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemAttn));
+    if (r.n_stages == 0) {
+        // no cached positions in this slice: at most the current token, held by warp 0
+        if (warp == 0 && !cs.dead) {
 #pragma unroll
-    for (int pass = 0; pass < GQA / HP; ++pass) {
-        for (int half = kConsumerWarps / 2; half >= 1; half >>= 1) {
-            if (warp >= half && warp < 2 * half) {
-                float* slot = scratch + (warp - half) * kAttnSlotFloats;
-#pragma unroll
-                for (int hh = 0; hh < HP; ++hh) {
-                    const int h = pass * HP + hh;
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) slot[hh * 132 + lane * DPL + i] = acc.o[h][i];
-                    if (lane == 0) {
-                        slot[hh * 132 + 128] = acc.m[h];
-                        slot[hh * 132 + 129] = acc.l[h];
+            for (int h = 0; h < GQA; ++h) {
+                const int head = kvh * GQA + h;
+                const float inv = acc.l[h] > 0.f ? 1.f / acc.l[h] : 0.f;
+                if (p.skip_attn_reduction) {
+                    __nv_bfloat16* dst = p.attn_out + (size_t)head * D + lane * DPL;
+                    if constexpr (DPL == 4) {
+                        uint2 v;
+                        v.x = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
+                        v.y = pack_bf16x2(acc.o[h][2] * inv, acc.o[h][3] * inv);
+                        *reinterpret_cast<uint2*>(dst) = v;
+                    } else {
+                        *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
                     }
+                } else {
+                    float* dst = p.attn_o + ((size_t)head * p.max_partials + pi) * D + lane * DPL;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) dst[i] = acc.o[h][i] * inv;
+                    if (lane == 0)
+                        p.attn_lse[(size_t)head * p.max_partials + pi] =
+                            acc.l[h] > 0.f ? acc.m[h] + log2f(acc.l[h]) : -INFINITY;
                 }
             }
-            consumer_sync();
-            if (warp < half) {
-                const float* slot = scratch + warp * kAttnSlotFloats;
-#pragma unroll
-                for (int hh = 0; hh < HP; ++hh) {
-                    const int h = pass * HP + hh;
-                    const float m2 = slot[hh * 132 + 128], l2 = slot[hh * 132 + 129];
-                    const float mx = fmaxf(acc.m[h], m2);
-                    const float ms = (mx == -INFINITY) ? 0.f : mx;
-                    const float a1 = exp2f(acc.m[h] - ms), a2 = exp2f(m2 - ms);
-                    acc.m[h] = mx;
-                    acc.l[h] = acc.l[h] * a1 + l2 * a2;
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i)
-                        acc.o[h][i] = acc.o[h][i] * a1 + slot[hh * 132 + lane * DPL + i] * a2;
-                }
+            __syncwarp();
+            if (p.skip_attn_reduction) {
+                if (lane == 0)
+                    red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);
+            } else {
+                if (lane < GQA)
+                    red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, kvh * GQA + lane), 1);
             }
-            consumer_sync();
         }
+        return true;
     }
 
-    if (warp == 0 && !cs.dead) {
+    // One-round merge of the 16 warps: everybody parks (m, l, O) in shared memory -
+    // O in the KV stage we still own, [warp][head][D] - then thread (head, dim)
+    // combines the 16 entries of its output element.
+    float* so = reinterpret_cast<float*>(__cvta_shared_to_generic(c.stage_addr(cs.slot)));
+    float* sml = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemAttn));
 #pragma unroll
-        for (int h = 0; h < GQA; ++h) {
-            const int head = kvh * GQA + h;
-            const float inv = acc.l[h] > 0.f ? 1.f / acc.l[h] : 0.f;
-            if (p.skip_attn_reduction) {
-                __nv_bfloat16* dst = p.attn_out + (size_t)head * D + lane * DPL;
-                if constexpr (DPL == 4) {
-                    uint2 v;
-                    v.x = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
-                    v.y = pack_bf16x2(acc.o[h][2] * inv, acc.o[h][3] * inv);
-                    *reinterpret_cast<uint2*>(dst) = v;
-                } else {
-                    *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
-                }
-            } else {
-                float* dst = p.attn_o + ((size_t)head * p.max_partials + pi) * D + lane * DPL;
+    for (int pass = 0; pass < GQA / HP; ++pass) {
+        if (pass > 0) consumer_sync();
 #pragma unroll
-                for (int i = 0; i < DPL; ++i) dst[i] = acc.o[h][i] * inv;
-                if (lane == 0)
-                    p.attn_lse[(size_t)head * p.max_partials + pi] =
-                        acc.l[h] > 0.f ? acc.m[h] + log2f(acc.l[h]) : -INFINITY;
+        for (int hh = 0; hh < HP; ++hh) {
+            const int h = pass * HP + hh;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) so[(warp * HP + hh) * D + lane * DPL + i] = acc.o[h][i];
+            if (lane == 0) {
+                sml[(warp * HP + hh) * 2 + 0] = acc.m[h];
+                sml[(warp * HP + hh) * 2 + 1] = acc.l[h];
             }
         }
-        __syncwarp();
+        consumer_sync();
+        if (tid < HP * D) {  // whole warps: HP * D is a multiple of 32
+            const int hh = tid / D, d = tid % D;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w2 = 0; w2 < kConsumerWarps; ++w2) mx = fmaxf(mx, sml[(w2 * HP + hh) * 2]);
+            const float ms = (mx == -INFINITY) ? 0.f : mx;
+            float num = 0.f, den = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < kConsumerWarps; ++w2) {
+                const float a = exp2f(sml[(w2 * HP + hh) * 2] - ms);
+                den = fmaf(a, sml[(w2 * HP + hh) * 2 + 1], den);
+                num = fmaf(a, so[(w2 * HP + hh) * D + d], num);
+            }
+            const float val = den > 0.f ? num / den : 0.f;
+            const int head = kvh * GQA + pass * HP + hh;
+            if (p.skip_attn_reduction) {
+                const float hi = __shfl_down_sync(0xffffffffu, val, 1);
+                if ((d & 1) == 0 && !cs.dead)
+                    *reinterpret_cast<uint32_t*>(p.attn_out + (size_t)head * D + d) = pack_bf16x2(val, hi);
+            } else if (!cs.dead) {
+                p.attn_o[((size_t)head * p.max_partials + pi) * D + d] = val;
+                if (d == 0)
+                    p.attn_lse[(size_t)head * p.max_partials + pi] =
+                        den > 0.f ? mx + log2f(den) : -INFINITY;
+            }
+        }
+    }
+    consumer_sync();  // scratch reads and global stores of all threads are done
+    consumer_release_stage(c, cs, lane);
+    if (warp == 0 && !cs.dead) {
         if (p.skip_attn_reduction) {
             if (lane == 0)
                 red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);

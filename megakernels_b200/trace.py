@@ -56,6 +56,9 @@ def summarize(globs) -> dict:
                 d["stream"].append(us(T_CONSUMER_DONE) - us(T_FIRST_STAGE))
                 d["loader_lead"].append(us(T_CONSUMER_START) - us(T_LOADER_START))
                 d["storer_tail"].append(us(T_STORER_DONE) - us(T_CONSUMER_DONE))
+            elif op == 2:
+                d["stages"].append(us(5) - us(T_WAIT_DONE))
+                d["merge_store"].append(us(T_CONSUMER_DONE) - us(5))
             else:
                 d["work"].append(us(T_CONSUMER_DONE) - us(T_WAIT_DONE))
             key = (_layer_of(ins[sm, i]), op)
