@@ -58,7 +58,7 @@ def parse_args():
     ap.add_argument("--workload", default="llama-3.1-8b", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=0, help="override depth (profiling small cases)")
     ap.add_argument("--prefill", type=int, default=0)
-    ap.add_argument("--sched", default="wave")
+    ap.add_argument("--sched", default="rr")
     ap.add_argument("--attn-partitions", type=int, default=0, help="0 = pick from the length")
     ap.add_argument("--no-coalesce-o-proj", action="store_true")
     ap.add_argument("--barrier-fill", type=int, default=0,
@@ -254,7 +254,7 @@ def build_engine(args, device):
     for c in model.stacked_kv_cache:
         c[:, :, :prefill] = torch.randn(c[:, :, :prefill].shape, generator=gen, device=device).to(c.dtype)
     n_part = args.attn_partitions or pick_num_attention_partitions(
-        prefill, args.steps + args.warmup, device, model.num_kv_heads()
+        prefill, args.steps + args.warmup, device, model.num_kv_heads(), min_chunk_size=128
     )
     options = LatencyScheduleOptions(
         num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj

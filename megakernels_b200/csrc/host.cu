@@ -63,7 +63,7 @@ struct DeviceState {
 // L2 look-ahead of the loader in 32 KiB stages per SM; MKB_L2_WINDOW_KB overrides (0 disables).
 int l2_window_from_env() {
     const char* e = getenv("MKB_L2_WINDOW_KB");
-    int kb = e ? atoi(e) : 512;
+    int kb = e ? atoi(e) : 128;
     if (kb == -1) return -12345;  // experiment: consumers skip the math
     if (kb < 0) kb = 0;
     if (kb > 4096) kb = 4096;
@@ -114,10 +114,10 @@ int kv_tensor_map(DeviceState& ds, const void* ptr, int D, int Hkv, int T, int L
     return MKB_OK;
 }
 
-// 4-D view [256, K/256, rows, L] of a stacked weight [L, rows, K]; one box is one ring
-// stage of an R-column slice: {256, R/256, rows per stage, 1}.
-int weight_tensor_map(DeviceState& ds, const void* ptr, int K, int R, int rows, int L, CUtensorMap* out) {
-    KvMapKey key{ptr, -K, R, rows, L};
+// 4-D view [64, rows, K/64, L] of a stacked weight [L, rows, K] with the 128-byte swizzle;
+// one box is one ring stage of a `kc`-column slice: {64, 16 rows, min(kc, 1024)/64, 1}.
+int weight_tensor_map(DeviceState& ds, const void* ptr, int K, int kc, int rows, int L, CUtensorMap* out) {
+    KvMapKey key{ptr, -K, kc, rows, L};
     for (auto& e : ds.maps)
         if (e.key == key) {
             *out = e.map;
@@ -125,15 +125,15 @@ int weight_tensor_map(DeviceState& ds, const void* ptr, int K, int R, int rows, 
         }
     int rc = get_encode_fn();
     if (rc) return rc;
-    const int nr = stage_rows_for(R);
-    cuuint64_t dims[4] = {256, (cuuint64_t)K / 256, (cuuint64_t)rows, (cuuint64_t)L};
-    cuuint64_t strides[3] = {512, (cuuint64_t)K * 2, (cuuint64_t)rows * K * 2};
-    cuuint32_t box[4] = {256, (cuuint32_t)R / 256, (cuuint32_t)nr, 1};
+    const int cols = kc > 1024 ? 1024 : kc;
+    cuuint64_t dims[4] = {64, (cuuint64_t)rows, (cuuint64_t)K / 64, (cuuint64_t)L};
+    cuuint64_t strides[3] = {(cuuint64_t)K * 2, 128, (cuuint64_t)rows * K * 2};
+    cuuint32_t box[4] = {64, 16, (cuuint32_t)cols / 64, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUtensorMap m;
     CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims,
                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
@@ -305,18 +305,30 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     const unsigned ms = g->wait_timeout_ms ? g->wait_timeout_ms : 2000u;
     p.timeout_ns = (unsigned long long)ms * 1000000ull;
     p.l2_window_stages = g_l2_window_stages;
+    {
+        const char* e = getenv("MKB_POLL_SLEEP_NS");
+        p.poll_sleep_ns = e ? atoi(e) : 20;
+    }
 
     rc = kv_tensor_map(*ds, g->k_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.k_map);
     if (rc) return rc;
     rc = kv_tensor_map(*ds, g->v_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.v_map);
     if (rc) return rc;
 
-    if (p.o_in != p.R) {
-        rc = weight_tensor_map(*ds, g->o_proj_weights, p.o_in, p.R, p.H, p.L, &p.o_map);
-        if (rc) return rc;
-    }
-    if (p.I != p.R) {
-        rc = weight_tensor_map(*ds, g->down_proj_weights, p.I, p.R, p.H, p.L, &p.down_map);
+    const struct {
+        const void* ptr;
+        int K, kc, rows, L;
+        CUtensorMap* out;
+    } wmaps[] = {
+        {g->qkv_weights, p.H, p.H, p.qkv_rows, p.L, &p.qkv_map},
+        {g->o_proj_weights, p.o_in, p.R, p.H, p.L, &p.o_map},
+        {g->up_proj_weights, p.H, p.H, p.I, p.L, &p.up_map},
+        {g->gate_proj_weights, p.H, p.H, p.I, p.L, &p.gate_map},
+        {g->down_proj_weights, p.I, p.R, p.H, p.L, &p.down_map},
+        {g->lm_head_weights, p.H, p.H, p.V, 1, &p.lm_map},
+    };
+    for (const auto& wm : wmaps) {
+        rc = weight_tensor_map(*ds, wm.ptr, wm.K, wm.kc, wm.rows, wm.L, wm.out);
         if (rc) return rc;
     }
 

@@ -142,7 +142,7 @@ __device__ __noinline__ bool wait_counter(const Ctx& c, const int* addr, int thr
                 return false;
             }
         }
-        __nanosleep(20);
+        __nanosleep(c.p->poll_sleep_ns);
     }
 }
 
@@ -151,22 +151,15 @@ __device__ __forceinline__ int* bar_addr(const KParams& p, int layer, int row, i
 }
 
 // --------------------------------------------------------------------------- //
-// matvec geometry: how a 16-row x KC block is cut into ring stages and threads
+// matvec geometry
 // --------------------------------------------------------------------------- //
-template <int KC>
-struct MV {
-    static constexpr int CHUNKS = KC / 8;                      // 16-byte chunks per row
-    static constexpr int CPT = CHUNKS > 512 ? CHUNKS / 512 : 1;  // chunks per thread
-    static constexpr int TPR = CHUNKS / CPT;                   // threads covering one row
-    static constexpr int G = kConsumerThreads / TPR;           // row groups
-    static constexpr int NR = (kStageBytes / (KC * 2)) > 16 ? 16 : (kStageBytes / (KC * 2));
-    static constexpr int SPB = kBlockRows / NR;                // stages per block
-    static constexpr int RPT = NR / G;                         // rows per thread per stage
-    static constexpr int NACC = kBlockRows / G;                // accumulators per thread
-    static constexpr int WPG = TPR / 32;                       // warps per group = partials per row
-    static constexpr int STAGE_TX = NR * KC * 2;
-};
-
+// A 16-row x KC block of a weight matrix is streamed as KC/1024 ring stages of
+// 16 rows x 1024 columns (one stage of 16 x KC when KC < 1024).  A stage is one
+// tiled TMA copy with the 128-byte swizzle, laid out [64-column chunk][row][128 B];
+// consumer warp w multiplies column chunk w with four m16n8k16 tensor-core MMAs.
+constexpr int kStageCols = 1024;
+__host__ __device__ inline int stages_per_block(int kc) { return kc > kStageCols ? kc / kStageCols : 1; }
+__host__ __device__ inline int stage_cols(int kc) { return kc > kStageCols ? kStageCols : kc; }
 
 // Sum N per-lane values across the warp so that lane `l` ends with the total
 // of element `l / (32 / N)`; costs N shuffles instead of 5 * N.
@@ -218,16 +211,17 @@ __device__ __forceinline__ AttnRange attn_range(const KParams& p, int num_partia
     return r;
 }
 
-// One ring stage worth of work for the loader.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// One ring stage worth of work for the loader: a tiled TMA copy.
 struct StageDesc {
-    const __nv_bfloat16* src;  // contiguous weights: first row of the stage
-    int ld, kc, nr;            // row stride (elements), row length, rows in the stage
-    int kind;                  // kStageContig, kStageStrided or kStageAttn
-    const CUtensorMap* map;    // strided weights: 4-D view [256, K/256, rows, L]
-    int c1, c2, c3;            // ... and its coordinates (column chunk, row, layer)
-    int kvh, t, lb;            // K/V tile coordinates
+    const CUtensorMap* map;  // weights: 4-D view [64, rows, K/64, L]; nullptr for a K/V tile
+    int c1, c2, c3;          // weights: row, 64-column chunk, layer
+    uint32_t bytes;
+    int kvh, t, lb;          // K/V tile coordinates
 };
-enum { kStageContig = 0, kStageStrided = 1, kStageAttn = 2 };
 
 // Walks the instruction queue and yields its ring stages in consumption order.
 // The loader keeps two of these: one for the stages it copies into the ring and
@@ -236,21 +230,22 @@ struct StreamCursor {
     int i = -1;  // instruction index
     int op = 0;
     int b = 0, eb = 0;  // block (or KV stage) counter within the instruction
-    int r0 = 0;         // row offset inside the current 16-row block
+    int st = 0;         // stage inside the current block
     int sb = 0;         // first block index of a range instruction
-    const __nv_bfloat16* base = nullptr;
-    const __nv_bfloat16* base2 = nullptr;  // gate matrix of the up/gate op
     const int* w = nullptr;
-    int ld = 0, kc = 0, nr = 0;
+    const CUtensorMap* map = nullptr;
+    const CUtensorMap* map2 = nullptr;  // gate matrix of the up/gate op
+    int chunk0 = 0, layer = 0;          // first 64-column chunk of the slice, layer
+    int spb = 1;                        // stages per block
+    uint32_t bytes = 0;
     int kvh = 0, t0 = 0, lb = 0, ts = 0;
-    const CUtensorMap* map = nullptr;  // set for column-sliced matrices (o-proj, down-proj)
-    int map_c1 = 0, map_layer = 0;
 
-    __device__ __forceinline__ void set_matrix(const __nv_bfloat16* m, int ld_, int kc_) {
-        base = m;
-        ld = ld_;
-        kc = kc_;
-        nr = stage_rows_for(kc_);
+    __device__ __forceinline__ void set_matrix(const CUtensorMap* m, int kc, int chunk0_, int layer_) {
+        map = m;
+        spb = stages_per_block(kc);
+        bytes = (uint32_t)kBlockRows * stage_cols(kc) * 2u;
+        chunk0 = chunk0_;
+        layer = layer_;
     }
 
     // decode instruction `i`; leaves b == eb when it streams nothing
@@ -258,46 +253,36 @@ struct StreamCursor {
         w = queue + i * MKB_INTS_PER_INSTRUCTION;
         op = __ldg(w);
         b = eb = 0;
-        r0 = 0;
-        map = nullptr;
+        st = 0;
         switch (op) {
             case MKB_OP_RMS_QKV_ROPE_APPEND:
                 sb = __ldg(w + 2);
                 eb = __ldg(w + 3) - sb;
-                set_matrix(p.qkv_w + (size_t)__ldg(w + 1) * p.qkv_rows * p.H, p.H, p.H);
+                set_matrix(&p.qkv_map, p.H, 0, __ldg(w + 1));
+                // the consumers will want this layer's norm weights: have them in L2 by then
+                prefetch_l2_bulk(p.attn_ln_w + (size_t)__ldg(w + 1) * p.H, (uint32_t)p.H * 2u);
                 break;
             case MKB_OP_O_PROJ_RESIDUAL:
                 sb = __ldg(w + 2);
                 eb = __ldg(w + 3) - sb;
-                set_matrix(p.o_w + (size_t)__ldg(w + 1) * p.H * p.o_in + (size_t)__ldg(w + 4) * p.R,
-                           p.o_in, p.R);
-                if (p.o_in != p.R) {
-                    map = &p.o_map;
-                    map_c1 = __ldg(w + 4) * (p.R / 256);
-                    map_layer = __ldg(w + 1);
-                }
+                set_matrix(&p.o_map, p.R, __ldg(w + 4) * (p.R / 64), __ldg(w + 1));
                 break;
-            case MKB_OP_RMS_UPGATE_SILU: {
-                const size_t off = (size_t)__ldg(w + 1) * p.I * p.H;
+            case MKB_OP_RMS_UPGATE_SILU:
                 eb = 2 * __ldg(w + 2);
-                set_matrix(p.up_w + off, p.H, p.H);
-                base2 = p.gate_w + off;
-            } break;
+                set_matrix(&p.up_map, p.H, 0, __ldg(w + 1));
+                map2 = &p.gate_map;
+                prefetch_l2_bulk(p.mlp_ln_w + (size_t)__ldg(w + 1) * p.H, (uint32_t)p.H * 2u);
+                break;
             case MKB_OP_DOWN_PROJ_RESIDUAL:
                 sb = __ldg(w + 2);
                 eb = __ldg(w + 3) - sb;
-                set_matrix(p.down_w + (size_t)__ldg(w + 1) * p.H * p.I + (size_t)__ldg(w + 4) * p.R,
-                           p.I, p.R);
-                if (p.I != p.R) {
-                    map = &p.down_map;
-                    map_c1 = __ldg(w + 4) * (p.R / 256);
-                    map_layer = __ldg(w + 1);
-                }
+                set_matrix(&p.down_map, p.R, __ldg(w + 4) * (p.R / 64), __ldg(w + 1));
                 break;
             case MKB_OP_RMS_LM_HEAD:
                 sb = __ldg(w + 1);
                 eb = __ldg(w + 2) - sb;
-                set_matrix(p.lm_head_w, p.H, p.H);
+                set_matrix(&p.lm_map, p.H, 0, 0);
+                prefetch_l2_bulk(p.lm_norm_w, (uint32_t)p.H * 2u);
                 break;
             case MKB_OP_PARTIAL_ATTENTION: {
                 const AttnRange r = attn_range(p, __ldg(w + 3), __ldg(w + 4));
@@ -319,42 +304,35 @@ struct StreamCursor {
             decode(p, queue);
         }
         if (op == MKB_OP_PARTIAL_ATTENTION) {
-            d.kind = kStageAttn;
+            d.map = nullptr;
             d.kvh = kvh;
             d.t = t0 + b * ts;
             d.lb = lb;
+            d.bytes = kStageBytes;
             ++b;
             return true;
         }
         int blk;
-        const __nv_bfloat16* m = base;
+        const CUtensorMap* m = map;
         if (op == MKB_OP_RMS_UPGATE_SILU) {
             blk = __ldg(w + 3 + (b >> 1));
-            if (b & 1) m = base2;
+            if (b & 1) m = map2;
         } else {
             blk = sb + b;
         }
-        d.kind = map ? kStageStrided : kStageContig;
-        d.src = m + ((size_t)blk * kBlockRows + r0) * ld;
-        d.ld = ld;
-        d.kc = kc;
-        d.nr = nr;
-        d.map = map;
-        d.c1 = map_c1;
-        d.c2 = blk * kBlockRows + r0;
-        d.c3 = map_layer;
-        r0 += nr;
-        if (r0 >= kBlockRows) {
-            r0 = 0;
+        d.map = m;
+        d.c1 = blk * kBlockRows;
+        d.c2 = chunk0 + st * (kStageCols / 64);
+        d.c3 = layer;
+        d.bytes = bytes;
+        if (++st >= spb) {
+            st = 0;
             ++b;
         }
         return true;
     }
 };
 
-__device__ __forceinline__ void prefetch_l2_bulk(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void prefetch_l2_tile4(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map),
                  "r"(c0), "r"(c1), "r"(c2), "r"(c3)
@@ -399,10 +377,7 @@ __device__ void loader_main(Ctx c) {
                 ahead_more = ahead.next(p, queue, da);
                 if (ahead_more) {
                     ++ahead_stage;
-                    if (da.kind == kStageContig)
-                        prefetch_l2_bulk(da.src, (uint32_t)da.kc * 2u * da.nr);
-                    else if (da.kind == kStageStrided)
-                        prefetch_l2_tile4(da.map, 0, da.c1, da.c2, da.c3);
+                    if (da.map) prefetch_l2_tile4(da.map, 0, da.c1, da.c2, da.c3);
                 }
                 continue;
             }
@@ -410,17 +385,12 @@ __device__ void loader_main(Ctx c) {
         }
         const uint32_t bar = c.full_bar(slot);
         const uint32_t dst = c.stage_addr(slot);
-        if (d.kind == kStageAttn) {
-            mbar_expect_tx(bar, kStageBytes);
+        mbar_expect_tx(bar, d.bytes);
+        if (d.map == nullptr) {
             tma_tile4_g2s(dst, &p.k_map, 0, d.kvh, d.t, d.lb, bar, policy);
             tma_tile4_g2s(dst + kStageBytes / 2, &p.v_map, 0, d.kvh, d.t, d.lb, bar, policy);
         } else {
-            const uint32_t bytes = (uint32_t)d.kc * 2u * d.nr;
-            mbar_expect_tx(bar, bytes);
-            if (d.kind == kStageContig)
-                tma_bulk_g2s(dst, d.src, bytes, bar, policy);
-            else  // one tiled copy brings nr rows x kc columns of a column-sliced matrix
-                tma_tile4_g2s(dst, d.map, 0, d.c1, d.c2, d.c3, bar, policy);
+            tma_tile4_g2s(dst, d.map, 0, d.c1, d.c2, d.c3, bar, policy);
         }
         ++stage;
         have = issue.next(p, queue, d);
@@ -456,16 +426,14 @@ __device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
     f[6] = bf16_lo(w.w); f[7] = bf16_hi(w.w);
 }
 
-__device__ __forceinline__ float dot8(const uint4& w, const float* a, float acc) {
-    acc = fmaf(bf16_lo(w.x), a[0], acc);
-    acc = fmaf(bf16_hi(w.x), a[1], acc);
-    acc = fmaf(bf16_lo(w.y), a[2], acc);
-    acc = fmaf(bf16_hi(w.y), a[3], acc);
-    acc = fmaf(bf16_lo(w.z), a[4], acc);
-    acc = fmaf(bf16_hi(w.z), a[5], acc);
-    acc = fmaf(bf16_lo(w.w), a[6], acc);
-    acc = fmaf(bf16_hi(w.w), a[7], acc);
-    return acc;
+// D(16x8, fp32) += A(16x16, bf16, row-major) * B(16x8, bf16, column-major)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Wait for the ring stage at cs.slot.  Every lane performs the acquiring
@@ -486,51 +454,62 @@ __device__ __forceinline__ void consumer_release_stage(const Ctx& c, ConsumerSta
     }
 }
 
-// Multiply `nblocks` consecutive ring blocks (16 rows x KC) against the
-// activation registers and hand each block's per-warp partial sums to the storer.
-template <int KC>
-__device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, int nblocks,
-                                               const float (&act)[MV<KC>::CPT * 8]) {
-    using M = MV<KC>;
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int grp = tid / M::TPR;
-    const int col = tid % M::TPR;
-    const int wi = col >> 5;  // warp index inside its row group
+// Multiply `nblocks` consecutive ring blocks (16 rows x kc) against the bf16
+// activation vector parked in shared memory and hand each block's per-warp
+// partial sums to the storer.
+//
+// Tensor-core formulation of the matvec: weights are the A operand (16 rows x 16
+// k), the activation vector is column 0 of the B operand (the other 7 columns are
+// zero; a batch of up to 8 tokens would fill them).  The k order inside an MMA is
+// free as long as A and B agree, so thread (g = lane / 4, t = lane % 4) feeds the
+// MMAs straight from 16-byte chunks: chunk t (and t + 4) of weight rows pi(g),
+// pi(g) + 8 and the same chunk of the activations.  pi interleaves rows so that
+// the two rows of one shared-memory phase fall into different swizzle classes,
+// which makes the loads bank-conflict free.  After the last stage of a block the
+// lanes with t == 0 hold the 16 row sums of this warp's 64 columns per stage.
+__device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, int nblocks, int kc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = ((g & 1) << 2) | (g >> 1);  // pi(g): 0,4,1,5,2,6,3,7
+    const int spb = stages_per_block(kc);
+    const bool has_cols = warp * 64 < stage_cols(kc);
+    // byte offsets of this thread's two chunks inside a stage, rows row0 and row0 + 8
+    const uint32_t line = (uint32_t)(warp * 16 + row0) * 128u;
+    const uint32_t off_a = line + (uint32_t)((t ^ row0) << 4);
+    const uint32_t off_b = line + (uint32_t)(((t + 4) ^ row0) << 4);
+    const uint32_t act0 = c.base + kSmemAttn + (uint32_t)(warp * 64 + t * 8) * 2u;
 
-    const uint32_t thread_off = (uint32_t)grp * (KC * 2) + (uint32_t)col * 16;
     for (int b = 0; b < nblocks; ++b) {
-        float acc[M::NACC];
-#pragma unroll
-        for (int i = 0; i < M::NACC; ++i) acc[i] = 0.f;
-#pragma unroll
-        for (int st = 0; st < M::SPB; ++st) {
-            const uint32_t sbase = consumer_wait_stage(c, cs) + thread_off;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int st = 0; st < spb; ++st) {
+            const uint32_t sbase = consumer_wait_stage(c, cs);
             if (st == 0 && b == 0 && tid == 0) rec(c, MKB_T_CONSUMER_FIRST_STAGE);
-            if (c.p->l2_window_stages != -12345) {
-#pragma unroll
-            for (int j = 0; j < M::RPT; ++j) {
-#pragma unroll
-                for (int cc = 0; cc < M::CPT; ++cc) {
-                    const uint4 w = lds_v4(sbase + (uint32_t)(j * M::G) * (KC * 2) + cc * 512 * 16);
-                    acc[st * M::RPT + j] = dot8(w, &act[cc * 8], acc[st * M::RPT + j]);
+            if (has_cols && c.p->l2_window_stages != -12345) {
+                const uint4 w0 = lds_v4(sbase + off_a);
+                const uint4 w1 = lds_v4(sbase + off_a + 8 * 128);
+                const uint4 w2 = lds_v4(sbase + off_b);
+                const uint4 w3 = lds_v4(sbase + off_b + 8 * 128);
+                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+                if (g == 0) {
+                    x0 = lds_v4(act0 + (uint32_t)st * (kStageCols * 2));
+                    x1 = lds_v4(act0 + (uint32_t)st * (kStageCols * 2) + 64);
                 }
-            }
+                mma_16816(d, w0.x, w1.x, w0.y, w1.y, x0.x, x0.y);
+                mma_16816(d, w0.z, w1.z, w0.w, w1.w, x0.z, x0.w);
+                mma_16816(d, w2.x, w3.x, w2.y, w3.y, x1.x, x1.y);
+                mma_16816(d, w2.z, w3.z, w2.w, w3.w, x1.z, x1.w);
             }
             consumer_release_stage(c, cs, lane);
         }
-        // acc[i] belongs to block row grp + i * G
-        const float total = warp_transpose_reduce<M::NACC>(acc, lane);
         const uint32_t obar = c.out_empty_bar(cs.oslot);
         if (!cs.dead && !mbar_try_wait(obar, cs.ophase ^ 1u)) {
             if (!mbar_wait_slow(c, obar, cs.ophase ^ 1u, true)) cs.dead = true;
         }
-        constexpr int LPE = 32 / M::NACC;  // lanes holding the same element
-        if ((lane % LPE) == 0) {
-            const int row = grp + (lane / LPE) * M::G;
+        if (t == 0) {  // column 0 of D: rows row0 (d[0]) and row0 + 8 (d[2])
             float* out = reinterpret_cast<float*>(__cvta_shared_to_generic(
-                c.base + kSmemOut + (cs.oslot * kOutSlotFloats + row * 16 + wi) * 4));
-            *out = total;
+                c.base + kSmemOut + (cs.oslot * kOutSlotFloats + row0 * 16 + warp) * 4));
+            out[0] = d[0];
+            out[8 * 16] = d[2];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(c.out_full_bar(cs.oslot));
@@ -541,58 +520,94 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
     }
 }
 
-// Load this thread's slice of a bf16 activation vector (fp32 registers).
-template <int KC>
-__device__ __forceinline__ void load_activation(const __nv_bfloat16* vec,
-                                                float (&act)[MV<KC>::CPT * 8]) {
-    using M = MV<KC>;
-    const int col = threadIdx.x % M::TPR;
-#pragma unroll
-    for (int cc = 0; cc < M::CPT; ++cc) {
-        const uint4 v = ld_cg_v4(vec + (size_t)(col + cc * 512) * 8);
-        float f[8];
-        unpack8(v, f);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) act[cc * 8 + k] = f[k];
-    }
+// Activation chunks (8 bf16 = 16 bytes) are parked in shared memory at
+// act[chunk]; warp w only ever reads chunks {st * 128 + w * 8 + j}, so each warp
+// loads, normalises and writes exactly its own chunks and a __syncwarp suffices.
+// Lane l of warp w owns chunk (st, j) = (l / 8 + 4 * k, l % 8) for k = 0, 1.
+__device__ __forceinline__ int own_chunk(int warp, int lane, int k, int kc) {
+    const int st = (lane >> 3) + 4 * k;
+    const int col_chunk = warp * 8 + (lane & 7);  // within the stage
+    if (st >= stages_per_block(kc) || col_chunk * 8 >= stage_cols(kc)) return -1;
+    return st * (kStageCols / 8) + col_chunk;
 }
 
-// RMSNorm of the hidden state into registers.  Mirrors the reference's
-// arithmetic: fp32 statistics, bf16 round of x * rstd, then times the bf16
-// weight, rounded to bf16 (python_vm.py:50-56).
-template <int KC>
-__device__ __forceinline__ void rms_activation(const Ctx& c, const __nv_bfloat16* norm_w,
-                                               float (&act)[MV<KC>::CPT * 8]) {
-    using M = MV<KC>;
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c2, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c2), "r"(d) : "memory");
+}
+
+// Park a bf16 activation vector of `kc` elements in shared memory.
+__device__ __forceinline__ void stage_activation(const Ctx& c, const __nv_bfloat16* vec, int kc) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int ch = own_chunk(warp, lane, k, kc);
+        if (ch >= 0) {
+            const uint4 v = ld_cg_v4(vec + (size_t)ch * 8);
+            st_shared_v4(c.base + kSmemAttn + ch * 16, v.x, v.y, v.z, v.w);
+        }
+    }
+    __syncwarp();
+}
+
+// RMSNorm of the hidden state into shared memory (bf16).  Mirrors the
+// reference's arithmetic: fp32 statistics, bf16 round of x * rstd, then times
+// the bf16 weight, rounded to bf16 (python_vm.py:50-56).
+struct RmsPrefetch {
+    uint4 wv[2];
+    int chs[2];
+};
+// The norm weights do not depend on the barrier: fetch them before waiting.
+__device__ __forceinline__ void rms_prefetch(const Ctx& c, const __nv_bfloat16* norm_w, RmsPrefetch& pf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        pf.chs[k] = own_chunk(warp, lane, k, c.p->H);
+        if (pf.chs[k] >= 0) pf.wv[k] = ld_nc_v4(norm_w + (size_t)pf.chs[k] * 8);
+    }
+}
+__device__ __forceinline__ void rms_activation(const Ctx& c, const RmsPrefetch& pf) {
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int col = tid % M::TPR;
-    float wgt[M::CPT * 8];
-#pragma unroll
-    for (int cc = 0; cc < M::CPT; ++cc) {
-        const uint4 v = ld_nc_v4(norm_w + (size_t)(col + cc * 512) * 8);
-        float f[8];
-        unpack8(v, f);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) wgt[cc * 8 + k] = f[k];
-    }
-    load_activation<KC>(p.hidden, act);
+    uint4 xv[2];
     float ss = 0.f;
-    if (tid < M::TPR) {
 #pragma unroll
-        for (int k = 0; k < M::CPT * 8; ++k) ss = fmaf(act[k], act[k], ss);
+    for (int k = 0; k < 2; ++k)
+        if (pf.chs[k] >= 0) xv[k] = ld_cg_v4(p.hidden + (size_t)pf.chs[k] * 8);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        if (pf.chs[k] >= 0) {
+            float x[8];
+            unpack8(xv[k], x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+        }
     }
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     float* red = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemRed));
     if (lane == 0) red[warp] = ss;
+    if (tid == 0) rec(c, 6);
     consumer_sync();
+    if (tid == 0) rec(c, 7);
     float tot = 0.f;
 #pragma unroll
     for (int k = 0; k < kConsumerWarps; ++k) tot += red[k];
-    const float rstd = rsqrtf(tot / (float)KC + p.rms_eps);
+    const float rstd = rsqrtf(tot / (float)p.H + p.rms_eps);
 #pragma unroll
-    for (int k = 0; k < M::CPT * 8; ++k) act[k] = bf16_round(wgt[k] * bf16_round(act[k] * rstd));
+    for (int k = 0; k < 2; ++k) {
+        if (pf.chs[k] >= 0) {
+            float x[8], wgt[8];
+            unpack8(xv[k], x);
+            unpack8(pf.wv[k], wgt);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                o[e] = pack_bf16x2(wgt[2 * e] * bf16_round(x[2 * e] * rstd),
+                                   wgt[2 * e + 1] * bf16_round(x[2 * e + 1] * rstd));
+            st_shared_v4(c.base + kSmemAttn + pf.chs[k] * 16, o[0], o[1], o[2], o[3]);
+        }
+    }
+    __syncwarp();
 }
 
 // Consumer thread 0 waits for a counter; the verdict reaches all 512 consumer
@@ -611,29 +626,27 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     return *verdict != 0;
 }
 
-template <int KC>
 __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
                                                     const __nv_bfloat16* norm_w, int nblocks,
                                                     int wait_layer, int wait_row, int threshold,
                                                     bool needed) {
+    RmsPrefetch pf;
+    rms_prefetch(c, norm_w, pf);
     if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
-    float act[MV<KC>::CPT * 8];
-    rms_activation<KC>(c, norm_w, act);
+    rms_activation(c, pf);
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
-    consume_blocks<KC>(c, cs, nblocks, act);
+    consume_blocks(c, cs, nblocks, c.p->H);
     return true;
 }
 
-template <int KC>
 __device__ __forceinline__ bool consumer_plain_matvec(const Ctx& c, ConsumerState& cs,
                                                       const __nv_bfloat16* vec, int nblocks,
                                                       int wait_layer, int wait_row, int wait_slot,
                                                       int threshold) {
     if (!consumers_wait_counter(c, cs, wait_layer, wait_row, wait_slot, threshold, true)) return false;
-    float act[MV<KC>::CPT * 8];
-    load_activation<KC>(vec, act);
+    stage_activation(c, vec, c.p->R);
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
-    consume_blocks<KC>(c, cs, nblocks, act);
+    consume_blocks(c, cs, nblocks, c.p->R);
     return true;
 }
 
@@ -857,7 +870,9 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
     float* sml = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemAttn));
 #pragma unroll
     for (int pass = 0; pass < GQA / HP; ++pass) {
-        if (pass > 0) consumer_sync();
+        // pass 0: every warp must be done reading K/V from the stage before anyone
+        // overwrites it; later passes: the previous pass's readers must be done
+        consumer_sync();
 #pragma unroll
         for (int hh = 0; hh < HP; ++hh) {
             const int h = pass * HP + hh;
@@ -1004,38 +1019,35 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
 // --------------------------------------------------------------------------- //
 // consumer dispatch
 // --------------------------------------------------------------------------- //
-template <int KH>
 __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
     const KParams& p = *c.p;
     switch (op) {
         case MKB_OP_RMS_QKV_ROPE_APPEND: {
             const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
-            return consumer_rms_matvec<KH>(c, cs, p.attn_ln_w + (size_t)layer * p.H, eb - sb,
-                                           layer - 1, MKB_OP_DOWN_PROJ_RESIDUAL - 1,
-                                           p.thr_qkv_waits_down, layer > 0);
+            return consumer_rms_matvec(c, cs, p.attn_ln_w + (size_t)layer * p.H, eb - sb, layer - 1,
+                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, layer > 0);
         }
         case MKB_OP_RMS_UPGATE_SILU: {
             const int layer = __ldg(w + 1), n = __ldg(w + 2);
-            return consumer_rms_matvec<KH>(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
-                                           MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true);
+            return consumer_rms_matvec(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
+                                       MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true);
         }
         default: {  // MKB_OP_RMS_LM_HEAD
             const int sb = __ldg(w + 1), eb = __ldg(w + 2);
-            return consumer_rms_matvec<KH>(c, cs, p.lm_norm_w, eb - sb, p.L - 1,
-                                           MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true);
+            return consumer_rms_matvec(c, cs, p.lm_norm_w, eb - sb, p.L - 1,
+                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true);
         }
     }
 }
 
-template <int KR>
 __device__ bool consumer_residual_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
     const KParams& p = *c.p;
     const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3), rb = __ldg(w + 4);
     if (op == MKB_OP_O_PROJ_RESIDUAL)
-        return consumer_plain_matvec<KR>(c, cs, p.attn_out + (size_t)rb * p.R, eb - sb, layer,
-                                         MKB_OP_ATTENTION_REDUCTION - 1, 0, p.thr_oproj_waits_attn);
-    return consumer_plain_matvec<KR>(c, cs, p.silu_out + (size_t)rb * p.R, eb - sb, layer,
-                                     MKB_OP_RMS_UPGATE_SILU - 1, rb, p.thr_down_waits_upgate);
+        return consumer_plain_matvec(c, cs, p.attn_out + (size_t)rb * p.R, eb - sb, layer,
+                                     MKB_OP_ATTENTION_REDUCTION - 1, 0, p.thr_oproj_waits_attn);
+    return consumer_plain_matvec(c, cs, p.silu_out + (size_t)rb * p.R, eb - sb, layer,
+                                 MKB_OP_RMS_UPGATE_SILU - 1, rb, p.thr_down_waits_upgate);
 }
 
 __device__ void consumer_main(Ctx c) {
@@ -1056,15 +1068,11 @@ __device__ void consumer_main(Ctx c) {
             case MKB_OP_RMS_QKV_ROPE_APPEND:
             case MKB_OP_RMS_UPGATE_SILU:
             case MKB_OP_RMS_LM_HEAD:
-                if (p.H == 2048) ok = consumer_rms_op<2048>(c, cs, op, w);
-                else if (p.H == 4096) ok = consumer_rms_op<4096>(c, cs, op, w);
-                else ok = consumer_rms_op<8192>(c, cs, op, w);
+                ok = consumer_rms_op(c, cs, op, w);
                 break;
             case MKB_OP_O_PROJ_RESIDUAL:
             case MKB_OP_DOWN_PROJ_RESIDUAL:
-                if (p.R == 2048) ok = consumer_residual_op<2048>(c, cs, op, w);
-                else if (p.R == 1024) ok = consumer_residual_op<1024>(c, cs, op, w);
-                else ok = consumer_residual_op<512>(c, cs, op, w);
+                ok = consumer_residual_op(c, cs, op, w);
                 break;
             case MKB_OP_PARTIAL_ATTENTION: {
                 const int gqa = p.Hq / p.Hkv;
@@ -1152,8 +1160,7 @@ __device__ void storer_main(Ctx c) {
     const int row = lane & 15;
     const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
     c.role = kRoleStorer;
-    const int kh_partials = partials_per_row_for(p.H);
-    const int kr_partials = partials_per_row_for(p.R);
+    const int kh_partials = kConsumerWarps, kr_partials = kConsumerWarps;  // one partial per warp
     const int k_start = p.Hq * p.D, v_start = (p.Hq + p.Hkv) * p.D;
 
     for (int i = 0; i < p.queue_len; ++i) {

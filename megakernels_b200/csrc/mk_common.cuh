@@ -52,16 +52,6 @@ constexpr int kSmemCtl = kSmemBars + kNumMbars * 8;            // 8 ints of cont
 constexpr int kSmemTotal = kSmemCtl + 8 * 4;
 constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack to align the base
 
-// rows of a 16-row block that fit one ring stage, and per-row partial sums, for row length kc
-__host__ __device__ inline int stage_rows_for(int kc) {
-    int nr = kStageBytes / (kc * 2);
-    return nr > 16 ? 16 : nr;
-}
-__host__ __device__ inline int partials_per_row_for(int kc) {
-    int chunks = kc / 8;
-    return (chunks > 512 ? 512 : chunks) / 32;
-}
-
 enum Role { kRoleLoader = 0, kRoleConsumer = 1, kRoleStorer = 2 };
 
 // status record layout (int32 words), mirrors MkbStatus; word 15 is the abort flag
@@ -98,12 +88,13 @@ struct KParams {
     int thr_upgate_waits_oproj; // (H/16) * (o_in/R)
     int thr_down_waits_upgate;  // R/16
     unsigned long long timeout_ns;
+    int poll_sleep_ns;     // back-off between polls of a barrier counter
     int l2_window_stages;  // how many ring stages the loader may prefetch into L2 ahead of the ring
     // TMA descriptors of the KV cache, 4-D [D, Hkv, T, L*B], box {D, 1, TS, 1}
     CUtensorMap k_map, v_map;
-    // column-sliced projections as 4-D [256, K/256, rows, L], box {256, R/256, rows per stage, 1}:
-    // one tiled copy then fetches a whole stage although its rows are not contiguous
-    CUtensorMap o_map, down_map;
+    // weight matrices as 4-D [64, rows, K/64, L] with the 128-byte swizzle; one box is a ring
+    // stage: 16 rows x up to 1024 columns, stored [64-column chunk][row][128 B]
+    CUtensorMap qkv_map, o_map, up_map, gate_map, down_map, lm_map;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------- //

@@ -52,6 +52,10 @@ def summarize(globs) -> dict:
             d["wait"].append(us(T_WAIT_DONE) - us(T_CONSUMER_START))
             if op in (1, 4, 5, 6, 7):
                 d["activation"].append(us(T_ACT_READY) - us(T_WAIT_DONE))
+                if op in (1, 5, 7):
+                    d["act:load"].append(us(6) - us(T_WAIT_DONE))
+                    d["act:sync"].append(us(7) - us(6))
+                    d["act:norm"].append(us(T_ACT_READY) - us(7))
                 d["first_stage"].append(us(T_FIRST_STAGE) - us(T_ACT_READY))
                 d["stream"].append(us(T_CONSUMER_DONE) - us(T_FIRST_STAGE))
                 d["loader_lead"].append(us(T_CONSUMER_START) - us(T_LOADER_START))
