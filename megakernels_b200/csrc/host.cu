@@ -64,7 +64,6 @@ struct DeviceState {
 int l2_window_from_env() {
     const char* e = getenv("MKB_L2_WINDOW_KB");
     int kb = e ? atoi(e) : 128;
-    if (kb == -1) return -12345;  // experiment: consumers skip the math
     if (kb < 0) kb = 0;
     if (kb > 4096) kb = 4096;
     return kb == 0 ? 0 : kNumStages + kb * 1024 / kStageBytes;
@@ -87,13 +86,14 @@ int get_encode_fn() {
 }
 
 // 4-D view [D, Hkv, T, L*B] of a KV cache; one box is TS positions of one head.
-int kv_tensor_map(DeviceState& ds, const void* ptr, int D, int Hkv, int T, int LB, CUtensorMap* out) {
+int kv_tensor_map(DeviceState* ds, const void* ptr, int D, int Hkv, int T, int LB, CUtensorMap* out) {
     KvMapKey key{ptr, D, Hkv, T, LB};
-    for (auto& e : ds.maps)
-        if (e.key == key) {
-            *out = e.map;
-            return MKB_OK;
-        }
+    if (ds)
+        for (auto& e : ds->maps)
+            if (e.key == key) {
+                *out = e.map;
+                return MKB_OK;
+            }
     int rc = get_encode_fn();
     if (rc) return rc;
     const int ts = (kStageBytes / 4) / D;
@@ -108,21 +108,24 @@ int kv_tensor_map(DeviceState& ds, const void* ptr, int D, int Hkv, int T, int L
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-    if (ds.maps.size() >= 64) ds.maps.erase(ds.maps.begin());
-    ds.maps.push_back({key, m});
+    if (ds) {
+        if (ds->maps.size() >= 64) ds->maps.erase(ds->maps.begin());
+        ds->maps.push_back({key, m});
+    }
     *out = m;
     return MKB_OK;
 }
 
 // 4-D view [64, rows, K/64, L] of a stacked weight [L, rows, K] with the 128-byte swizzle;
 // one box is one ring stage of a `kc`-column slice: {64, 16 rows, min(kc, 1024)/64, 1}.
-int weight_tensor_map(DeviceState& ds, const void* ptr, int K, int kc, int rows, int L, CUtensorMap* out) {
+int weight_tensor_map(DeviceState* ds, const void* ptr, int K, int kc, int rows, int L, CUtensorMap* out) {
     KvMapKey key{ptr, -K, kc, rows, L};
-    for (auto& e : ds.maps)
-        if (e.key == key) {
-            *out = e.map;
-            return MKB_OK;
-        }
+    if (ds)
+        for (auto& e : ds->maps)
+            if (e.key == key) {
+                *out = e.map;
+                return MKB_OK;
+            }
     int rc = get_encode_fn();
     if (rc) return rc;
     const int cols = kc > 1024 ? 1024 : kc;
@@ -137,8 +140,10 @@ int weight_tensor_map(DeviceState& ds, const void* ptr, int K, int kc, int rows,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
-    if (ds.maps.size() >= 64) ds.maps.erase(ds.maps.begin());
-    ds.maps.push_back({key, m});
+    if (ds) {
+        if (ds->maps.size() >= 64) ds->maps.erase(ds->maps.begin());
+        ds->maps.push_back({key, m});
+    }
     *out = m;
     return MKB_OK;
 }
@@ -233,30 +238,23 @@ int device_state(DeviceState** out) {
     return MKB_OK;
 }
 
-}  // namespace
-
-extern "C" {
-
-int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
+// Validate `g` and build the kernel parameters.  `ds` carries the descriptor cache; with
+// ds == nullptr the TMA descriptors are encoded afresh and no host memory is allocated.
+int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_count, KParams& p) {
     int rc = validate(g);
     if (rc) return rc;
-    std::lock_guard<std::mutex> lock(g_mutex);
-    DeviceState* ds = nullptr;
-    rc = device_state(&ds);
-    if (rc) return rc;
-    if (g->num_sms > ds->sm_count)
+    if (g->num_sms > sm_count)
         return fail(MKB_ERR_INVALID_ARGUMENT,
                     "%d instruction queues but the device has %d SMs: all CTAs must be co-resident",
-                    g->num_sms, ds->sm_count);
+                    g->num_sms, sm_count);
 
-    KParams p;
     memset(&p, 0, sizeof(p));
     p.barriers = g->barriers;
     p.instructions = g->instructions;
     p.timings = (g->flags & MKB_FLAG_RECORD_TIMINGS) ? g->timings : nullptr;
     if ((g->flags & MKB_FLAG_RECORD_TIMINGS) && !g->timings)
         return fail(MKB_ERR_INVALID_ARGUMENT, "MKB_FLAG_RECORD_TIMINGS needs a timings tensor");
-    p.status = g->status ? g->status : ds->status;
+    p.status = status;
     p.queue_len = g->queue_len;
     p.barrier_ops = g->barrier_ops;
     p.barrier_width = g->barrier_width;
@@ -305,14 +303,11 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     const unsigned ms = g->wait_timeout_ms ? g->wait_timeout_ms : 2000u;
     p.timeout_ns = (unsigned long long)ms * 1000000ull;
     p.l2_window_stages = g_l2_window_stages;
-    {
-        const char* e = getenv("MKB_POLL_SLEEP_NS");
-        p.poll_sleep_ns = e ? atoi(e) : 20;
-    }
+    p.poll_sleep_ns = 20;
 
-    rc = kv_tensor_map(*ds, g->k_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.k_map);
+    rc = kv_tensor_map(ds, g->k_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.k_map);
     if (rc) return rc;
-    rc = kv_tensor_map(*ds, g->v_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.v_map);
+    rc = kv_tensor_map(ds, g->v_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.v_map);
     if (rc) return rc;
 
     const struct {
@@ -328,14 +323,40 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
         {g->lm_head_weights, p.H, p.H, p.V, 1, &p.lm_map},
     };
     for (const auto& wm : wmaps) {
-        rc = weight_tensor_map(*ds, wm.ptr, wm.K, wm.kc, wm.rows, wm.L, wm.out);
+        rc = weight_tensor_map(ds, wm.ptr, wm.K, wm.kc, wm.rows, wm.L, wm.out);
         if (rc) return rc;
     }
 
+    return MKB_OK;
+}
+
+
+}  // namespace
+
+namespace mkb {
+// Shared with the other translation units of the library (not part of the C ABI).
+int prepare_launch_uncached(const MkbGlobals* g, int* status, int sm_count, KParams& p) {
+    return prepare_launch(g, nullptr, status, sm_count, p);
+}
+int set_error(int code, const char* msg) { return fail(code, "%s", msg); }
+}  // namespace mkb
+
+extern "C" {
+
+int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    KParams p;
+    rc = prepare_launch(g, ds, (g && g->status) ? g->status : ds->status, ds->sm_count, p);
+    if (rc) return rc;
     megakernel<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     MKB_CUDA(cudaGetLastError());
     return MKB_OK;
 }
+
+
 
 int mkb_sync_status(const MkbGlobals* g, void* cuda_stream, MkbStatus* out) {
     if (!out) return fail(MKB_ERR_INVALID_ARGUMENT, "status output pointer is NULL");

@@ -484,7 +484,7 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
         for (int st = 0; st < spb; ++st) {
             const uint32_t sbase = consumer_wait_stage(c, cs);
             if (st == 0 && b == 0 && tid == 0) rec(c, MKB_T_CONSUMER_FIRST_STAGE);
-            if (has_cols && c.p->l2_window_stages != -12345) {
+            if (has_cols) {
                 const uint4 w0 = lds_v4(sbase + off_a);
                 const uint4 w1 = lds_v4(sbase + off_a + 8 * 128);
                 const uint4 w2 = lds_v4(sbase + off_b);

@@ -1,0 +1,66 @@
+"""The C-ABI library loads and exports every symbol `include/mkb200.h` declares (no GPU needed)."""
+
+import ctypes
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_functions():
+    text = (ROOT / "include" / "mkb200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mkb_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for must in ("mkb_launch", "mkb_sync_status", "mkb_validate_instructions", "mkb_last_error",
+                 "mkb_sm_count", "mkb_smem_bytes", "mkb_block_threads", "mkb_abi_version"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    import __graft_entry__ as entry
+
+    entry.build()
+    lib = ctypes.CDLL(str(ROOT / "megakernels_b200" / "native" / "libmkb200.so"))
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in mkb200.h but not exported"
+    lib.mkb_abi_version.restype = ctypes.c_int
+    assert lib.mkb_abi_version() == 1
+    lib.mkb_smem_bytes.restype = ctypes.c_int
+    assert 0 < lib.mkb_smem_bytes() <= 227 * 1024
+
+
+def test_struct_layout_matches_between_header_and_shim():
+    """Field names and order of MkbGlobals in the ctypes shim equal the header's."""
+    import sys
+
+    sys.path.insert(0, str(ROOT / "megakernels_b200" / "native"))
+    import mk_llama
+
+    text = (ROOT / "include" / "mkb200.h").read_text()
+    body = text[text.index("typedef struct MkbGlobals {") : text.index("} MkbGlobals;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = re.findall(r"[\w\*]\s+\**(\w+);", body)
+    assert names == [f[0] for f in mk_llama.MkbGlobals._fields_]
+
+
+def test_host_validation_without_a_gpu():
+    """mkb_validate_instructions is pure host code: it must reject a bad schedule here."""
+    import sys
+
+    import torch
+
+    sys.path.insert(0, str(ROOT / "megakernels_b200" / "native"))
+    import mk_llama
+
+    lib = mk_llama.load_library()
+    g = mk_llama.MkbGlobals()
+    g.abi_version = 0
+    lib.mkb_validate_instructions.argtypes = [ctypes.POINTER(mk_llama.MkbGlobals), ctypes.c_void_p]
+    lib.mkb_validate_instructions.restype = ctypes.c_int
+    buf = torch.zeros(1, 1, 32, dtype=torch.int32)
+    rc = lib.mkb_validate_instructions(ctypes.byref(g), ctypes.c_void_p(buf.data_ptr()))
+    assert rc == 1 and b"ABI version" in lib.mkb_last_error()
