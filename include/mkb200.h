@@ -178,6 +178,33 @@ int mkb_sync_status(const MkbGlobals *g, void *cuda_stream, MkbStatus *out);
  */
 int mkb_validate_instructions(const MkbGlobals *g, const int32_t *host_instructions);
 
+/*
+ * Same decode step as mkb_launch for callers that cannot allocate: no counterpart in
+ * the reference.  Some hosts of this kernel run where cudaMalloc is not an option
+ * (all device memory already handed to their own pool, a memory plan fixed before
+ * the run, a latency-critical loop), yet mkb_launch allocates a status record on
+ * its first call per device and a host-side descriptor cache, and its caller must
+ * allocate the split-KV attention scratch.  This variant calls no cudaMalloc,
+ * cudaFree or other allocating routine, on the device or on the host: the status
+ * record and the attention scratch live in one static device array of
+ * MKB_NO_ALLOC_SCRATCH_BYTES that every GPU loading the library holds until exit.
+ *
+ *  - `g->attn_lse_intermediates` and `g->attn_out_intermediates` are ignored (may be
+ *    NULL); `g->num_attention_heads`, `g->max_partials` and `g->head_dim` size the
+ *    scratch: 256 + roundup256(Hq * max_partials * 4) + Hq * max_partials * D * 4
+ *    bytes must fit MKB_NO_ALLOC_SCRATCH_BYTES (e.g. Hq 64, 24 partials, D 128),
+ *    otherwise MKB_ERR_UNSUPPORTED is returned and nothing is launched;
+ *  - `g->status` may point at MKB_STATUS_WORDS int32 of caller memory, which
+ *    mkb_sync_status(g, ...) can then read back; with NULL the record is kept inside
+ *    the static array, cleared on every call, and is not readable through this ABI;
+ *  - the first call on each device looks up the array's device address and sets a
+ *    kernel attribute; make that first call outside any stream capture;
+ *  - every call shares the one array and it keeps the previous call's contents: two
+ *    calls whose kernels overlap on the GPU (different streams, no ordering) race.
+ */
+#define MKB_NO_ALLOC_SCRATCH_BYTES (1u << 20)
+int mkb_launch_no_alloc(const MkbGlobals *g, void *cuda_stream);
+
 /* Message of the last host-side error raised on the calling thread. */
 const char *mkb_last_error(void);
 

@@ -119,6 +119,8 @@ def load_library() -> ctypes.CDLL:
     lib = ctypes.CDLL(str(LIB_PATH))
     lib.mkb_launch.argtypes = [ctypes.POINTER(MkbGlobals), ctypes.c_void_p]
     lib.mkb_launch.restype = ctypes.c_int
+    lib.mkb_launch_no_alloc.argtypes = [ctypes.POINTER(MkbGlobals), ctypes.c_void_p]
+    lib.mkb_launch_no_alloc.restype = ctypes.c_int
     lib.mkb_sync_status.argtypes = [
         ctypes.POINTER(MkbGlobals),
         ctypes.c_void_p,
@@ -182,6 +184,8 @@ def pack_globals(
     wait_timeout_ms=0,
     status=None,
     record_timings=False,
+    num_attention_heads=None,
+    max_partials=None,
 ) -> MkbGlobals:
     """Fill the C struct from tensors; every dimension is read off the shapes."""
     bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
@@ -214,18 +218,27 @@ def pack_globals(
     g.hidden_states = _check_tensor("hidden_states", hidden_states, bf16)
     g.post_ln_rope_q = _check_tensor("post_ln_rope_q", post_ln_rope_q, bf16)
     g.attn_out = _check_tensor("attn_out", attn_out, bf16)
-    g.attn_lse_intermediates = _check_tensor(
-        "attn_lse_intermediates", attn_lse_intermediates, f32, 2
-    )
-    g.attn_out_intermediates = _check_tensor(
-        "attn_out_intermediates", attn_out_intermediates, f32, 3
-    )
+    if attn_lse_intermediates is None and attn_out_intermediates is None:
+        # only valid for mk_llama_no_alloc, which supplies its own scratch
+        if num_attention_heads is None or max_partials is None:
+            raise ValueError("without intermediates, num_attention_heads and max_partials are needed")
+        g.attn_lse_intermediates = None
+        g.attn_out_intermediates = None
+    else:
+        g.attn_lse_intermediates = _check_tensor(
+            "attn_lse_intermediates", attn_lse_intermediates, f32, 2
+        )
+        g.attn_out_intermediates = _check_tensor(
+            "attn_out_intermediates", attn_out_intermediates, f32, 3
+        )
+        num_attention_heads = attn_lse_intermediates.shape[0]
+        max_partials = attn_lse_intermediates.shape[1]
     g.silu_out = _check_tensor("silu_out", silu_out, bf16)
     g.logits = _check_tensor("logits", logits, bf16)
 
     L, qkv_rows, H = qkv_weights.shape
     LB, T, Hkv, D = k_cache.shape
-    Hq = attn_lse_intermediates.shape[0]
+    Hq = int(num_attention_heads)
     g.num_layers = L
     g.hidden_size = H
     g.intermediate_size = up_proj_weights.shape[1]
@@ -235,7 +248,7 @@ def pack_globals(
     g.vocab_size = lm_head_weights.shape[0]
     g.kv_max_len = T
     g.kv_batch = LB // L
-    g.max_partials = attn_lse_intermediates.shape[1]
+    g.max_partials = int(max_partials)
     if qkv_rows != (Hq + 2 * Hkv) * D:
         raise ValueError(
             f"qkv rows {qkv_rows} != (Hq + 2*Hkv)*D = {(Hq + 2 * Hkv) * D}"
@@ -314,3 +327,38 @@ def sync_status(g: MkbGlobals, stream=None) -> MkbStatus:
         msg = lib.mkb_last_error().decode()
         raise MegakernelError(rc, msg, st)
     return st
+
+
+def mk_llama_no_alloc(
+    *args,
+    stream=None,
+    matvec_reduction_size=None,
+    wait_timeout_ms=0,
+    status=None,
+    num_attention_heads=None,
+    max_partials=None,
+):
+    """One decode step through ``mkb_launch_no_alloc``: nothing is allocated by the call.
+
+    Same 27 positional arguments as :func:`mk_llama`; pass ``None`` for the two
+    attention intermediates together with ``num_attention_heads`` and
+    ``max_partials`` - the library keeps that scratch (and, unless ``status`` is
+    given, its error record) in a static device array, for callers whose device
+    memory is fully planned and who therefore cannot let a library call cudaMalloc.
+    The array is shared by all calls: do not overlap two of them on the GPU.
+    """
+    if len(args) != 27:
+        raise TypeError(f"mk_llama_no_alloc expects 27 positional arguments, got {len(args)}")
+    lib = load_library()
+    g = pack_globals(
+        *args,
+        matvec_reduction_size=matvec_reduction_size,
+        wait_timeout_ms=wait_timeout_ms,
+        status=status,
+        num_attention_heads=num_attention_heads,
+        max_partials=max_partials,
+    )
+    rc = lib.mkb_launch_no_alloc(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
+    if rc != 0:
+        raise MegakernelError(rc, lib.mkb_last_error().decode())
+    return g
