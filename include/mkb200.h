@@ -136,6 +136,13 @@ typedef struct MkbGlobals {
     float rms_norm_eps;
     int32_t skip_attn_reduction;
 
+    /* ---- extensions without a counterpart in the reference call ---- */
+    const int32_t *pos_id_device; /* if not NULL the position is read from this device word at
+                                     kernel start (lets one CUDA graph replay every token) */
+    float residual_scale;         /* o-proj / down-proj outputs are multiplied by this before the
+                                     residual add; 0 means 1.  Tensor-parallel ranks set it to the
+                                     TP degree and average their residual streams afterwards */
+
     /* ---- options ---- */
     uint32_t flags;           /* MKB_FLAG_* */
     uint32_t wait_timeout_ms; /* device-side wait budget; 0 selects the default (2000 ms) */

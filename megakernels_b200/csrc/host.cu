@@ -212,7 +212,7 @@ int validate(const MkbGlobals* g) {
         return fail(MKB_ERR_INVALID_ARGUMENT, "barriers tensor too small: ops %d width %d", g->barrier_ops, g->barrier_width);
     if (g->kv_batch < 1 || g->kv_max_len < 1)
         return fail(MKB_ERR_INVALID_ARGUMENT, "KV cache needs batch >= 1 and length >= 1");
-    if (g->pos_id < 0 || g->pos_id >= g->kv_max_len)
+    if (!g->pos_id_device && (g->pos_id < 0 || g->pos_id >= g->kv_max_len))
         return fail(MKB_ERR_INVALID_ARGUMENT, "pos_id %d outside the KV cache length %d", g->pos_id, g->kv_max_len);
     if (g->max_partials < 1) return fail(MKB_ERR_INVALID_ARGUMENT, "max_partials must be >= 1");
     return MKB_OK;
@@ -292,6 +292,8 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     p.qkv_rows = (p.Hq + 2 * p.Hkv) * p.D;
     p.o_in = p.Hq * p.D;
     p.pos_id = g->pos_id;
+    p.pos_id_ptr = g->pos_id_device;
+    p.residual_scale = g->residual_scale > 0.f ? g->residual_scale : 1.f;
     p.attn_scale_log2e = g->attn_scale * 1.4426950408889634f;
     p.rms_eps = g->rms_norm_eps;
     p.skip_attn_reduction = g->skip_attn_reduction;

@@ -25,6 +25,7 @@ struct Ctx {
     const KParams* p;
     uint32_t base;            // shared-window address of the aligned smem base
     volatile int* cta_abort;  // generic pointer to the CTA-wide abort word
+    int pos;                  // position of the token being decoded
     int instr;                // instruction index being executed (for reports)
     int opcode;
     int role;
@@ -194,8 +195,9 @@ struct AttnRange {
     int has_cur;    // the token being decoded falls into this partial
     int n_stages;
 };
-__device__ __forceinline__ AttnRange attn_range(const KParams& p, int num_partials, int partial_idx) {
-    const int seq_len = p.pos_id + 1;
+__device__ __forceinline__ AttnRange attn_range(const KParams& p, int pos, int num_partials,
+                                                int partial_idx) {
+    const int seq_len = pos + 1;
     const int total_blocks = (seq_len + 15) / 16;
     const int per = (total_blocks + num_partials - 1) / num_partials;
     const int b0 = partial_idx * per;
@@ -203,8 +205,8 @@ __device__ __forceinline__ AttnRange attn_range(const KParams& p, int num_partia
     AttnRange r;
     r.t0 = b0 * 16;
     const int t1 = min(b1 * 16, seq_len);
-    r.has_cur = (p.pos_id >= r.t0 && p.pos_id < t1) ? 1 : 0;
-    r.t_old_end = r.has_cur ? p.pos_id : t1;
+    r.has_cur = (pos >= r.t0 && pos < t1) ? 1 : 0;
+    r.t_old_end = r.has_cur ? pos : t1;
     const int n_old = max(0, r.t_old_end - r.t0);
     const int ts = (kStageBytes / 4) / p.D;  // positions per stage: K and V halves of 16 KiB
     r.n_stages = (n_old + ts - 1) / ts;
@@ -239,6 +241,7 @@ struct StreamCursor {
     int spb = 1;                        // stages per block
     uint32_t bytes = 0;
     int kvh = 0, t0 = 0, lb = 0, ts = 0;
+    int pos = 0;  // position of the token being decoded
 
     __device__ __forceinline__ void set_matrix(const CUtensorMap* m, int kc, int chunk0_, int layer_) {
         map = m;
@@ -285,7 +288,7 @@ struct StreamCursor {
                 prefetch_l2_bulk(p.lm_norm_w, (uint32_t)p.H * 2u);
                 break;
             case MKB_OP_PARTIAL_ATTENTION: {
-                const AttnRange r = attn_range(p, __ldg(w + 3), __ldg(w + 4));
+                const AttnRange r = attn_range(p, pos, __ldg(w + 3), __ldg(w + 4));
                 kvh = __ldg(w + 2);
                 lb = __ldg(w + 1) * p.B;
                 t0 = r.t0;
@@ -346,6 +349,7 @@ __device__ void loader_main(Ctx c) {
     c.role = kRoleLoader;
 
     StreamCursor issue, ahead;  // `ahead` is never behind `issue`
+    issue.pos = ahead.pos = c.pos;
     StageDesc d, da;
     uint32_t stage = 0;       // stages copied into the ring so far
     uint32_t ahead_stage = 0; // stages the look-ahead cursor has passed
@@ -726,7 +730,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int layer = __ldg(w + 1), kvh = __ldg(w + 2), np = __ldg(w + 3), pi = __ldg(w + 4);
-    const AttnRange r = attn_range(p, np, pi);
+    const AttnRange r = attn_range(p, c.pos, np, pi);
 
     // barrier: the GQA query heads, then this KV head's K and V blocks
     {
@@ -761,7 +765,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
 #pragma unroll
     for (int i = 0; i < DPL; ++i) k_cur[i] = v_cur[0][i] = 0.f;
     if (warp == 0 && r.has_cur) {
-        const size_t off = (((size_t)layer * p.B) * p.T + p.pos_id) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
+        const size_t off = (((size_t)layer * p.B) * p.T + c.pos) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
         load_row_gmem<DPL>(p.k_cache + off, k_cur);
         load_row_gmem<DPL>(p.v_cache + off, v_cur[0]);
     }
@@ -1179,8 +1183,8 @@ __device__ void storer_main(Ctx c) {
                     const int start = b * kBlockRows;
                     if (start < v_start) {
                         const int seg = start % p.D;
-                        const float cs_ = __ldg(p.rope_cos + (size_t)p.pos_id * p.D + seg + row);
-                        const float sn = __ldg(p.rope_sin + (size_t)p.pos_id * p.D + seg + row);
+                        const float cs_ = __ldg(p.rope_cos + (size_t)c.pos * p.D + seg + row);
+                        const float sn = __ldg(p.rope_sin + (size_t)c.pos * p.D + seg + row);
                         const float other = __shfl_xor_sync(0xffffffffu, v, 1);
                         const float rot = (row & 1) ? other : -other;
                         v = v * cs_ + rot * sn;
@@ -1190,7 +1194,7 @@ __device__ void storer_main(Ctx c) {
                     if (start < k_start) {
                         dst = p.q_rope + start;
                     } else {
-                        const size_t tok = (((size_t)layer * p.B) * p.T + p.pos_id) * p.Hkv * p.D;
+                        const size_t tok = (((size_t)layer * p.B) * p.T + c.pos) * p.Hkv * p.D;
                         dst = (start < v_start) ? p.k_cache + tok + (start - k_start)
                                                 : p.v_cache + tok + (start - v_start);
                     }
@@ -1204,7 +1208,9 @@ __device__ void storer_main(Ctx c) {
             case MKB_OP_DOWN_PROJ_RESIDUAL: {
                 const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
                 for (int b = sb; b < eb; ++b) {
-                    const float v = storer_take_block(c, ss, lane, kr_partials);
+                    // residual_scale is the tensor-parallel degree: ranks then average their
+                    // copies of the residual stream, which yields h + sum of the partials
+                    const float v = storer_take_block(c, ss, lane, kr_partials) * p.residual_scale;
                     const float hi = __shfl_down_sync(0xffffffffu, v, 1);
                     if (lane < 16 && (lane & 1) == 0)
                         red_add_bf16x2(p.hidden + b * kBlockRows + row, pack_bf16x2(v, hi));
@@ -1259,6 +1265,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
     c.instr = -1;
     c.opcode = -1;
     c.role = -1;
+    c.pos = p.pos_id_ptr ? __ldg(p.pos_id_ptr) : p.pos_id;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kNumStages; ++s) {
@@ -1274,6 +1281,10 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    if (c.pos < 0 || c.pos >= p.T) {  // uniform over the grid: every thread read the same word
+        if (threadIdx.x == 0) report_error(c, MKB_ERR_INVALID_ARGUMENT, c.pos, p.T, 0, 0);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5;
     if (warp < kConsumerWarps) {

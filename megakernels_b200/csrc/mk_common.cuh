@@ -78,6 +78,8 @@ struct KParams {
     int o_in;      // Hq * D
     // per token
     int pos_id;
+    const int* pos_id_ptr;   // when set, the position is read from device memory instead
+    float residual_scale;    // factor on o-proj / down-proj outputs before the residual add
     float attn_scale_log2e;  // attn_scale * log2(e)
     float rms_eps;
     int skip_attn_reduction;

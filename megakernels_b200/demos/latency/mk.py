@@ -51,6 +51,8 @@ def interpret_with_mk(globs: Globals, mk_func, stream=None, **kwargs):
         globs.skip_attn_reduction,
         stream=stream if stream is not None else torch.cuda.current_stream(),
         matvec_reduction_size=globs.matvec_reduction_size,
+        residual_scale=globs.residual_scale,
+        pos_id_device=globs.pos_id_device,
         **kwargs,
     )
 

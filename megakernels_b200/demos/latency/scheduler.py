@@ -181,7 +181,8 @@ def _split_jobs_within_columns(num_col_splits: int, num_row_blocks: int, sm_coun
     done = 0
     for sm in range(sm_count):
         per = (len(jobs) - done) / (sm_count - sm)
-        assert per > 1
+        if per <= 1:
+            return None  # the reference asserts here; the caller falls back to exact runs
         take = jobs[done : done + round(per)]
         col = take[0][0]
         take = [j for j in take if j[0] == col]
@@ -197,7 +198,7 @@ def schedule_downproj(globs: Globals, layer_idx: int):
     runs = None
     if splits * n_blocks > globs.sm_count():
         runs = _split_jobs_within_columns(splits, n_blocks, globs.sm_count())
-        if sum(e - s for _, s, e in runs) != n_blocks * splits:
+        if runs is not None and sum(e - s for _, s, e in runs) != n_blocks * splits:
             runs = None  # the truncating walk stranded jobs (shapes far from 1B)
     if runs is None:
         runs = _exact_runs(splits, n_blocks, globs.sm_count())
@@ -372,3 +373,26 @@ class LatencyScheduleBuilder(ScheduleBuilder):
 
     def make_dag(self, globs, stop_after_op=None, layer_limit=None):  # type: ignore[override]
         return make_dag(globs, stop_after_op, layer_limit, self.options)
+
+
+def split_at_collectives(instructions: list[Instruction]) -> list[tuple[list[Instruction], bool]]:
+    """Cut a topologically ordered stream where tensor parallelism needs an all-reduce.
+
+    Row-split projections (o-proj, down-proj) leave every rank with a partial sum of
+    the residual stream, so the stream is cut after each layer's o-proj group and
+    after each down-proj group.  Returns ``[(segment, needs_all_reduce_after), ...]``;
+    barrier counters carry over from one segment to the next.
+    """
+    segments: list[tuple[list[Instruction], bool]] = []
+    cur: list[Instruction] = []
+    for ins in instructions:
+        if cur and cur[-1].opcode() in (O_ProjResidual.opcode(), DownProjResidual.opcode()) and (
+            ins.opcode() != cur[-1].opcode()
+        ):
+            segments.append((cur, True))
+            cur = []
+        cur.append(ins)
+    if cur:
+        last = cur[-1].opcode()
+        segments.append((cur, last in (O_ProjResidual.opcode(), DownProjResidual.opcode())))
+    return segments

@@ -135,3 +135,63 @@ class MK_Generator(Generator):
         import mk_llama  # the module get_mk_func imported
 
         return mk_llama.sync_status(self.last_call)
+
+
+class TP_MK_Generator(MK_Generator):
+    """Megatron-style tensor-parallel decoding, one rank per GPU.
+
+    The reference's kernel has no tensor parallelism; its torch model shards
+    q/k/v/up/gate by rows and o/down by columns (megakernels/llama.py:665-691).
+    Here every rank runs the megakernel on its shard (``model`` built with
+    ``ExtraModelConfig(tp_size, tp_rank)``).  The instruction stream is cut after
+    every o-proj and down-proj group; between two cuts the ranks all-reduce the
+    residual stream.  Each rank adds ``tp_size`` times its partial projection to
+    its full copy of the residual (``globs.residual_scale``), so that the
+    *average* over ranks equals ``h + sum of partials`` and no separate scaling
+    or zeroing kernel is needed.
+    """
+
+    def __init__(self, model, interpreter, schedule, group=None, sched: str = "rr", all_reduce=None):
+        from megakernels_b200.demos.latency.scheduler import split_at_collectives
+        from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+        super().__init__(model, interpreter, schedule)
+        self.group = group
+        self.tp_size = model.extra_config.tp_size
+        globs = schedule.globs
+        globs.residual_scale = float(self.tp_size)
+        self.segments = []
+        for instructions, needs_all_reduce in split_at_collectives(schedule.get_linear_instructions()):
+            queues = assign_to_sms(sched, instructions=instructions, sm_count=globs.sm_count())
+            tensorize_instructions(globs, queues)
+            self.segments.append((globs.instructions, globs.timings, needs_all_reduce))
+        self.all_reduce = all_reduce or self._nccl_average
+
+    def _nccl_average(self, tensor: Tensor):
+        import torch.distributed as dist
+
+        dist.all_reduce(tensor, op=dist.ReduceOp.AVG, group=self.group)
+
+    def begin_token(self, input_ids: Tensor, pos_id: int):
+        globs = self.schedule.globs
+        post = self.model.model.embed_tokens(BatchState(input_ids=input_ids))
+        globs.hidden_states[:] = post.hidden_states.reshape(-1)
+        self.fill()
+        globs.pos_id = pos_id
+
+    def launch_segment(self, k: int) -> bool:
+        """Enqueue segment ``k``; returns whether an all-reduce must follow it."""
+        globs = self.schedule.globs
+        globs.instructions, globs.timings, needs_all_reduce = self.segments[k]
+        self.last_call = self.interpreter.interpret(globs)
+        return needs_all_reduce
+
+    def finish_token(self) -> Tensor:
+        return torch.argmax(self.schedule.globs.logits, dim=-1)
+
+    def run(self, input_ids: Tensor, pos_id: int):
+        self.begin_token(input_ids, pos_id)
+        for k in range(len(self.segments)):
+            if self.launch_segment(k):
+                self.all_reduce(self.schedule.globs.hidden_states)
+        return self.finish_token()

@@ -56,6 +56,9 @@ class BaseGlobals:
     def __post_init__(self):
         self.instructions: Tensor | None = None
         self.timings: Tensor | None = None
+        # extensions without a counterpart in the reference globals
+        self.residual_scale: float = 1.0  # tensor-parallel degree (see generators.TP_MK_Generator)
+        self.pos_id_device: Tensor | None = None  # int32[1]; overrides pos_id when set
 
     def sm_count(self) -> int:
         return get_sm_count(self.device)

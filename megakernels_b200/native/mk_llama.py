@@ -78,6 +78,8 @@ class MkbGlobals(ctypes.Structure):
         ("attn_scale", ctypes.c_float),
         ("rms_norm_eps", ctypes.c_float),
         ("skip_attn_reduction", ctypes.c_int32),
+        ("pos_id_device", ctypes.c_void_p),
+        ("residual_scale", ctypes.c_float),
         ("flags", ctypes.c_uint32),
         ("wait_timeout_ms", ctypes.c_uint32),
         ("status", ctypes.c_void_p),
@@ -186,6 +188,8 @@ def pack_globals(
     record_timings=False,
     num_attention_heads=None,
     max_partials=None,
+    pos_id_device=None,
+    residual_scale=1.0,
 ) -> MkbGlobals:
     """Fill the C struct from tensors; every dimension is read off the shapes."""
     bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
@@ -255,7 +259,9 @@ def pack_globals(
         )
     if rope_cos.shape[1] != D or rope_sin.shape != rope_cos.shape:
         raise ValueError("rope tables must be [positions, head_dim]")
-    if rope_cos.shape[0] <= int(pos_id):
+    if pos_id_device is not None:
+        g.pos_id_device = _check_tensor("pos_id_device", pos_id_device, i32)
+    elif rope_cos.shape[0] <= int(pos_id):
         raise ValueError(f"rope tables have {rope_cos.shape[0]} rows, pos_id is {pos_id}")
     if matvec_reduction_size is None:
         for r in (2048, 1024, 512):
@@ -269,6 +275,7 @@ def pack_globals(
     g.attn_scale = float(attn_scale)
     g.rms_norm_eps = float(rms_norm_eps)
     g.skip_attn_reduction = int(bool(skip_attn_reduction))
+    g.residual_scale = float(residual_scale)
     g.flags = MKB_FLAG_RECORD_TIMINGS if record_timings else 0
     if record_timings and timings is None:
         raise ValueError("record_timings needs the timings tensor")
@@ -292,6 +299,8 @@ def mk_llama(
     wait_timeout_ms=0,
     status=None,
     record_timings=False,
+    pos_id_device=None,
+    residual_scale=1.0,
 ):
     """Enqueue one decode step; positional arguments as in the reference call.
 
@@ -311,6 +320,8 @@ def mk_llama(
         wait_timeout_ms=wait_timeout_ms,
         status=status,
         record_timings=record_timings,
+        pos_id_device=pos_id_device,
+        residual_scale=residual_scale,
     )
     rc = lib.mkb_launch(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
     if rc != 0:

@@ -1,0 +1,157 @@
+"""Tensor parallelism: stream splitting on CPU, gloo ranks on CPU, emulated ranks on one GPU."""
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from megakernels_b200.demos.latency.instructions import DownProjResidual, O_ProjResidual
+from megakernels_b200.demos.latency.scheduler import (
+    LatencyScheduleOptions,
+    split_at_collectives,
+)
+from megakernels_b200.llama import LlamaConfig
+from megakernels_b200.utils import set_sm_count_override
+from oracle.llama_ref import TorchReferenceModel, assert_logits_parity
+from oracle.python_vm import PyVM_Interpreter
+from tests.oracle_utils import build_model, build_schedule, fill_kv, seeded_tokens
+
+CFG = dict(
+    hidden_size=2048, intermediate_size=4096, num_hidden_layers=2, num_attention_heads=16,
+    num_key_value_heads=4, head_dim=128, vocab_size=4096, tie_word_embeddings=False,
+)
+PREFILL = 24
+
+
+def tp_model(rank, tp, device="cpu"):
+    model = build_model(LlamaConfig(**CFG), 64, device=device, tp_size=tp, tp_rank=rank)
+    # every rank holds its own KV heads of the same seeded cache
+    full = build_model(LlamaConfig(**CFG), 64, device="cpu")
+    fill_kv(full, PREFILL, poison=True)
+    per = CFG["num_key_value_heads"] // tp
+    for dst, src in zip(model.stacked_kv_cache, full.stacked_kv_cache):
+        dst.copy_(src[:, :, :, rank * per : (rank + 1) * per])
+    return model
+
+
+def reference_logits(tokens):
+    full = build_model(LlamaConfig(**CFG), 64, device="cpu")
+    fill_kv(full, PREFILL, poison=True)
+    ref = TorchReferenceModel(full)
+    ref.load_kv(*full.stacked_kv_cache)
+    return [ref.decode_token(t, PREFILL + i) for i, t in enumerate(tokens)]
+
+
+def test_stream_is_cut_after_every_row_split_projection():
+    set_sm_count_override(148)
+    model = build_model(LlamaConfig(**CFG), 64, tp_size=2, tp_rank=0)
+    sched = build_schedule(model, LatencyScheduleOptions(coalesce_o_proj=True))
+    segs = split_at_collectives(sched.get_linear_instructions())
+    assert len(segs) == 2 * CFG["num_hidden_layers"] + 1
+    assert [ar for _, ar in segs] == [True] * (2 * CFG["num_hidden_layers"]) + [False]
+    for (ins, ar), kind in zip(segs[:-1], [O_ProjResidual, DownProjResidual] * CFG["num_hidden_layers"]):
+        assert isinstance(ins[-1], kind)
+    assert sum(len(s) for s, _ in segs) == len(sched.get_linear_instructions())
+
+
+def _gloo_rank(rank, world, port, tokens, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    set_sm_count_override(148)
+    model = tp_model(rank, world)
+    sched = build_schedule(model, LatencyScheduleOptions(coalesce_o_proj=True))
+    g = sched.globs
+    g.residual_scale = float(world)
+    vm = PyVM_Interpreter()
+    embed = model.model.embed_tokens.embed_tokens.weight
+    logits = []
+    for i, tok in enumerate(tokens):
+        g.hidden_states[:] = embed[tok]
+        g.barriers.zero_()
+        g.pos_id = PREFILL + i
+        for ins, needs_all_reduce in split_at_collectives(sched.get_linear_instructions()):
+            vm.interpret(g, ins)
+            if needs_all_reduce:  # gloo has no AVG: sum in fp32, divide, round once
+                h = g.hidden_states.float()
+                dist.all_reduce(h)
+                g.hidden_states.copy_((h / world).to(g.hidden_states.dtype))
+        logits.append(g.logits.clone())
+    if rank == 0:
+        torch.save(logits, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_unsharded_model(tmp_path):
+    """The sharding + scaled-residual + averaging scheme, with the CPU oracle as the kernel."""
+    tokens = seeded_tokens(CFG["vocab_size"], 2)
+    out = tmp_path / "logits.pt"
+    mp.spawn(_gloo_rank, args=(2, 29517, tokens, str(out)), nprocs=2, join=True)
+    got = torch.load(out)
+    for a, b in zip(got, reference_logits(tokens)):
+        assert_logits_parity(a, b, "tp=2 on gloo")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tp", [2, 4])
+def test_emulated_ranks_on_one_gpu(tp):
+    """All ranks' megakernels run on one GPU, segment by segment; the all-reduce is a host loop."""
+    from megakernels_b200.dispatch import make_mk_interpreter
+    from megakernels_b200.generators import TP_MK_Generator
+
+    tokens = seeded_tokens(CFG["vocab_size"], 2)
+    gens = []
+    for rank in range(tp):
+        model = tp_model(rank, tp, device="cuda:0")
+        sched = build_schedule(model, LatencyScheduleOptions(coalesce_o_proj=True))
+        gens.append(TP_MK_Generator(model, make_mk_interpreter("latency"), sched, all_reduce=lambda t: None))
+    want = reference_logits(tokens)
+    for i, tok in enumerate(tokens):
+        ids = torch.tensor([[tok]], device="cuda:0")
+        for g in gens:
+            g.begin_token(ids, PREFILL + i)
+        for k in range(len(gens[0].segments)):
+            flags = [g.launch_segment(k) for g in gens]
+            if flags[0]:
+                mean = torch.stack([g.schedule.globs.hidden_states.float() for g in gens]).mean(0)
+                for g in gens:
+                    g.schedule.globs.hidden_states.copy_(mean.to(torch.bfloat16))
+        for g in gens:
+            g.check()
+            assert_logits_parity(g.schedule.globs.logits, want[i], f"tp={tp} step {i}")
+
+
+def _nccl_rank(rank, world, port, tokens, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from megakernels_b200.dispatch import make_mk_interpreter
+    from megakernels_b200.generators import TP_MK_Generator
+
+    set_sm_count_override(torch.cuda.get_device_properties(rank).multi_processor_count)
+    model = tp_model(rank, world, device=f"cuda:{rank}")
+    sched = build_schedule(model, LatencyScheduleOptions(coalesce_o_proj=True))
+    gen = TP_MK_Generator(model, make_mk_interpreter("latency"), sched)
+    logits = []
+    for i, tok in enumerate(tokens):
+        gen.run(torch.tensor([[tok]], device=f"cuda:{rank}"), PREFILL + i)
+        gen.check()
+        logits.append(sched.globs.logits.cpu())
+    if rank == 0:
+        torch.save(logits, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_nccl_ranks_on_real_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    tokens = seeded_tokens(CFG["vocab_size"], 2)
+    out = tmp_path / "logits.pt"
+    mp.spawn(_nccl_rank, args=(2, 29519, tokens, str(out)), nprocs=2, join=True)
+    for a, b in zip(torch.load(out), reference_logits(tokens)):
+        assert_logits_parity(a, b, "tp=2 on NCCL")
