@@ -46,8 +46,10 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used when MEASURE
 NCU_TRAFFIC_RATIO = (2.8390e9 + 0.0295e9) / 2.7955e9
 
 WORKLOADS = {
-    "llama-3.1-8b": dict(preset="llama_3_1_8b", prefill=1024),
-    "llama-3.2-1b": dict(preset="llama_3_2_1b", prefill=32),
+    # tp=False: every rank runs an independent replica; tp=True: the ranks shard one model
+    "llama-3.1-8b": dict(preset="llama_3_1_8b", prefill=1024, tp=False),
+    "llama-3.2-1b": dict(preset="llama_3_2_1b", prefill=32, tp=False),
+    "llama-3.1-70b": dict(preset="llama_3_1_70b", prefill=2048, tp=True),
 }
 
 
@@ -65,6 +67,8 @@ def parse_args():
     ap.add_argument("--no-coalesce-o-proj", action="store_true")
     ap.add_argument("--barrier-fill", type=int, default=0,
                     help="experiment: preset all barrier counters (waits pass at once; results are garbage)")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="replay one captured decode step per token instead of launching eagerly")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -80,14 +84,15 @@ def model_config(args):
     return cfg, prefill
 
 
-def algorithmic_bytes_per_token(cfg, seq_len: int) -> dict:
-    """Bytes one decoded token must move: every bf16 matrix once, norms, KV read + append."""
+def algorithmic_bytes_per_token(cfg, seq_len: int, tp: int = 1) -> dict:
+    """Bytes one GPU must move per decoded token: every bf16 matrix of its shard once
+    (layers split over ``tp`` ranks, LM head replicated), norms, KV read + append."""
     H, I, L, D = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers, cfg.head_dim
     Hq, Hkv, V = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.vocab_size
-    per_layer = ((Hq + 2 * Hkv) * D * H + H * Hq * D + 3 * I * H) * 2
+    per_layer = ((Hq + 2 * Hkv) * D * H + H * Hq * D + 3 * I * H) * 2 // tp
     weights = L * per_layer + V * H * 2
     norms = (2 * L + 1) * H * 2
-    kv_row = 2 * Hkv * D * 2 * L
+    kv_row = 2 * Hkv * D * 2 * L // tp
     return dict(weights=weights, norms=norms, kv=kv_row * seq_len + kv_row)
 
 
@@ -237,22 +242,24 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------- #
 # our arm
 # --------------------------------------------------------------------------- #
-def build_engine(args, device):
+def build_engine(args, device, tp_size=1, tp_rank=0, group=None):
     from megakernels_b200.demos.latency.scheduler import (
         LatencyScheduleOptions,
         pick_num_attention_partitions,
     )
     from megakernels_b200.dispatch import make_mk_interpreter, make_schedule_builder
-    from megakernels_b200.generators import MK_Generator
+    from megakernels_b200.generators import MK_Generator, TP_MK_Generator
     from megakernels_b200.llama import LlamaForCausalLM
     from megakernels_b200.model_types import ExtraModelConfig
     from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
 
     cfg, prefill = model_config(args)
     total = prefill + args.steps + args.warmup + 8
-    extra = ExtraModelConfig(interleave_rope=True, max_len_override=total)
+    extra = ExtraModelConfig(
+        interleave_rope=True, max_len_override=total, tp_size=tp_size, tp_rank=tp_rank, tp_group=group
+    )
     model = LlamaForCausalLM.from_random(cfg, extra, device=device, seed=0, draw_on="device")
-    gen = torch.Generator(device=device).manual_seed(2)
+    gen = torch.Generator(device=device).manual_seed(2 + tp_rank)
     for c in model.stacked_kv_cache:
         c[:, :, :prefill] = torch.randn(c[:, :, :prefill].shape, generator=gen, device=device).to(c.dtype)
     n_part = args.attn_partitions or pick_num_attention_partitions(
@@ -263,12 +270,16 @@ def build_engine(args, device):
     )
     schedule = make_schedule_builder("latency", options).build(model)
     schedule.globs.pos_id = prefill
-    tensorize_instructions(schedule.globs, assign_to_sms(args.sched, schedule=schedule))
-    generator = MK_Generator(
-        model, make_mk_interpreter("latency"), schedule, barrier_fill_val=args.barrier_fill
-    )
-    info = dict(attn_partitions=n_part, queue_len=int(schedule.globs.instructions.shape[1]),
-                instructions=len(schedule.get_linear_instructions()))
+    interp = make_mk_interpreter("latency")
+    if tp_size > 1:
+        generator = TP_MK_Generator(model, interp, schedule, group=group, sched=args.sched)
+        launches_per_step = len(generator.segments)
+    else:
+        tensorize_instructions(schedule.globs, assign_to_sms(args.sched, schedule=schedule))
+        generator = MK_Generator(model, interp, schedule, barrier_fill_val=args.barrier_fill)
+        launches_per_step = 1
+    info = dict(attn_partitions=n_part, instructions=len(schedule.get_linear_instructions()),
+                launches_per_step=launches_per_step)
     return cfg, prefill, model, schedule, generator, info
 
 
@@ -289,18 +300,31 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    cfg, prefill, model, schedule, gen, info = build_engine(args, device)
+    tp = WORKLOADS[args.workload]["tp"] and world > 1
+    if WORKLOADS[args.workload]["tp"] and world == 1:
+        raise SystemExit(f"{args.workload} is the tensor-parallel workload: launch it on 2, 4 or 8 GPUs")
+    cfg, prefill, model, schedule, gen, info = build_engine(
+        args, device, tp_size=world if tp else 1, tp_rank=rank if tp else 0
+    )
     K, W = args.steps, args.warmup
     ids = torch.randint(0, cfg.vocab_size, (W + K,), generator=torch.Generator().manual_seed(3))
     ids_dev = ids.to(device).view(-1, 1, 1)
+    use_graph = args.cuda_graph or tp  # 2L+1 launches per token are launch-bound without a graph
 
-    # ---- device-resident timing: exactly K steps between barriers -------- #
+    # ---- warm-up ----------------------------------------------------------- #
+    for i in range(min(W, 3)):
+        gen.run(ids_dev[i], pos_id=prefill + i)
+    gen.check()
+    if use_graph:
+        gen.enable_cuda_graph(warmup_pos=prefill)
     for i in range(W):
         gen.run(ids_dev[i], pos_id=prefill + i)
     gen.check()
+
+    # ---- device-resident timing: exactly K steps between barriers -------- #
     sampler = ClockSampler(local_rank)
-    launch_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launch_events = []
     interp = gen.interpreter
     globs = schedule.globs
     embed = model.model.embed_tokens.embed_tokens.weight
@@ -308,23 +332,34 @@ def run_ours(args):
     sampler.start()
     torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see only the timed region
     start.record()
-    for i in range(K):
-        # the body of MK_Generator.run, with events around the kernel launch
-        globs.hidden_states[:] = embed[ids_dev[W + i]].reshape(-1)
-        gen.fill()
-        globs.pos_id = prefill + W + i
-        e0, e1 = launch_events[i]
-        e0.record()
-        gen.last_call = interp.interpret(globs)
-        e1.record()
-        torch.argmax(globs.logits, dim=-1)
+    if use_graph:
+        for i in range(K):
+            gen.run(ids_dev[W + i], pos_id=prefill + W + i)
+    else:
+        for i in range(K):
+            # the body of MK_Generator.run, with events around the kernel launch
+            globs.hidden_states[:] = embed[ids_dev[W + i]].reshape(-1)
+            gen.fill()
+            globs.pos_id = prefill + W + i
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gen.last_call = interp.interpret(globs)
+            e1.record()
+            launch_events.append((e0, e1))
+            torch.argmax(globs.logits, dim=-1)
     end.record()
     torch.cuda.profiler.stop()
     barrier()
     clocks = sampler.stop()
     gen.check()
     elapsed_ms = start.elapsed_time(end)
-    kernel_ms = sum(a.elapsed_time(b) for a, b in launch_events) / K
+    if launch_events:
+        kernel_ms = sum(a.elapsed_time(b) for a, b in launch_events) / K
+        kernel_scope = "megakernel launch"
+    else:
+        # inside a graph the launches cannot be bracketed: the roofline covers the whole step
+        kernel_ms = elapsed_ms / K
+        kernel_scope = "whole decode step (graph replay" + (", incl. all-reduces)" if tp else ")")
 
     # ---- end to end: token id from pinned host memory, produced token back to host ---- #
     e2e = None
@@ -362,30 +397,35 @@ def run_ours(args):
     if rank == 0:
         peak, peak_kind = hbm_peak()
         mid_len = prefill + W + K // 2
-        nbytes = algorithmic_bytes_per_token(cfg, mid_len)
+        nbytes = algorithmic_bytes_per_token(cfg, mid_len, tp=world if tp else 1)
         algo = sum(nbytes.values())
         achieved = algo / (kernel_ms * 1e-3) / 1e9
+        replicas = 1 if tp else world  # a tensor-parallel job decodes one sequence
         line = {
             "metric": METRIC,
-            "value": world * K / (elapsed_ms * 1e-3),
+            "value": replicas * K / (elapsed_ms * 1e-3),
             "unit": UNIT,
             "n_gpus": world,
             "steps": K,
             "warmup": W,
             "ms_per_step": elapsed_ms / K,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": "strong" if tp else "weak",
             "vs_baseline": None,
             "dtype": "bf16",
             "data": "synthetic",
             "config": {
                 "workload": f"{args.workload} batch-1 decode, {cfg.num_hidden_layers} layers, KV prefill {prefill}, "
-                            f"{K} teacher-forced steps" + (f", {world} independent replicas" if world > 1 else ""),
+                            f"{K} teacher-forced steps"
+                            + (f", tensor parallel over {world} GPUs (NCCL all-reduce after o-proj and down-proj)" if tp
+                               else (f", {world} independent replicas" if world > 1 else "")),
+                "launch": "cuda graph replay" if use_graph else "eager",
                 "inputs": "larger than L2 (weights re-streamed from HBM every step)",
                 "sched": args.sched,
                 **info,
             },
             "kernel_ms_per_launch": kernel_ms,
+            "roofline_scope": kernel_scope,
             "roofline": {
                 "bound": "hbm",
                 "achieved": achieved,
@@ -395,16 +435,16 @@ def run_ours(args):
                 "peak_source": f"{peak_kind} copy bandwidth",
                 "frac_of_nominal_8TBs": achieved / 8000.0,
                 "weight_only_frac": (nbytes["weights"] / (kernel_ms * 1e-3) / 1e9) / peak,
-                "algorithmic_bytes_per_launch": algo,
+                "algorithmic_bytes_per_launch": algo,  # per GPU and decoded token
                 "traffic": algo * NCU_TRAFFIC_RATIO,
                 "traffic_source": "ncu dram bytes of a 4-layer capture scaled to this launch",
             },
             "clocks": clocks,
-            "gpu_launches": world * K,
+            "gpu_launches": world * K * info["launches_per_step"],
         }
         if e2e is not None:
             line["e2e"] = {
-                "value": world * K / e2e,
+                "value": replicas * K / e2e,
                 "unit": UNIT,
                 "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8,

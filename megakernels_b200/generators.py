@@ -81,7 +81,52 @@ class MK_Generator(Generator):
     def replace_with_noops(self):
         self.schedule.globs.instructions.zero_()
 
+    # -- CUDA-graph replay of one decode step -------------------------------- #
+    def enable_cuda_graph(self, warmup_pos: int = 0):
+        """Capture one decode step (embed, barrier reset, kernel launches, collectives,
+        argmax) into a CUDA graph that every later ``run`` replays.
+
+        The position is then read by the kernel from a device word
+        (``globs.pos_id_device``) and the input token from a device buffer, so one
+        graph serves all tokens and the per-launch host work disappears.  The
+        reference launches eagerly (megakernels/generators.py:121-143).
+        """
+        globs = self.schedule.globs
+        device = globs.hidden_states.device
+        self._graph_tok = torch.zeros(1, 1, dtype=torch.long, device=device)
+        self._graph_out = torch.zeros(1, dtype=torch.long, device=device)
+        globs.pos_id_device = torch.full((1,), warmup_pos, dtype=torch.int32, device=device)
+        globs.pos_id = warmup_pos
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # first calls allocate (status record, descriptor cache, NCCL)
+                self._graph_out.copy_(self._step(self._graph_tok).reshape(-1))
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._graph_out.copy_(self._step(self._graph_tok).reshape(-1))
+        return self
+
+    def _step(self, input_ids: Tensor) -> Tensor:
+        """The device work of one token; the position is already in the globals."""
+        globs = self.schedule.globs
+        post = self.model.model.embed_tokens(BatchState(input_ids=input_ids))
+        globs.hidden_states[:] = post.hidden_states.reshape(-1)
+        self.fill()
+        self.last_call = self.interpreter.interpret(globs)
+        return torch.argmax(globs.logits, dim=-1)
+
+    def _replay(self, input_ids: Tensor, pos_id: int) -> Tensor:
+        self._graph_tok.copy_(input_ids.reshape(1, 1))
+        self.schedule.globs.pos_id_device.fill_(pos_id)
+        self._graph.replay()
+        return self._graph_out
+
     def run(self, input_ids: Tensor, pos_id: int):
+        if getattr(self, "_graph", None) is not None:
+            return self._replay(input_ids, pos_id)
         globs = self.schedule.globs
         if not self.skip_rest:
             post = self.model.model.embed_tokens(BatchState(input_ids=input_ids))
@@ -189,9 +234,18 @@ class TP_MK_Generator(MK_Generator):
     def finish_token(self) -> Tensor:
         return torch.argmax(self.schedule.globs.logits, dim=-1)
 
-    def run(self, input_ids: Tensor, pos_id: int):
-        self.begin_token(input_ids, pos_id)
+    def _step(self, input_ids: Tensor) -> Tensor:
+        globs = self.schedule.globs
+        post = self.model.model.embed_tokens(BatchState(input_ids=input_ids))
+        globs.hidden_states[:] = post.hidden_states.reshape(-1)
+        self.fill()
         for k in range(len(self.segments)):
             if self.launch_segment(k):
-                self.all_reduce(self.schedule.globs.hidden_states)
+                self.all_reduce(globs.hidden_states)
         return self.finish_token()
+
+    def run(self, input_ids: Tensor, pos_id: int):
+        if getattr(self, "_graph", None) is not None:
+            return self._replay(input_ids, pos_id)
+        self.schedule.globs.pos_id = pos_id
+        return self._step(input_ids)
