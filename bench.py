@@ -303,9 +303,12 @@ def run_ours(args):
     tp = WORKLOADS[args.workload]["tp"] and world > 1
     if WORKLOADS[args.workload]["tp"] and world == 1:
         raise SystemExit(f"{args.workload} is the tensor-parallel workload: launch it on 2, 4 or 8 GPUs")
+    log("building model and schedule")
     cfg, prefill, model, schedule, gen, info = build_engine(
         args, device, tp_size=world if tp else 1, tp_rank=rank if tp else 0
     )
+    gen_holder = [gen]
+    log(f"engine ready: {info}")
     K, W = args.steps, args.warmup
     ids = torch.randint(0, cfg.vocab_size, (W + K,), generator=torch.Generator().manual_seed(3))
     ids_dev = ids.to(device).view(-1, 1, 1)
@@ -315,13 +318,16 @@ def run_ours(args):
     for i in range(min(W, 3)):
         gen.run(ids_dev[i], pos_id=prefill + i)
     gen.check()
+    log("eager warm-up done")
     if use_graph:
         gen.enable_cuda_graph(warmup_pos=prefill)
+        log("graph captured")
     for i in range(W):
         gen.run(ids_dev[i], pos_id=prefill + i)
     gen.check()
 
     # ---- device-resident timing: exactly K steps between barriers -------- #
+    log("warm-up done, timing")
     sampler = ClockSampler(local_rank)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launch_events = []
@@ -329,6 +335,7 @@ def run_ours(args):
     globs = schedule.globs
     embed = model.model.embed_tokens.embed_tokens.weight
     barrier()
+    log("barrier passed")
     sampler.start()
     torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see only the timed region
     start.record()
@@ -349,7 +356,9 @@ def run_ours(args):
             torch.argmax(globs.logits, dim=-1)
     end.record()
     torch.cuda.profiler.stop()
+    log("timed steps enqueued")
     barrier()
+    log("timed steps finished")
     clocks = sampler.stop()
     gen.check()
     elapsed_ms = start.elapsed_time(end)
@@ -457,8 +466,22 @@ def run_ours(args):
             line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
     if distributed:
+        # Tear down in a fixed order: captured graphs hold NCCL kernels, and destroying the
+        # communicator underneath them was seen to block at interpreter exit.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        if getattr(gen_holder[0], "_graph", None) is not None:
+            gen_holder[0]._graph = None
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def log(msg: str):
+    """Progress lines on stderr when MKB_BENCH_VERBOSE is set (stdout carries only the JSON line)."""
+    if os.environ.get("MKB_BENCH_VERBOSE"):
+        print(f"[bench {time.strftime('%H:%M:%S')} rank {os.environ.get('RANK', '0')}] {msg}",
+              file=sys.stderr, flush=True)
 
 
 def main():
