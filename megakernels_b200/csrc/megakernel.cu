@@ -725,8 +725,6 @@ template <int D, int GQA>
 __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w) {
     constexpr int DPL = D / 32;
     constexpr int TS = (kStageBytes / 4) / D;      // positions per stage
-    constexpr int NPW = TS / kConsumerWarps;       // positions per warp per stage
-    constexpr int HP = kAttnHeadsPerPass;
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int layer = __ldg(w + 1), kvh = __ldg(w + 2), np = __ldg(w + 3), pi = __ldg(w + 4);
@@ -749,110 +747,158 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         if (*verdict == 0) return false;
     }
 
-    // q for the GQA heads, pre-scaled into the log2 domain
-    float q[GQA][DPL];
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-        load_row_gmem<DPL>(p.q_rope + (size_t)(kvh * GQA + h) * D + lane * DPL, q[h]);
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) q[h][i] *= p.attn_scale_log2e;
-    }
+    // ---- tensor-core flash decoding ------------------------------------------------
+    // A stage holds TS positions of K and V.  It is cut into units of 16 positions
+    // and the head dimension into slices of 32: warp (unit, slice) computes the
+    // scores of its unit over the full head dimension (S^T = Q K^T, M = heads padded
+    // to 16, N = 8 positions per MMA) and accumulates O for its 32 dimensions
+    // (O = P V with V fed through ldmatrix.trans).  Warps of the same unit repeat the
+    // cheap score computation so that no exchange is needed before the end.
+    constexpr int U = TS / 16;            // units per stage
+    constexpr int SL = D / 32;            // 32-dim slices; U * SL == 16 warps
+    static_assert(U * SL == kConsumerWarps, "warp grid must cover a stage");
+    constexpr int KP = D / 32;            // 16-byte chunk pairs of a K row per thread (2 k-steps each)
+    const int unit = warp / SL, slice = warp % SL;
+    const int g = lane >> 2, t = lane & 3;
+    const bool head_ok = g < GQA;
 
+    // Q as A operand: row g = head g, chunk (t + 4 j) of the head dimension
+    uint4 qa[KP];
+#pragma unroll
+    for (int j = 0; j < KP; ++j) {
+        qa[j] = make_uint4(0, 0, 0, 0);
+        if (head_ok) qa[j] = ld_cg_v4(p.q_rope + (size_t)(kvh * GQA + g) * D + (t + 4 * j) * 8);
+    }
     if (tid == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     // the token being decoded: its K/V were appended by another SM in this launch,
     // so warp 0 reads them straight from global memory (issued now, used last)
-    float k_cur[DPL], v_cur[1][DPL];
+    float k_cur[DPL], v_cur[DPL];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) k_cur[i] = v_cur[0][i] = 0.f;
+    for (int i = 0; i < DPL; ++i) k_cur[i] = v_cur[i] = 0.f;
+    float q_cur[GQA][DPL];
     if (warp == 0 && r.has_cur) {
         const size_t off = (((size_t)layer * p.B) * p.T + c.pos) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
         load_row_gmem<DPL>(p.k_cache + off, k_cur);
-        load_row_gmem<DPL>(p.v_cache + off, v_cur[0]);
+        load_row_gmem<DPL>(p.v_cache + off, v_cur);
+#pragma unroll
+        for (int h = 0; h < GQA; ++h)
+            load_row_gmem<DPL>(p.q_rope + (size_t)(kvh * GQA + h) * D + lane * DPL, q_cur[h]);
     }
 
-    AttnAcc<GQA, DPL> acc;
-    acc.init();
+    float m_run = -INFINITY, l_run = 0.f;  // head g, replicated over t
+    float o[4][4];                          // 4 n-tiles of 8 dims; [i][0..1] belong to head g
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
     for (int s = 0; s < r.n_stages; ++s) {
         const uint32_t kbase = consumer_wait_stage(c, cs);
         const uint32_t vbase = kbase + kStageBytes / 2;
-        const int tbase = r.t0 + s * TS;
-        if (tbase + warp < r.t_old_end) {  // this warp has at least one valid position
-            float part[NPW * GQA];
-            float vv[NPW][DPL];
+        const int pos0 = r.t0 + s * TS + unit * 16;  // first position of this warp's unit
+        if (pos0 < r.t_old_end) {
+            // scores: two n-tiles of 8 positions
+            float sc[2][4];
 #pragma unroll
-            for (int j = 0; j < NPW; ++j) {
-                const int pos_in_stage = warp + j * kConsumerWarps;
-                float kk[DPL];
-                load_row_smem<DPL>(kbase + (uint32_t)pos_in_stage * (D * 2) + lane * (DPL * 2), kk);
-                load_row_smem<DPL>(vbase + (uint32_t)pos_in_stage * (D * 2) + lane * (DPL * 2), vv[j]);
+            for (int nt = 0; nt < 2; ++nt) {
+                sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+                const uint32_t krow = kbase + (uint32_t)(unit * 16 + nt * 8 + g) * (D * 2) + t * 16;
 #pragma unroll
-                for (int h = 0; h < GQA; ++h) {
-                    float d = 0.f;
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) d = fmaf(q[h][i], kk[i], d);
-                    part[j * GQA + h] = d;
+                for (int j = 0; j < KP; ++j) {
+                    const uint4 kk = lds_v4(krow + j * 64);
+                    mma_16816(sc[nt], qa[j].x, 0u, qa[j].y, 0u, kk.x, kk.y);
+                    mma_16816(sc[nt], qa[j].z, 0u, qa[j].w, 0u, kk.z, kk.w);
                 }
             }
-            // lane l now gets the full dot product of element l / (32 / N)
-            constexpr int N = NPW * GQA;
-            static_assert(N <= 32, "scores per warp per stage must fit one warp");
-            const float mine = warp_transpose_reduce<N>(part, lane);
-            float s_all[NPW][GQA];
+            // scale into the log2 domain, mask, running max of head g
+            float smax = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < NPW; ++j) {
-                const bool valid = (tbase + warp + j * kConsumerWarps) < r.t_old_end;
+            for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int h = 0; h < GQA; ++h) {
-                    const float sv = __shfl_sync(0xffffffffu, mine, (j * GQA + h) * (32 / N));
-                    s_all[j][h] = valid ? sv : -INFINITY;
+                for (int e = 0; e < 2; ++e) {
+                    const int pos = pos0 + nt * 8 + 2 * t + e;
+                    const float v = (pos < r.t_old_end) ? sc[nt][e] * p.attn_scale_log2e : -INFINITY;
+                    sc[nt][e] = v;
+                    smax = fmaxf(smax, v);
                 }
+            smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, 1));
+            smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, 2));
+            const float m_new = fmaxf(m_run, smax);
+            const float ms = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = exp2f(m_run - ms);
+            m_run = m_new;
+            float psum = 0.f;
+            uint32_t pa[2];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const float p0 = exp2f(sc[nt][0] - ms), p1 = exp2f(sc[nt][1] - ms);
+                psum += p0 + p1;
+                pa[nt] = pack_bf16x2(p0, p1);
             }
-            attn_fold<GQA, DPL, NPW>(acc, s_all, vv);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            l_run = l_run * alpha + psum;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                o[i][0] *= alpha;
+                o[i][1] *= alpha;
+            }
+            // O += P V: V rows (positions) x 8-dim column tiles through ldmatrix.trans
+            const int mat = lane >> 3, rr = lane & 7;
+            const uint32_t vrow = vbase + (uint32_t)(unit * 16 + (mat & 1) * 8 + rr) * (D * 2) +
+                                  (uint32_t)(slice * 32 + (mat >> 1) * 8) * 2;
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {  // two pairs of n-tiles
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                             : "r"(vrow + h2 * 32));
+                mma_16816(o[2 * h2], pa[0], 0u, pa[1], 0u, b0, b1);
+                mma_16816(o[2 * h2 + 1], pa[0], 0u, pa[1], 0u, b2, b3);
+            }
         }
         // the last KV stage stays ours: its 32 KiB become the merge scratch below
         if (s + 1 < r.n_stages) consumer_release_stage(c, cs, lane);
     }
     if (tid == 0) rec(c, 5);
 
+    // score of the token being decoded (warp 0, fp32): one more entry for the merge
+    float s_cur[GQA];
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) s_cur[h] = -INFINITY;
     if (warp == 0 && r.has_cur) {
-        float s1[1][GQA];
 #pragma unroll
         for (int h = 0; h < GQA; ++h) {
             float d = 0.f;
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) d = fmaf(q[h][i], k_cur[i], d);
+            for (int i = 0; i < DPL; ++i) d = fmaf(q_cur[h][i], k_cur[i], d);
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-            s1[0][h] = d;
+            for (int o2 = 16; o2 >= 1; o2 >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o2);
+            s_cur[h] = d * p.attn_scale_log2e;
         }
-        attn_fold<GQA, DPL, 1>(acc, s1, v_cur);
     }
 
     if (r.n_stages == 0) {
-        // no cached positions in this slice: at most the current token, held by warp 0
+        // no cached positions in this slice: at most the current token, whose softmax weight is 1
         if (warp == 0 && !cs.dead) {
 #pragma unroll
             for (int h = 0; h < GQA; ++h) {
                 const int head = kvh * GQA + h;
-                const float inv = acc.l[h] > 0.f ? 1.f / acc.l[h] : 0.f;
+                const float wgt = r.has_cur ? 1.f : 0.f;
                 if (p.skip_attn_reduction) {
                     __nv_bfloat16* dst = p.attn_out + (size_t)head * D + lane * DPL;
                     if constexpr (DPL == 4) {
                         uint2 v;
-                        v.x = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
-                        v.y = pack_bf16x2(acc.o[h][2] * inv, acc.o[h][3] * inv);
+                        v.x = pack_bf16x2(v_cur[0] * wgt, v_cur[1] * wgt);
+                        v.y = pack_bf16x2(v_cur[2] * wgt, v_cur[3] * wgt);
                         *reinterpret_cast<uint2*>(dst) = v;
                     } else {
-                        *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(acc.o[h][0] * inv, acc.o[h][1] * inv);
+                        *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(v_cur[0] * wgt, v_cur[1] * wgt);
                     }
                 } else {
                     float* dst = p.attn_o + ((size_t)head * p.max_partials + pi) * D + lane * DPL;
 #pragma unroll
-                    for (int i = 0; i < DPL; ++i) dst[i] = acc.o[h][i] * inv;
+                    for (int i = 0; i < DPL; ++i) dst[i] = v_cur[i] * wgt;
                     if (lane == 0)
-                        p.attn_lse[(size_t)head * p.max_partials + pi] =
-                            acc.l[h] > 0.f ? acc.m[h] + log2f(acc.l[h]) : -INFINITY;
+                        p.attn_lse[(size_t)head * p.max_partials + pi] = r.has_cur ? s_cur[h] : -INFINITY;
                 }
             }
             __syncwarp();
@@ -867,52 +913,58 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         return true;
     }
 
-    // One-round merge of the 16 warps: everybody parks (m, l, O) in shared memory -
-    // O in the KV stage we still own, [warp][head][D] - then thread (head, dim)
-    // combines the 16 entries of its output element.
+    // One-round merge of the U units (+ the current token as entry U): O goes into the
+    // KV stage we still own, [entry][head][D]; (m, l) into the small scratch.
     float* so = reinterpret_cast<float*>(__cvta_shared_to_generic(c.stage_addr(cs.slot)));
     float* sml = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemAttn));
+    consumer_sync();  // every warp is done reading K/V from the stage
+    if (head_ok) {
 #pragma unroll
-    for (int pass = 0; pass < GQA / HP; ++pass) {
-        // pass 0: every warp must be done reading K/V from the stage before anyone
-        // overwrites it; later passes: the previous pass's readers must be done
-        consumer_sync();
+        for (int i = 0; i < 4; ++i) {
+            float* dst = so + (size_t)(unit * GQA + g) * D + slice * 32 + i * 8 + 2 * t;
+            dst[0] = o[i][0];
+            dst[1] = o[i][1];
+        }
+        if (slice == 0 && t == 0) {
+            sml[(unit * GQA + g) * 2 + 0] = m_run;
+            sml[(unit * GQA + g) * 2 + 1] = l_run;
+        }
+    }
+    if (warp == 0) {
 #pragma unroll
-        for (int hh = 0; hh < HP; ++hh) {
-            const int h = pass * HP + hh;
+        for (int h = 0; h < GQA; ++h) {
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) so[(warp * HP + hh) * D + lane * DPL + i] = acc.o[h][i];
+            for (int i = 0; i < DPL; ++i) so[(size_t)(U * GQA + h) * D + lane * DPL + i] = v_cur[i];
             if (lane == 0) {
-                sml[(warp * HP + hh) * 2 + 0] = acc.m[h];
-                sml[(warp * HP + hh) * 2 + 1] = acc.l[h];
+                sml[(U * GQA + h) * 2 + 0] = s_cur[h];
+                sml[(U * GQA + h) * 2 + 1] = r.has_cur ? 1.f : 0.f;
             }
         }
-        consumer_sync();
-        if (tid < HP * D) {  // whole warps: HP * D is a multiple of 32
-            const int hh = tid / D, d = tid % D;
-            float mx = -INFINITY;
+    }
+    consumer_sync();
+    for (int idx = tid; idx < GQA * D; idx += kConsumerThreads) {  // whole warps: D is a multiple of 32
+        const int hh = idx / D, d = idx % D;
+        float mx = -INFINITY;
 #pragma unroll
-            for (int w2 = 0; w2 < kConsumerWarps; ++w2) mx = fmaxf(mx, sml[(w2 * HP + hh) * 2]);
-            const float ms = (mx == -INFINITY) ? 0.f : mx;
-            float num = 0.f, den = 0.f;
+        for (int e = 0; e <= U; ++e) mx = fmaxf(mx, sml[(e * GQA + hh) * 2]);
+        const float ms = (mx == -INFINITY) ? 0.f : mx;
+        float num = 0.f, den = 0.f;
 #pragma unroll
-            for (int w2 = 0; w2 < kConsumerWarps; ++w2) {
-                const float a = exp2f(sml[(w2 * HP + hh) * 2] - ms);
-                den = fmaf(a, sml[(w2 * HP + hh) * 2 + 1], den);
-                num = fmaf(a, so[(w2 * HP + hh) * D + d], num);
-            }
-            const float val = den > 0.f ? num / den : 0.f;
-            const int head = kvh * GQA + pass * HP + hh;
-            if (p.skip_attn_reduction) {
-                const float hi = __shfl_down_sync(0xffffffffu, val, 1);
-                if ((d & 1) == 0 && !cs.dead)
-                    *reinterpret_cast<uint32_t*>(p.attn_out + (size_t)head * D + d) = pack_bf16x2(val, hi);
-            } else if (!cs.dead) {
-                p.attn_o[((size_t)head * p.max_partials + pi) * D + d] = val;
-                if (d == 0)
-                    p.attn_lse[(size_t)head * p.max_partials + pi] =
-                        den > 0.f ? mx + log2f(den) : -INFINITY;
-            }
+        for (int e = 0; e <= U; ++e) {
+            const float a2 = exp2f(sml[(e * GQA + hh) * 2] - ms);
+            den = fmaf(a2, sml[(e * GQA + hh) * 2 + 1], den);
+            num = fmaf(a2, so[(size_t)(e * GQA + hh) * D + d], num);
+        }
+        const float val = den > 0.f ? num / den : 0.f;
+        const int head = kvh * GQA + hh;
+        if (p.skip_attn_reduction) {
+            const float hi = __shfl_down_sync(0xffffffffu, val, 1);
+            if ((d & 1) == 0 && !cs.dead)
+                *reinterpret_cast<uint32_t*>(p.attn_out + (size_t)head * D + d) = pack_bf16x2(val, hi);
+        } else if (!cs.dead) {
+            p.attn_o[((size_t)head * p.max_partials + pi) * D + d] = val;
+            if (d == 0)
+                p.attn_lse[(size_t)head * p.max_partials + pi] = den > 0.f ? mx + log2f(den) : -INFINITY;
         }
     }
     consumer_sync();  // scratch reads and global stores of all threads are done
