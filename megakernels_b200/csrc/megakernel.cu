@@ -147,6 +147,40 @@ __device__ __noinline__ bool wait_counter(const Ctx& c, const int* addr, int thr
     }
 }
 
+// Warp-collective bounded wait on up to 32 counters at once: lane i polls addr (nullptr =
+// nothing to wait for).  Sequential waits would cost one L2 round trip per counter.
+__device__ __noinline__ bool warp_wait_counters(const Ctx& c, const int* addr, int threshold,
+                                                int layer, int row, int slot) {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        const int v = addr ? ld_acquire_gpu(addr) : threshold;
+        if (__all_sync(0xffffffffu, v >= threshold)) return true;
+        if ((++spins & 63u) == 0) {
+            int stop = 0;
+            if ((threadIdx.x & 31) == 0) {
+                if (*c.cta_abort) stop = 1;
+                else if (global_abort(c)) {
+                    *c.cta_abort = 1;
+                    stop = 1;
+                } else {
+                    const unsigned long long now = globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > c.p->timeout_ns) stop = 2;
+                }
+            }
+            stop = __shfl_sync(0xffffffffu, stop, 0);
+            if (stop == 2) {  // the first lane still waiting names the stuck counter
+                const unsigned late = __ballot_sync(0xffffffffu, v < threshold);
+                if ((int)(threadIdx.x & 31) == __ffs(late) - 1)
+                    report_error(c, MKB_ERR_DEVICE_TIMEOUT, layer, row, slot, v);
+            }
+            if (stop) return false;
+        }
+        __nanosleep(c.p->poll_sleep_ns);
+    }
+}
+
 __device__ __forceinline__ int* bar_addr(const KParams& p, int layer, int row, int slot) {
     return p.barriers + ((size_t)layer * p.barrier_ops + row) * p.barrier_width + slot;
 }
@@ -733,15 +767,20 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
     // barrier: the GQA query heads, then this KV head's K and V blocks
     {
         volatile int* verdict = verdict_word(c, cs);
-        if (tid == 0) {
-            bool ok = !*c.cta_abort;
+        if (warp == 0) {
+            // lanes 0..GQA-1: the query heads; then this KV head's K and V slots
             const int row = MKB_OP_RMS_QKV_ROPE_APPEND - 1;
-            for (int h = 0; h < GQA && ok; ++h)
-                ok = wait_counter(c, bar_addr(p, layer, row, kvh * GQA + h), p.thr_attn_waits_qkv, layer, row, kvh * GQA + h);
-            if (ok) ok = wait_counter(c, bar_addr(p, layer, row, p.Hq + kvh), p.thr_attn_waits_qkv, layer, row, p.Hq + kvh);
-            if (ok) ok = wait_counter(c, bar_addr(p, layer, row, p.Hq + p.Hkv + kvh), p.thr_attn_waits_qkv, layer, row, p.Hq + p.Hkv + kvh);
-            rec(c, MKB_T_CONSUMER_WAIT_DONE);
-            *verdict = ok ? 1 : 0;
+            int slot = -1;
+            if (lane < GQA) slot = kvh * GQA + lane;
+            else if (lane == GQA) slot = p.Hq + kvh;
+            else if (lane == GQA + 1) slot = p.Hq + p.Hkv + kvh;
+            bool ok = __shfl_sync(0xffffffffu, *c.cta_abort, 0) == 0;  // uniform over the warp
+            ok = ok && warp_wait_counters(c, slot >= 0 ? bar_addr(p, layer, row, slot) : nullptr,
+                                          p.thr_attn_waits_qkv, layer, row, slot);
+            if (lane == 0) {
+                rec(c, MKB_T_CONSUMER_WAIT_DONE);
+                *verdict = ok ? 1 : 0;
+            }
         }
         consumer_sync();
         if (*verdict == 0) return false;
@@ -991,13 +1030,15 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
     const int is_terminal = __ldg(w + 4), n = __ldg(w + 5);
     const int out_idx = __ldg(w + 6 + n);
     volatile int* verdict = verdict_word(c, cs);
-    if (tid == 0) {
-        bool ok = !*c.cta_abort;
+    if (warp == 0) {
         const int row = MKB_OP_PARTIAL_ATTENTION - 1;
-        for (int h = 0; h < 4 && ok; ++h)
-            ok = wait_counter(c, bar_addr(p, layer, row, h0 + h), num_partials, layer, row, h0 + h);
-        rec(c, MKB_T_CONSUMER_WAIT_DONE);
-        *verdict = ok ? 1 : 0;
+        bool ok = __shfl_sync(0xffffffffu, *c.cta_abort, 0) == 0;  // uniform over the warp
+        ok = ok && warp_wait_counters(c, lane < 4 ? bar_addr(p, layer, row, h0 + lane) : nullptr,
+                                      num_partials, layer, row, h0 + lane);
+        if (lane == 0) {
+            rec(c, MKB_T_CONSUMER_WAIT_DONE);
+            *verdict = ok ? 1 : 0;
+        }
     }
     consumer_sync();
     if (*verdict == 0) return false;
