@@ -296,8 +296,6 @@ struct StreamCursor {
                 sb = __ldg(w + 2);
                 eb = __ldg(w + 3) - sb;
                 set_matrix(&p.qkv_map, p.H, 0, __ldg(w + 1));
-                // the consumers will want this layer's norm weights: have them in L2 by then
-                prefetch_l2_bulk(p.attn_ln_w + (size_t)__ldg(w + 1) * p.H, (uint32_t)p.H * 2u);
                 break;
             case MKB_OP_O_PROJ_RESIDUAL:
                 sb = __ldg(w + 2);
@@ -308,7 +306,6 @@ struct StreamCursor {
                 eb = 2 * __ldg(w + 2);
                 set_matrix(&p.up_map, p.H, 0, __ldg(w + 1));
                 map2 = &p.gate_map;
-                prefetch_l2_bulk(p.mlp_ln_w + (size_t)__ldg(w + 1) * p.H, (uint32_t)p.H * 2u);
                 break;
             case MKB_OP_DOWN_PROJ_RESIDUAL:
                 sb = __ldg(w + 2);
@@ -319,7 +316,6 @@ struct StreamCursor {
                 sb = __ldg(w + 1);
                 eb = __ldg(w + 2) - sb;
                 set_matrix(&p.lm_map, p.H, 0, 0);
-                prefetch_l2_bulk(p.lm_norm_w, (uint32_t)p.H * 2u);
                 break;
             case MKB_OP_PARTIAL_ATTENTION: {
                 const AttnRange r = attn_range(p, pos, __ldg(w + 3), __ldg(w + 4));
@@ -382,6 +378,21 @@ __device__ void loader_main(Ctx c) {
     const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
     c.role = kRoleLoader;
 
+    // Norm weights are tiny but sit on the critical path right after every barrier; a miss
+    // to HBM under full streaming load costs microseconds.  Pin them in L2 up front: CTA b
+    // takes rows b, b + gridDim.x, ... of the 2 L + 1 norm vectors.
+    {
+        uint64_t keep;
+        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
+        for (int row = blockIdx.x; row < 2 * p.L + 1; row += gridDim.x) {
+            const __nv_bfloat16* src = row < p.L ? p.attn_ln_w + (size_t)row * p.H
+                                       : row < 2 * p.L ? p.mlp_ln_w + (size_t)(row - p.L) * p.H
+                                                       : p.lm_norm_w;
+            asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(src),
+                         "r"((uint32_t)p.H * 2u), "l"(keep)
+                         : "memory");
+        }
+    }
     StreamCursor issue, ahead;  // `ahead` is never behind `issue`
     issue.pos = ahead.pos = c.pos;
     StageDesc d, da;
@@ -1051,27 +1062,19 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
         idx = __ldg(w + 6 + lane);
         lse = ld_cg_f32(p.attn_lse + (size_t)head * p.max_partials + idx);
     }
-    float mx = lse;
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    const float ms = (mx == -INFINITY) ? 0.f : mx;
-    const float wgt = exp2f(lse - ms);
-    float denom = wgt;
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    // Batches of 12 partial rows: all loads of a batch are issued before the first value
+    // (the LSEs included) is used, so the L2 round trips overlap instead of adding up.
+    constexpr int NB = 12;
     float o_acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) o_acc[i] = 0.f;
-    // batches of 8 partials: issue all loads of a batch, then accumulate, so the
-    // L2 round trips overlap instead of adding up
-    for (int j0 = 0; j0 < n; j0 += 8) {
-        float part[8][DPL];
-        float wj[8];
+    float mx = 0.f, wgt = 0.f, denom = 0.f;
+    for (int j0 = 0; j0 < n; j0 += NB) {
+        float part[NB][DPL];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
+        for (int jj = 0; jj < NB; ++jj) {
             const int j = j0 + jj;
             const int ij = __shfl_sync(0xffffffffu, idx, j & 31);
-            wj[jj] = (j < n) ? __shfl_sync(0xffffffffu, wgt, j & 31) : 0.f;
             const float* src = p.attn_o + ((size_t)head * p.max_partials + (j < n ? ij : 0)) * D + lane * DPL;
             if constexpr (DPL == 4) {
                 const uint4 v = ld_cg_v4(src);
@@ -1082,10 +1085,23 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
                 part[jj][0] = __uint_as_float(v.x); part[jj][1] = __uint_as_float(v.y);
             }
         }
+        if (j0 == 0) {
+            mx = lse;
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj)
+            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float ms = (mx == -INFINITY) ? 0.f : mx;
+            wgt = exp2f(lse - ms);
+            denom = wgt;
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) o_acc[i] = fmaf(wj[jj], part[jj][i], o_acc[i]);
+            for (int o = 16; o >= 1; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+        }
+#pragma unroll
+        for (int jj = 0; jj < NB; ++jj) {
+            const int j = j0 + jj;
+            const float wj = (j < n) ? __shfl_sync(0xffffffffu, wgt, j & 31) : 0.f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o_acc[i] = fmaf(wj, part[jj][i], o_acc[i]);
+        }
     }
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
     if (is_terminal) {
@@ -1258,6 +1274,13 @@ __device__ void storer_main(Ctx c) {
     const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
     c.role = kRoleStorer;
     const int kh_partials = kConsumerWarps, kr_partials = kConsumerWarps;  // one partial per warp
+    // this token's RoPE row is only read by this warp: fetch it once, off the critical path
+    for (int d = lane; d < p.D; d += 32) {
+        float* rope = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemRope));
+        rope[d] = __ldg(p.rope_cos + (size_t)c.pos * p.D + d);
+        rope[128 + d] = __ldg(p.rope_sin + (size_t)c.pos * p.D + d);
+    }
+    __syncwarp();
     const int k_start = p.Hq * p.D, v_start = (p.Hq + p.Hkv) * p.D;
 
     for (int i = 0; i < p.queue_len; ++i) {
@@ -1276,8 +1299,8 @@ __device__ void storer_main(Ctx c) {
                     const int start = b * kBlockRows;
                     if (start < v_start) {
                         const int seg = start % p.D;
-                        const float cs_ = __ldg(p.rope_cos + (size_t)c.pos * p.D + seg + row);
-                        const float sn = __ldg(p.rope_sin + (size_t)c.pos * p.D + seg + row);
+                        const float cs_ = __uint_as_float(lds_u32(c.base + kSmemRope + (seg + row) * 4));
+                        const float sn = __uint_as_float(lds_u32(c.base + kSmemRope + (128 + seg + row) * 4));
                         const float other = __shfl_xor_sync(0xffffffffu, v, 1);
                         const float rot = (row & 1) ? other : -other;
                         v = v * cs_ + rot * sn;

@@ -46,7 +46,8 @@ constexpr int kSmemRing = 0;
 constexpr int kSmemOut = kSmemRing + kNumStages * kStageBytes;
 constexpr int kSmemAttn = kSmemOut + kOutSlots * kOutSlotFloats * 4;
 constexpr int kSmemRed = kSmemAttn + kAttnScratchFloats * 4;  // 32 floats
-constexpr int kSmemBars = kSmemRed + 32 * 4;                   // mbarriers, 8 B each
+constexpr int kSmemRope = kSmemRed + 32 * 4;                   // cos[D], sin[D] of this token's position
+constexpr int kSmemBars = kSmemRope + 2 * 128 * 4;             // mbarriers, 8 B each
 constexpr int kNumMbars = 2 * kNumStages + 2 * kOutSlots;
 constexpr int kSmemCtl = kSmemBars + kNumMbars * 8;            // 8 ints of control words
 constexpr int kSmemTotal = kSmemCtl + 8 * 4;
