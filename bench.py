@@ -65,6 +65,8 @@ def parse_args():
     ap.add_argument("--sched", default="rr")
     ap.add_argument("--attn-partitions", type=int, default=0, help="0 = pick from the length")
     ap.add_argument("--no-coalesce-o-proj", action="store_true")
+    ap.add_argument("--balance", action="store_true",
+                    help="timeline-model builder with pinned SMs instead of the even split + --sched")
     ap.add_argument("--barrier-fill", type=int, default=0,
                     help="experiment: preset all barrier counters (waits pass at once; results are garbage)")
     ap.add_argument("--cuda-graph", action="store_true",
@@ -265,9 +267,12 @@ def build_engine(args, device, tp_size=1, tp_rank=0, group=None):
     n_part = args.attn_partitions or pick_num_attention_partitions(
         prefill, args.steps + args.warmup, device, model.num_kv_heads(), min_chunk_size=128
     )
+    balance = args.balance
     options = LatencyScheduleOptions(
-        num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj
+        num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj, balance=balance
     )
+    if balance:
+        args.sched = "hint"
     schedule = make_schedule_builder("latency", options).build(model)
     schedule.globs.pos_id = prefill
     interp = make_mk_interpreter("latency")

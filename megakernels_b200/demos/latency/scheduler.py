@@ -44,6 +44,9 @@ class LatencyScheduleOptions:
 
     num_attention_partitions: int = 1
     coalesce_o_proj: bool = False
+    # block split and SM mapping from a per-SM timeline model (demos/latency/balanced.py);
+    # the resulting stream must be assigned with assign_to_sms("hint", ...)
+    balance: bool = False
 
 
 def pick_num_attention_partitions(
@@ -329,6 +332,11 @@ def make_dag(
     options: LatencyScheduleOptions | None = None,
 ):
     """Reference: megakernels/demos/latency/scheduler.py:235-267."""
+    if options is not None and options.balance:
+        from megakernels_b200.demos.latency.balanced import make_balanced_dag
+
+        assert stop_after_op is None, "the balanced builder emits whole layers"
+        return make_balanced_dag(globs, options, layer_limit)
     nodes: list[DAG_Node] = []
     nlayers = globs.num_hidden_layers if layer_limit is None else layer_limit
     last_outputs: list[DAG_Node] = []

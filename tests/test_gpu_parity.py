@@ -255,3 +255,20 @@ def test_greedy_generation_matches_oracle():
             assert got[i] == want, f"token {i}: {got[i]} vs {want}"
         if i + 1 < ntok:
             logits = ref.decode_token(got[i], prompt.numel() + i)
+
+
+@pytest.mark.parametrize("shape", ["1b", "8b"])
+def test_balanced_schedule_matches_oracle(shape):
+    """The timeline-model builder (pinned SMs, overlapping up/gate and down-proj)."""
+    cfg = small_1b() if shape == "1b" else small_8b()
+    opts = LatencyScheduleOptions(num_attention_partitions=3, coalesce_o_proj=True, balance=True)
+    cpu_model, cpu_sched, gpu_model, gpu_sched = make_pair(cfg, 300, 280, options=opts, sched="hint")
+    embed = cpu_model.model.embed_tokens.embed_tokens.weight
+    for i, tok in enumerate(seeded_tokens(cfg.vocab_size, 2)):
+        pos = 280 + i
+        run_cpu_step(cpu_model, cpu_sched, embed[tok], pos)
+        st = run_gpu_step(gpu_sched, embed[tok], pos)
+        assert st.code == 0
+        compare_globals(gpu_sched.globs, cpu_sched.globs, pos)
+        assert_logits_parity(gpu_sched.globs.logits, cpu_sched.globs.logits, f"pos {pos}")
+        assert torch.equal(gpu_sched.globs.barriers.cpu(), cpu_sched.globs.barriers)
