@@ -382,6 +382,11 @@ def run_ours(args):
         host_out = torch.empty(1, dtype=torch.long).pin_memory()
         dev_in = torch.empty(1, 1, dtype=torch.long, device=device)
         pos0 = prefill + W  # re-decode the same positions: same work per step
+        if not use_graph:
+            # the public generator replays the whole step (embedding row, counter reset, megakernel,
+            # argmax) as one CUDA graph; the device-timed loop above stays eager so that each
+            # megakernel launch can be bracketed by events
+            gen.enable_cuda_graph(warmup_pos=prefill)
         for i in range(3):
             host_in[0] = ids[W + i]
             dev_in.copy_(host_in.view(1, 1), non_blocking=True)
@@ -434,6 +439,7 @@ def run_ours(args):
                             + (f", tensor parallel over {world} GPUs (NCCL all-reduce after o-proj and down-proj)" if tp
                                else (f", {world} independent replicas" if world > 1 else "")),
                 "launch": "cuda graph replay" if use_graph else "eager",
+                "e2e_launch": "cuda graph replay of the whole step",
                 "inputs": "larger than L2 (weights re-streamed from HBM every step)",
                 "sched": args.sched,
                 **info,

@@ -60,15 +60,19 @@ struct DeviceState {
     std::vector<KvMapEntry> maps;
 };
 
-// L2 look-ahead of the loader in 32 KiB stages per SM; MKB_L2_WINDOW_KB overrides (0 disables).
-int l2_window_from_env() {
-    const char* e = getenv("MKB_L2_WINDOW_KB");
-    int kb = e ? atoi(e) : 128;
+// L2 look-ahead of the loader beyond the ring, in 32 KiB stages per SM.  MKB_L2_WINDOW_KB is the
+// depth while the consumers drain the ring (0 disables), MKB_L2_STALL_WINDOW_KB the depth while
+// they sit in a barrier wait, when HBM would otherwise idle.  Measured on the 8B shape: a deep
+// steady window re-reads from DRAM (L2 evictions), a deep stall window does not.
+int l2_window_from_env(const char* name, int default_kb) {
+    const char* e = getenv(name);
+    int kb = e ? atoi(e) : default_kb;
     if (kb < 0) kb = 0;
     if (kb > 4096) kb = 4096;
     return kb == 0 ? 0 : kNumStages + kb * 1024 / kStageBytes;
 }
-const int g_l2_window_stages = l2_window_from_env();
+const int g_l2_window_stages = l2_window_from_env("MKB_L2_WINDOW_KB", 64);
+const int g_l2_stall_window_stages = l2_window_from_env("MKB_L2_STALL_WINDOW_KB", 1024);
 
 std::mutex g_mutex;
 DeviceState g_devices[64];
@@ -305,6 +309,8 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     const unsigned ms = g->wait_timeout_ms ? g->wait_timeout_ms : 2000u;
     p.timeout_ns = (unsigned long long)ms * 1000000ull;
     p.l2_window_stages = g_l2_window_stages;
+    p.l2_stall_window_stages = g_l2_stall_window_stages > g_l2_window_stages ? g_l2_stall_window_stages
+                                                                             : g_l2_window_stages;
     p.poll_sleep_ns = 20;
 
     rc = kv_tensor_map(ds, g->k_cache, p.D, p.Hkv, p.T, p.L * p.B, &p.k_map);

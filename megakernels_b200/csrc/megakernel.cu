@@ -416,7 +416,10 @@ __device__ void loader_main(Ctx c) {
         if (!mbar_try_wait(c.empty_bar(slot), parity)) {
             // ring full: use the time to pull upcoming weights into L2, where the
             // stalls of this SM's consumers cannot stop HBM from streaming
-            if (ahead_more && (int)(ahead_stage - stage) < p.l2_window_stages) {
+            // while the consumers sit in a barrier wait the ring cannot drain, so the
+            // look-ahead may run deeper than in steady state
+            const int window = c.cta_abort[4] ? p.l2_stall_window_stages : p.l2_window_stages;
+            if (ahead_more && (int)(ahead_stage - stage) < window) {
                 if (ahead_stage < stage + kNumStages) {
                     // skip what the ring already holds or is about to receive
                     ahead_more = ahead.next(p, queue, da);
@@ -667,7 +670,11 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     volatile int* verdict = verdict_word(c, cs);
     if (threadIdx.x == 0) {
         bool ok = !*c.cta_abort;
-        if (ok && needed) ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
+        if (ok && needed) {
+            c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
+            ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
+            c.cta_abort[4] = 0;
+        }
         rec(c, MKB_T_CONSUMER_WAIT_DONE);
         *verdict = ok ? 1 : 0;
     }

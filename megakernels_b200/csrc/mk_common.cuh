@@ -93,6 +93,7 @@ struct KParams {
     unsigned long long timeout_ns;
     int poll_sleep_ns;     // back-off between polls of a barrier counter
     int l2_window_stages;  // how many ring stages the loader may prefetch into L2 ahead of the ring
+    int l2_stall_window_stages;  // the same while this SM's consumers wait on a barrier counter
     // TMA descriptors of the KV cache, 4-D [D, Hkv, T, L*B], box {D, 1, TS, 1}
     CUtensorMap k_map, v_map;
     // weight matrices as 4-D [64, rows, K/64, L] with the 128-byte swizzle; one box is a ring
