@@ -71,6 +71,10 @@ def parse_args():
                     help="experiment: preset all barrier counters (waits pass at once; results are garbage)")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="replay one captured decode step per token instead of launching eagerly")
+    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
+                    help="tensor-parallel workloads: all-reduce inside the kernel over peer memory "
+                         "(one launch per token) or NCCL between 2L+1 launches")
+    ap.add_argument("--tp-chunks", type=int, default=0, help="chunks per in-kernel all-reduce (0 = TP degree)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -250,7 +254,7 @@ def build_engine(args, device, tp_size=1, tp_rank=0, group=None):
         pick_num_attention_partitions,
     )
     from megakernels_b200.dispatch import make_mk_interpreter, make_schedule_builder
-    from megakernels_b200.generators import MK_Generator, TP_MK_Generator
+    from megakernels_b200.generators import MK_Generator, TP_MK_Generator, TP_Peer_MK_Generator
     from megakernels_b200.llama import LlamaForCausalLM
     from megakernels_b200.model_types import ExtraModelConfig
     from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
@@ -268,15 +272,21 @@ def build_engine(args, device, tp_size=1, tp_rank=0, group=None):
         prefill, args.steps + args.warmup, device, model.num_kv_heads(), min_chunk_size=128
     )
     balance = args.balance
+    peer = tp_size > 1 and args.tp_exchange == "peer"
     options = LatencyScheduleOptions(
-        num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj, balance=balance
+        num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj, balance=balance,
+        tp_all_reduce_chunks=(args.tp_chunks or tp_size) if peer else 0,
     )
     if balance:
         args.sched = "hint"
     schedule = make_schedule_builder("latency", options).build(model)
     schedule.globs.pos_id = prefill
     interp = make_mk_interpreter("latency")
-    if tp_size > 1:
+    if peer:
+        tensorize_instructions(schedule.globs, assign_to_sms(args.sched, schedule=schedule))
+        generator = TP_Peer_MK_Generator(model, interp, schedule, group=group)
+        launches_per_step = 1
+    elif tp_size > 1:
         generator = TP_MK_Generator(model, interp, schedule, group=group, sched=args.sched)
         launches_per_step = len(generator.segments)
     else:
@@ -317,7 +327,8 @@ def run_ours(args):
     K, W = args.steps, args.warmup
     ids = torch.randint(0, cfg.vocab_size, (W + K,), generator=torch.Generator().manual_seed(3))
     ids_dev = ids.to(device).view(-1, 1, 1)
-    use_graph = args.cuda_graph or tp  # 2L+1 launches per token are launch-bound without a graph
+    # 2L+1 launches per token (NCCL exchange) are launch-bound without a graph
+    use_graph = args.cuda_graph or (tp and args.tp_exchange == "nccl")
 
     # ---- warm-up ----------------------------------------------------------- #
     for i in range(min(W, 3)):
@@ -358,6 +369,8 @@ def run_ours(args):
             gen.last_call = interp.interpret(globs)
             e1.record()
             launch_events.append((e0, e1))
+            if globs.tp is not None:
+                globs.tp.epoch_device.add_(1)  # as TP_Peer_MK_Generator._step does
             torch.argmax(globs.logits, dim=-1)
     end.record()
     torch.cuda.profiler.stop()
@@ -436,7 +449,9 @@ def run_ours(args):
             "config": {
                 "workload": f"{args.workload} batch-1 decode, {cfg.num_hidden_layers} layers, KV prefill {prefill}, "
                             f"{K} teacher-forced steps"
-                            + (f", tensor parallel over {world} GPUs (NCCL all-reduce after o-proj and down-proj)" if tp
+                            + (f", tensor parallel over {world} GPUs ("
+                               + ("in-kernel all-reduce over peer memory" if args.tp_exchange == "peer" else "NCCL all-reduce")
+                               + " after o-proj and down-proj)" if tp
                                else (f", {world} independent replicas" if world > 1 else "")),
                 "launch": "cuda graph replay" if use_graph else "eager",
                 "e2e_launch": "cuda graph replay of the whole step",

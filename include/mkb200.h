@@ -16,13 +16,14 @@
 #ifndef MKB200_H
 #define MKB200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
 extern "C" {
 #endif
 
-#define MKB_ABI_VERSION 1
+#define MKB_ABI_VERSION 2
 
 /* instruction encoding (megakernels/scheduler.py:13-14) */
 #define MKB_INTS_PER_INSTRUCTION 32
@@ -40,6 +41,10 @@ enum {
     MKB_OP_RMS_UPGATE_SILU = 5,
     MKB_OP_DOWN_PROJ_RESIDUAL = 6,
     MKB_OP_RMS_LM_HEAD = 7,
+    /* No counterpart in the reference (its kernel is single-GPU): one chunk of the
+     * tensor-parallel all-reduce of the residual stream, see MkbTensorParallel.
+     * words: [8, layer, which (0 after o-proj, 1 after down-proj), chunk, num_chunks] */
+    MKB_OP_TP_ALL_REDUCE = 8,
 };
 
 /* MkbGlobals.flags */
@@ -68,6 +73,46 @@ enum {
     MKB_ERR_BAD_OPCODE = 4,       /* the device met an opcode it does not know */
     MKB_ERR_UNSUPPORTED = 5,      /* valid request this build cannot run */
 };
+
+/*
+ * Tensor parallelism inside the kernel (no counterpart in the reference, which shards
+ * only its torch model, megakernels/llama.py:665-691).  With `size` > 1 every rank runs
+ * the same launch on its shard and the o-proj / down-proj partial sums are exchanged by
+ * MKB_OP_TP_ALL_REDUCE instructions over peer memory instead of a library collective:
+ *
+ *   1. o-proj / down-proj store their fp32 block sums into `partial[slice][H]` (local)
+ *      instead of adding them to hidden_states;
+ *   2. the instruction for chunk c (elements [c*H/n, (c+1)*H/n), n = num_chunks) waits
+ *      for the local projection, sums the slices and writes the result into row `rank` of
+ *      the receive buffer of the chunk's owner (rank c % size), then bumps the owner's
+ *      arrival counter with a system-scope release;
+ *   3. on the owner the same instruction waits for `size` arrivals, adds the rows in rank
+ *      order to hidden_states in fp32, rounds to bf16 once, writes the chunk into the
+ *      hidden_states of EVERY rank and bumps each rank's completion counter;
+ *   4. the following RMSNorm instruction waits for num_chunks completions.
+ *
+ * All ranks therefore hold bit-identical residual streams.  The counters are never
+ * zeroed: they count up by a fixed amount per launch and waits compare against
+ * (*epoch_device + 1) * amount, so a fast rank can never race a slow rank's reset.
+ * `*epoch_device` must be the number of launches completed so far on this rank group
+ * (same value on all ranks; the caller increments it after every launch).
+ * Every peer pointer must be valid on THIS device (cudaIpcOpenMemHandle or an
+ * equivalent mapping with peer access enabled); entry `rank` is the local buffer.
+ */
+#define MKB_MAX_TP 8
+#define MKB_TP_MAX_CHUNKS 32
+typedef struct MkbTensorParallel {
+    int32_t size;        /* ranks; 0 or 1 disables everything below */
+    int32_t rank;
+    int32_t num_chunks;  /* chunks per all-reduce: a multiple of size, <= MKB_TP_MAX_CHUNKS */
+    int32_t reserved;
+    void *hidden_peers[MKB_MAX_TP];      /* bf16 [H]: hidden_states of every rank */
+    float *recv_peers[MKB_MAX_TP];       /* fp32 [size][H]: receive buffer of every rank */
+    int32_t *counters_peers[MKB_MAX_TP]; /* int32 [L][2][1 + MKB_TP_MAX_CHUNKS]: word 0 counts
+                                            completed chunks, word 1 + c arrivals for chunk c */
+    float *partial;                      /* local fp32 [max(Hq*D, I) / R][H] */
+    const int32_t *epoch_device;         /* launches completed so far */
+} MkbTensorParallel;
 
 /*
  * The kernel's argument set.  Replaces `globals_t` of the reference
@@ -143,6 +188,8 @@ typedef struct MkbGlobals {
                                      residual add; 0 means 1.  Tensor-parallel ranks set it to the
                                      TP degree and average their residual streams afterwards */
 
+    MkbTensorParallel tp;         /* in-kernel tensor-parallel all-reduce; tp.size <= 1: off */
+
     /* ---- options ---- */
     uint32_t flags;           /* MKB_FLAG_* */
     uint32_t wait_timeout_ms; /* device-side wait budget; 0 selects the default (2000 ms) */
@@ -211,6 +258,20 @@ int mkb_validate_instructions(const MkbGlobals *g, const int32_t *host_instructi
  */
 #define MKB_NO_ALLOC_SCRATCH_BYTES (1u << 20)
 int mkb_launch_no_alloc(const MkbGlobals *g, void *cuda_stream);
+
+/*
+ * Peer-visible device memory for MkbTensorParallel (no counterpart in the reference).
+ * mkb_peer_alloc: cudaMalloc + zero-fill of `bytes` on the current device and an opaque
+ * 64-byte handle another process can open; mkb_peer_open maps such a handle into the
+ * calling process for the current device (peer access is enabled on demand);
+ * mkb_peer_close / mkb_peer_free undo them.  The handle travels by whatever channel the
+ * host has (a torch.distributed all-gather in this repository).
+ */
+#define MKB_PEER_HANDLE_BYTES 64
+int mkb_peer_alloc(size_t bytes, void **device_ptr, unsigned char handle[MKB_PEER_HANDLE_BYTES]);
+int mkb_peer_open(const unsigned char handle[MKB_PEER_HANDLE_BYTES], void **device_ptr);
+int mkb_peer_close(void *device_ptr);
+int mkb_peer_free(void *device_ptr);
 
 /* Message of the last host-side error raised on the calling thread. */
 const char *mkb_last_error(void);

@@ -219,6 +219,26 @@ int validate(const MkbGlobals* g) {
     if (!g->pos_id_device && (g->pos_id < 0 || g->pos_id >= g->kv_max_len))
         return fail(MKB_ERR_INVALID_ARGUMENT, "pos_id %d outside the KV cache length %d", g->pos_id, g->kv_max_len);
     if (g->max_partials < 1) return fail(MKB_ERR_INVALID_ARGUMENT, "max_partials must be >= 1");
+    const MkbTensorParallel& tp = g->tp;
+    if (tp.size > 1) {
+        if (tp.size > MKB_MAX_TP || tp.rank < 0 || tp.rank >= tp.size)
+            return fail(MKB_ERR_INVALID_ARGUMENT, "tp: size %d (max %d), rank %d", tp.size, MKB_MAX_TP, tp.rank);
+        if (tp.num_chunks < tp.size || tp.num_chunks > MKB_TP_MAX_CHUNKS || tp.num_chunks % tp.size != 0 ||
+            H % (2 * tp.num_chunks) != 0)
+            return fail(MKB_ERR_INVALID_ARGUMENT,
+                        "tp: num_chunks %d must be a multiple of size %d, at most %d, and divide H/2",
+                        tp.num_chunks, tp.size, MKB_TP_MAX_CHUNKS);
+        for (int r = 0; r < tp.size; ++r) {
+            if (!tp.hidden_peers[r] || !tp.recv_peers[r] || !tp.counters_peers[r])
+                return fail(MKB_ERR_INVALID_ARGUMENT, "tp: peer pointers of rank %d are NULL", r);
+            if (!aligned16(tp.hidden_peers[r]) || !aligned16(tp.recv_peers[r]) || !aligned16(tp.counters_peers[r]))
+                return fail(MKB_ERR_INVALID_ARGUMENT, "tp: peer pointers of rank %d must be 16-byte aligned", r);
+        }
+        if (tp.hidden_peers[tp.rank] != g->hidden_states)
+            return fail(MKB_ERR_INVALID_ARGUMENT, "tp: hidden_peers[rank] must be hidden_states");
+        if (!tp.partial || !aligned16(tp.partial)) return fail(MKB_ERR_INVALID_ARGUMENT, "tp: partial buffer is NULL or unaligned");
+        if (!tp.epoch_device) return fail(MKB_ERR_INVALID_ARGUMENT, "tp: epoch_device is NULL");
+    }
     return MKB_OK;
 }
 
@@ -298,6 +318,18 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     p.pos_id = g->pos_id;
     p.pos_id_ptr = g->pos_id_device;
     p.residual_scale = g->residual_scale > 0.f ? g->residual_scale : 1.f;
+    if (g->tp.size > 1) {
+        p.tp_size = g->tp.size;
+        p.tp_rank = g->tp.rank;
+        p.tp_chunks = g->tp.num_chunks;
+        p.tp_epoch_ptr = g->tp.epoch_device;
+        p.tp_partial = g->tp.partial;
+        for (int r = 0; r < g->tp.size; ++r) {
+            p.tp_hidden[r] = (__nv_bfloat16*)g->tp.hidden_peers[r];
+            p.tp_recv[r] = g->tp.recv_peers[r];
+            p.tp_counters[r] = g->tp.counters_peers[r];
+        }
+    }
     p.attn_scale_log2e = g->attn_scale * 1.4426950408889634f;
     p.rms_eps = g->rms_norm_eps;
     p.skip_attn_reduction = g->skip_attn_reduction;
@@ -446,6 +478,12 @@ int mkb_validate_instructions(const MkbGlobals* g, const int32_t* host_instructi
                     break;
                 case MKB_OP_RMS_LM_HEAD:
                     if (!range_ok(w[1], w[2], g->vocab_size / 16)) return bad("block range outside the vocabulary");
+                    break;
+                case MKB_OP_TP_ALL_REDUCE:
+                    if (g->tp.size <= 1) return bad("all-reduce instruction without tensor parallelism");
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (w[2] < 0 || w[2] > 1) return bad("which must be 0 (o-proj) or 1 (down-proj)");
+                    if (w[4] != g->tp.num_chunks || w[3] < 0 || w[3] >= w[4]) return bad("chunk outside tp.num_chunks");
                     break;
                 default:
                     return bad("unknown opcode");

@@ -4,13 +4,14 @@
 // shape-generic, hand-written sm_100a code:
 //
 //   loader warp   - walks the queue ahead of everybody else and streams every
-//                   weight block (cp.async.bulk) and KV tile (cp.async.bulk.tensor)
-//                   into a ring of 32 KiB stages; it never looks at a barrier,
-//                   because weights and old KV positions depend on nothing.
-//   16 consumer   - wait for the instruction's global barrier, load (and
-//   warps           RMS-normalise) the activation vector into registers, then
-//                   multiply ring stages against it with fp32 FMAs; each warp
-//                   owns a column slice, rows are reduced with warp shuffles.
+//                   weight block and KV tile (one tiled cp.async.bulk.tensor per
+//                   stage) into a ring of 32 KiB stages; it never looks at a
+//                   barrier, because weights and old KV positions depend on nothing.
+//   16 consumer   - wait for the instruction's global barrier, park the (RMS-
+//   warps           normalised) activation vector in shared memory, then multiply
+//                   ring stages against it with mma.sync (weights are the A operand,
+//                   the activation vector column 0 of B); each warp owns a column
+//                   slice of the stage.
 //   storer warp   - sums the per-warp partials of a 16-row block, applies the
 //                   op's epilogue (RoPE + KV append, SiLU*up, residual add,
 //                   logits) and signals the next op's barrier counter.
@@ -26,6 +27,7 @@ struct Ctx {
     uint32_t base;            // shared-window address of the aligned smem base
     volatile int* cta_abort;  // generic pointer to the CTA-wide abort word
     int pos;                  // position of the token being decoded
+    int epoch;                // launches completed before this one (tensor-parallel counters)
     int instr;                // instruction index being executed (for reports)
     int opcode;
     int role;
@@ -122,12 +124,13 @@ __device__ __forceinline__ bool warp_mbar_wait(const Ctx& c, uint32_t bar, uint3
 }
 
 // Bounded wait for `*addr >= threshold` with acquire semantics.
+// `sys`: the counter is bumped by other GPUs (system-scope acquire).
 __device__ __noinline__ bool wait_counter(const Ctx& c, const int* addr, int threshold, int layer,
-                                          int row, int slot) {
+                                          int row, int slot, bool sys = false) {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
-        int v = ld_acquire_gpu(addr);
+        int v = sys ? ld_acquire_sys(addr) : ld_acquire_gpu(addr);
         if (v >= threshold) return true;
         if ((++spins & 63u) == 0) {
             if (*c.cta_abort) return false;
@@ -664,15 +667,15 @@ __device__ __forceinline__ void rms_activation(const Ctx& c, const RmsPrefetch& 
 
 // Consumer thread 0 waits for a counter; the verdict reaches all 512 consumer
 // threads through shared memory so that they leave the instruction together.
-__device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerState& cs, int layer,
-                                                       int row, int slot, int threshold,
-                                                       bool needed) {
+__device__ __forceinline__ bool consumers_wait_addr(const Ctx& c, ConsumerState& cs, const int* addr,
+                                                    int threshold, bool sys, int layer, int row,
+                                                    int slot, bool needed) {
     volatile int* verdict = verdict_word(c, cs);
     if (threadIdx.x == 0) {
         bool ok = !*c.cta_abort;
         if (ok && needed) {
             c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
-            ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
+            ok = wait_counter(c, addr, threshold, layer, row, slot, sys);
             c.cta_abort[4] = 0;
         }
         rec(c, MKB_T_CONSUMER_WAIT_DONE);
@@ -681,6 +684,30 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     consumer_sync();
     return *verdict != 0;
 }
+__device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerState& cs, int layer,
+                                                       int row, int slot, int threshold,
+                                                       bool needed) {
+    return consumers_wait_addr(c, cs, bar_addr(*c.p, layer, row, slot), threshold, false, layer, row,
+                               slot, needed);
+}
+
+// Tensor-parallel counters of rank r: word 0 of (layer, which) counts chunks whose reduced
+// values have reached this rank's hidden_states, word 1 + chunk the ranks whose partial sums
+// have reached this rank's receive buffer.  They only ever count up (see MkbTensorParallel).
+__device__ __forceinline__ int* tp_counter(const KParams& p, int r, int layer, int which, int word) {
+    return p.tp_counters[r] + ((size_t)layer * 2 + which) * (1 + MKB_TP_MAX_CHUNKS) + word;
+}
+// In tensor-parallel mode the residual stream is complete once every chunk of the
+// all-reduce after (layer, which) has been written here by its owner.
+__device__ __forceinline__ bool consumers_wait_residual(const Ctx& c, ConsumerState& cs, int layer,
+                                                        int which, int row, int threshold,
+                                                        bool needed) {
+    const KParams& p = *c.p;
+    if (p.tp_size > 1)
+        return consumers_wait_addr(c, cs, tp_counter(p, p.tp_rank, layer, which, 0),
+                                   p.tp_chunks * (c.epoch + 1), true, layer, 100 + which, 0, needed);
+    return consumers_wait_counter(c, cs, layer, row, 0, threshold, needed);
+}
 
 __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
                                                     const __nv_bfloat16* norm_w, int nblocks,
@@ -688,7 +715,8 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
                                                     bool needed) {
     RmsPrefetch pf;
     rms_prefetch(c, norm_w, pf);
-    if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
+    const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
+    if (!consumers_wait_residual(c, cs, wait_layer, which, wait_row, threshold, needed)) return false;
     rms_activation(c, pf);
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->H);
@@ -1137,6 +1165,63 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
 }
 
 // --------------------------------------------------------------------------- //
+// consumers: tensor-parallel all-reduce of one chunk of the residual stream
+// --------------------------------------------------------------------------- //
+// Reduce-scatter then all-gather over peer memory with plain stores and one counter
+// bump per peer (protocol in MkbTensorParallel).  No thread ever waits without a budget:
+// a rank that never arrives turns into MKB_ERR_DEVICE_TIMEOUT on the others.
+__device__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState& cs, const int* w) {
+    const KParams& p = *c.p;
+    const int tid = threadIdx.x;
+    const int layer = __ldg(w + 1), which = __ldg(w + 2), chunk = __ldg(w + 3), nchunks = __ldg(w + 4);
+    const int E = p.H / nchunks, e0 = chunk * E;
+    const int owner = chunk % p.tp_size;
+    const int slices = (which == 0 ? p.o_in : p.I) / p.R;
+    const int row = (which == 0 ? MKB_OP_O_PROJ_RESIDUAL : MKB_OP_DOWN_PROJ_RESIDUAL) - 1;
+    const int thr = which == 0 ? p.thr_upgate_waits_oproj : p.thr_qkv_waits_down;
+
+    // 1. this rank's projection is complete: sum its column slices, send to the owner
+    if (!consumers_wait_counter(c, cs, layer, row, 0, thr, true)) return false;
+    {
+        float* dst = p.tp_recv[owner] + (size_t)p.tp_rank * p.H + e0;
+        for (int e = tid * 2; e < E; e += kConsumerThreads * 2) {
+            float sx = 0.f, sy = 0.f;
+            for (int sl = 0; sl < slices; ++sl) {
+                const uint2 v = ldv_cg_v2(p.tp_partial + (size_t)sl * p.H + e0 + e);
+                sx += __uint_as_float(v.x);
+                sy += __uint_as_float(v.y);
+            }
+            st_global_v2_f32(dst + e, sx, sy);
+        }
+    }
+    consumer_sync();
+    if (tid == 0) red_release_sys_add(tp_counter(p, owner, layer, which, 1 + chunk), 1);
+    if (owner != p.tp_rank) return true;
+
+    // 2. owner: all ranks' sums have arrived; reduce in rank order, round once, broadcast
+    if (!consumers_wait_addr(c, cs, tp_counter(p, p.tp_rank, layer, which, 1 + chunk),
+                             p.tp_size * (c.epoch + 1), true, layer, 200 + which, chunk, true))
+        return false;
+    {
+        const float* src = p.tp_recv[p.tp_rank] + e0;
+        for (int e = tid * 2; e < E; e += kConsumerThreads * 2) {
+            float sx = 0.f, sy = 0.f;
+            for (int r = 0; r < p.tp_size; ++r) {
+                const uint2 v = ldv_cg_v2(src + (size_t)r * p.H + e);
+                sx += __uint_as_float(v.x);
+                sy += __uint_as_float(v.y);
+            }
+            const uint32_t h = ldv_cg_u32(p.hidden + e0 + e);
+            const uint32_t out = pack_bf16x2(bf16_lo(h) + sx, bf16_hi(h) + sy);
+            for (int r = 0; r < p.tp_size; ++r) st_global_u32(p.tp_hidden[r] + e0 + e, out);
+        }
+    }
+    consumer_sync();
+    if (tid < p.tp_size) red_release_sys_add(tp_counter(p, tid, layer, which, 0), 1);
+    return true;
+}
+
+// --------------------------------------------------------------------------- //
 // consumer dispatch
 // --------------------------------------------------------------------------- //
 __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
@@ -1204,6 +1289,12 @@ __device__ void consumer_main(Ctx c) {
                 if (p.D == 64) ok = consumer_attn_reduction<64>(c, cs, w);
                 else ok = consumer_attn_reduction<128>(c, cs, w);
                 break;
+            case MKB_OP_TP_ALL_REDUCE:
+                if (p.tp_size > 1) {
+                    ok = consumer_tp_all_reduce(c, cs, w);
+                    break;
+                }
+                [[fallthrough]];
             default:
                 if (threadIdx.x == 0) report_error(c, MKB_ERR_BAD_OPCODE, op, 0, 0, 0);
                 ok = false;
@@ -1330,13 +1421,23 @@ __device__ void storer_main(Ctx c) {
             case MKB_OP_O_PROJ_RESIDUAL:
             case MKB_OP_DOWN_PROJ_RESIDUAL: {
                 const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
-                for (int b = sb; b < eb; ++b) {
-                    // residual_scale is the tensor-parallel degree: ranks then average their
-                    // copies of the residual stream, which yields h + sum of the partials
-                    const float v = storer_take_block(c, ss, lane, kr_partials) * p.residual_scale;
-                    const float hi = __shfl_down_sync(0xffffffffu, v, 1);
-                    if (lane < 16 && (lane & 1) == 0)
-                        red_add_bf16x2(p.hidden + b * kBlockRows + row, pack_bf16x2(v, hi));
+                if (p.tp_size > 1) {
+                    // in-kernel tensor parallelism: the fp32 block sums of this column slice
+                    // go to the rank's partial buffer; MKB_OP_TP_ALL_REDUCE adds them up
+                    float* part = p.tp_partial + (size_t)__ldg(w + 4) * p.H;
+                    for (int b = sb; b < eb; ++b) {
+                        const float v = storer_take_block(c, ss, lane, kr_partials);
+                        if (lane < 16) part[b * kBlockRows + row] = v;
+                    }
+                } else {
+                    for (int b = sb; b < eb; ++b) {
+                        // residual_scale is the tensor-parallel degree when the host averages the
+                        // ranks' residual streams between launches (h + sum of the partials)
+                        const float v = storer_take_block(c, ss, lane, kr_partials) * p.residual_scale;
+                        const float hi = __shfl_down_sync(0xffffffffu, v, 1);
+                        if (lane < 16 && (lane & 1) == 0)
+                            red_add_bf16x2(p.hidden + b * kBlockRows + row, pack_bf16x2(v, hi));
+                    }
                 }
                 storer_signal(ss, lane, bar_addr(p, layer, op - 1, 0), eb - sb);
                 storer_flush(ss, lane);
@@ -1389,6 +1490,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
     c.opcode = -1;
     c.role = -1;
     c.pos = p.pos_id_ptr ? __ldg(p.pos_id_ptr) : p.pos_id;
+    c.epoch = (p.tp_size > 1 && p.tp_epoch_ptr) ? __ldg(p.tp_epoch_ptr) : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kNumStages; ++s) {

@@ -84,6 +84,13 @@ struct KParams {
     float attn_scale_log2e;  // attn_scale * log2(e)
     float rms_eps;
     int skip_attn_reduction;
+    // in-kernel tensor-parallel all-reduce (MkbTensorParallel); tp_size <= 1: off
+    int tp_size, tp_rank, tp_chunks;
+    const int* tp_epoch_ptr;
+    __nv_bfloat16* tp_hidden[MKB_MAX_TP];
+    float* tp_recv[MKB_MAX_TP];
+    int* tp_counters[MKB_MAX_TP];
+    float* tp_partial;
     // barrier thresholds, derived on the host from the shapes
     int thr_qkv_waits_down;     // (H/16) * (I/R)
     int thr_attn_waits_qkv;     // D/16
@@ -157,6 +164,32 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+// system scope: the counter lives in (or is written from) another GPU's memory
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+    asm volatile("fence.acq_rel.sys;\n\tred.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// ordered variants (volatile, memory clobber) for data another GPU wrote or will read
+__device__ __forceinline__ uint2 ldv_cg_v2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ldv_cg_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_global_v2_f32(float* p, float a, float b) {
+    asm volatile("st.global.v2.f32 [%0], {%1,%2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void st_global_u32(void* p, uint32_t v) {
+    asm volatile("st.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
     asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

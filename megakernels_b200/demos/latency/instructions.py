@@ -14,7 +14,12 @@ Reference: megakernels/demos/latency/instructions.py.  Word layouts (after
  5    LayerNormDoubleMatVecSiLU       [5, layer, n, blk_0..blk_{n-1}]
  6    DownProjResidual                [6, layer, start_blk, end_blk, red_blk]
  7    RMS_LM_Head                     [7, start_blk, end_blk]
+ 8    TP_AllReduce                    [8, layer, which, chunk, num_chunks]
 ====  ==============================  ==========================================
+
+Opcode 8 has no counterpart in the reference: it is one chunk of the in-kernel
+tensor-parallel all-reduce of the residual stream (``which`` 0: after the
+o-proj, 1: after the down-proj), only scheduled when ``globs.tp`` is set.
 
 A block is 16 output rows.  ``red_blk`` selects the input-column slice
 ``[red_blk * matvec_reduction_size, (red_blk + 1) * matvec_reduction_size)``.
@@ -207,6 +212,36 @@ class DownProjResidual(MatVecAdd):
     def cost(self, globs: Globals):
         n = self.end_block_idx - self.start_block_idx
         return n * globs.down_proj_block_size * globs.matvec_reduction_size
+
+
+@dataclass
+class TP_AllReduce(Instruction):
+    """One chunk of the all-reduce of the row-split projections' partial sums.
+
+    Sums this rank's column slices for elements ``[chunk * H / num_chunks, ...)``,
+    sends them to rank ``chunk % tp.size``; that rank adds all ranks' sums to the
+    residual stream in fp32, rounds to bf16 once and writes the chunk into every
+    rank's ``hidden_states``.
+    """
+
+    layer_idx: int
+    which: int  # 0: after o-proj, 1: after down-proj
+    chunk_idx: int
+    num_chunks: int
+
+    @classmethod
+    def opcode(cls) -> int:
+        return 8
+
+    @classmethod
+    def prev_opcode(cls) -> int:
+        raise NotImplementedError("depends on `which`")
+
+    def producer_opcode(self) -> int:
+        return O_ProjResidual.opcode() if self.which == 0 else DownProjResidual.opcode()
+
+    def cost(self, globs: Globals):
+        return globs.hidden_size // self.num_chunks * 64
 
 
 @dataclass

@@ -53,6 +53,7 @@ def interpret_with_mk(globs: Globals, mk_func, stream=None, **kwargs):
         matvec_reduction_size=globs.matvec_reduction_size,
         residual_scale=globs.residual_scale,
         pos_id_device=globs.pos_id_device,
+        tp=globs.tp,
         **kwargs,
     )
 

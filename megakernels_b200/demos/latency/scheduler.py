@@ -10,7 +10,10 @@ word.  Differences are generalisations the reference does not have:
   instructions plus one terminal ``AttentionReduction`` per group of 4 Q heads
   (the reference asserts ``skip_attn_reduction``, latency/scheduler.py:276-277);
 * ``coalesce_o_proj`` emits one block-range O-proj instruction per SM instead
-  of one per 16-row block (latency/scheduler.py:344-354).
+  of one per 16-row block (latency/scheduler.py:344-354);
+* ``tp_all_reduce_chunks`` (tensor-parallel shards only) emits ``TP_AllReduce``
+  instructions after every o-proj and down-proj group, so that the ranks
+  exchange their partial sums inside the kernel and a token stays one launch.
 """
 
 from __future__ import annotations
@@ -30,8 +33,9 @@ from megakernels_b200.demos.latency.instructions import (
     O_ProjResidual,
     PartialAttention,
     RMS_LM_Head,
+    TP_AllReduce,
 )
-from megakernels_b200.instructions import NoOp
+from megakernels_b200.instructions import NoOp, TensorParallelState
 from megakernels_b200.scheduler import DAG_Node, ScheduleBuilder
 from megakernels_b200.utils import assert_div, get_sm_count
 
@@ -47,6 +51,10 @@ class LatencyScheduleOptions:
     # block split and SM mapping from a per-SM timeline model (demos/latency/balanced.py);
     # the resulting stream must be assigned with assign_to_sms("hint", ...)
     balance: bool = False
+    # > 0 on a tensor-parallel shard: all-reduce the residual stream inside the kernel,
+    # split into this many chunks (a multiple of the TP degree); 0 leaves the exchange
+    # to the host (generators.TP_MK_Generator cuts the stream and calls NCCL)
+    tp_all_reduce_chunks: int = 0
 
 
 def pick_num_attention_partitions(
@@ -310,6 +318,10 @@ def make_dag_layer(
     new_nodes.extend(o_nodes)
     if stop_after_op == "oproj":
         return new_nodes, o_nodes
+    if globs.tp is not None:
+        n = globs.tp.num_chunks
+        o_nodes = [DAG_Node(TP_AllReduce(layer_idx, 0, c, n), o_nodes) for c in range(n)]
+        new_nodes.extend(o_nodes)
 
     upgate_nodes = [DAG_Node(ins, o_nodes) for ins in schedule_upgate(globs, layer_idx)]
     new_nodes.extend(upgate_nodes)
@@ -320,6 +332,10 @@ def make_dag_layer(
     new_nodes.extend(down_nodes)
     if stop_after_op == "downproj":
         return new_nodes, down_nodes
+    if globs.tp is not None:
+        n = globs.tp.num_chunks
+        down_nodes = [DAG_Node(TP_AllReduce(layer_idx, 1, c, n), down_nodes) for c in range(n)]
+        new_nodes.extend(down_nodes)
 
     assert stop_after_op is None
     return new_nodes, down_nodes
@@ -372,7 +388,12 @@ class LatencyScheduleBuilder(ScheduleBuilder):
 
     def make_globals(self, model):  # type: ignore[override]
         skip = self.options.num_attention_partitions == 1
-        return make_globals(model, skip_attn_reduction=skip)
+        globs = make_globals(model, skip_attn_reduction=skip)
+        extra = model.extra_config
+        if self.options.tp_all_reduce_chunks and extra.tp_size > 1:
+            assert not self.options.balance, "the balanced builder has no all-reduce instructions"
+            globs.tp = TensorParallelState(extra.tp_size, extra.tp_rank, self.options.tp_all_reduce_chunks)
+        return globs
 
     def with_new_globals(self, schedule, model):  # type: ignore[override]
         from dataclasses import replace

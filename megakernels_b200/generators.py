@@ -249,3 +249,41 @@ class TP_MK_Generator(MK_Generator):
             return self._replay(input_ids, pos_id)
         self.schedule.globs.pos_id = pos_id
         return self._step(input_ids)
+
+
+class TP_Peer_MK_Generator(MK_Generator):
+    """Tensor-parallel decoding with the all-reduce inside the kernel: one launch per token.
+
+    No counterpart in the reference.  The schedule must have been built with
+    ``LatencyScheduleOptions(tp_all_reduce_chunks=n)`` on a model shard
+    (``ExtraModelConfig(tp_size, tp_rank)``), which puts ``TP_AllReduce``
+    instructions after every o-proj and down-proj group; this class attaches the
+    peer-mapped buffers (``megakernels_b200.peer.connect``, a collective over
+    ``group``) and keeps the launch counter the device-side protocol compares
+    its arrival counters against.  All ranks must call ``run`` the same number of
+    times; the ranks' kernels wait for each other with a time budget, so a rank
+    that stops shows up as ``MegakernelError`` (device timeout) on the others.
+    """
+
+    def __init__(self, model, interpreter, schedule, group=None):
+        from megakernels_b200 import peer
+
+        super().__init__(model, interpreter, schedule)
+        self.group = group
+        self.block = peer.connect(schedule.globs, group)
+
+    def _step(self, input_ids: Tensor) -> Tensor:
+        out = super()._step(input_ids)
+        tp = self.schedule.globs.tp
+        tp.epoch_device.add_(1)  # on the launch stream: the next launch reads the new value
+        return out
+
+    def run(self, input_ids: Tensor, pos_id: int):
+        if getattr(self, "_graph", None) is not None:
+            return self._replay(input_ids, pos_id)  # the captured step includes the increment
+        self.schedule.globs.pos_id = pos_id
+        return self._step(input_ids)
+
+    def close(self):
+        self._graph = None
+        self.block.close()

@@ -16,6 +16,43 @@ from megakernels_b200.model_types import DeviceType
 from megakernels_b200.utils import get_sm_count
 
 
+TP_MAX_RANKS = 8  # MKB_MAX_TP
+TP_MAX_CHUNKS = 32  # MKB_TP_MAX_CHUNKS
+
+
+@dataclass
+class TensorParallelState:
+    """Host mirror of ``MkbTensorParallel`` (include/mkb200.h): the in-kernel all-reduce.
+
+    No counterpart in the reference, whose kernel is single-GPU.  ``size``,
+    ``rank`` and ``num_chunks`` are known when the schedule is built (the
+    builder emits one ``TP_AllReduce`` instruction per chunk after every o-proj
+    and down-proj group); the buffers are attached later by whoever owns the
+    exchange: ``megakernels_b200.peer.connect`` for GPUs (peer-mapped memory),
+    the CPU checker for its own emulation (``exchange`` callback).
+    """
+
+    size: int
+    rank: int
+    num_chunks: int
+    epoch: int = 0  # launches completed so far; mirrors ``epoch_device``
+    partial: Tensor | None = None  # fp32 [max slices, H], local
+    recv: Tensor | None = None  # fp32 [size, H], written by peers
+    counters: Tensor | None = None  # int32 [L, 2, 1 + TP_MAX_CHUNKS], written by peers, never zeroed
+    epoch_device: Tensor | None = None  # int32 [1]
+    hidden_ptrs: list[int] | None = None  # device address of hidden_states on every rank
+    recv_ptrs: list[int] | None = None
+    counter_ptrs: list[int] | None = None
+    exchange: Any = None  # CPU checker only: fp32 tensor -> sum over ranks
+
+    def __post_init__(self):
+        assert 1 < self.size <= TP_MAX_RANKS and 0 <= self.rank < self.size
+        assert self.num_chunks % self.size == 0 and self.num_chunks <= TP_MAX_CHUNKS
+
+    def owner(self, chunk: int) -> int:
+        return chunk % self.size
+
+
 @dataclass
 class BaseGlobals:
     # model parameters, stacked over layers
@@ -59,6 +96,7 @@ class BaseGlobals:
         # extensions without a counterpart in the reference globals
         self.residual_scale: float = 1.0  # tensor-parallel degree (see generators.TP_MK_Generator)
         self.pos_id_device: Tensor | None = None  # int32[1]; overrides pos_id when set
+        self.tp: TensorParallelState | None = None  # in-kernel tensor-parallel all-reduce
 
     def sm_count(self) -> int:
         return get_sm_count(self.device)

@@ -18,7 +18,10 @@ import torch
 _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libmkb200.so"
 
-MKB_ABI_VERSION = 1
+MKB_ABI_VERSION = 2
+MKB_MAX_TP = 8
+MKB_TP_MAX_CHUNKS = 32
+MKB_PEER_HANDLE_BYTES = 64
 MKB_STATUS_WORDS = 16
 MKB_FLAG_RECORD_TIMINGS = 1
 
@@ -30,6 +33,20 @@ ERROR_NAMES = {
     4: "MKB_ERR_BAD_OPCODE",
     5: "MKB_ERR_UNSUPPORTED",
 }
+
+
+class MkbTensorParallel(ctypes.Structure):
+    _fields_ = [
+        ("size", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("num_chunks", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("hidden_peers", ctypes.c_void_p * MKB_MAX_TP),
+        ("recv_peers", ctypes.c_void_p * MKB_MAX_TP),
+        ("counters_peers", ctypes.c_void_p * MKB_MAX_TP),
+        ("partial", ctypes.c_void_p),
+        ("epoch_device", ctypes.c_void_p),
+    ]
 
 
 class MkbGlobals(ctypes.Structure):
@@ -80,6 +97,7 @@ class MkbGlobals(ctypes.Structure):
         ("skip_attn_reduction", ctypes.c_int32),
         ("pos_id_device", ctypes.c_void_p),
         ("residual_scale", ctypes.c_float),
+        ("tp", MkbTensorParallel),
         ("flags", ctypes.c_uint32),
         ("wait_timeout_ms", ctypes.c_uint32),
         ("status", ctypes.c_void_p),
@@ -129,6 +147,12 @@ def load_library() -> ctypes.CDLL:
         ctypes.POINTER(MkbStatus),
     ]
     lib.mkb_sync_status.restype = ctypes.c_int
+    lib.mkb_peer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
+    lib.mkb_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.mkb_peer_close.argtypes = [ctypes.c_void_p]
+    lib.mkb_peer_free.argtypes = [ctypes.c_void_p]
+    for name in ("mkb_peer_alloc", "mkb_peer_open", "mkb_peer_close", "mkb_peer_free"):
+        getattr(lib, name).restype = ctypes.c_int
     lib.mkb_last_error.restype = ctypes.c_char_p
     for name in ("mkb_sm_count", "mkb_smem_bytes", "mkb_block_threads", "mkb_abi_version"):
         getattr(lib, name).restype = ctypes.c_int
@@ -190,6 +214,7 @@ def pack_globals(
     max_partials=None,
     pos_id_device=None,
     residual_scale=1.0,
+    tp=None,
 ) -> MkbGlobals:
     """Fill the C struct from tensors; every dimension is read off the shapes."""
     bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
@@ -276,6 +301,17 @@ def pack_globals(
     g.rms_norm_eps = float(rms_norm_eps)
     g.skip_attn_reduction = int(bool(skip_attn_reduction))
     g.residual_scale = float(residual_scale)
+    if tp is not None:
+        # megakernels_b200.instructions.TensorParallelState with its buffers attached
+        if tp.hidden_ptrs is None or tp.partial is None or tp.epoch_device is None:
+            raise ValueError("tensor-parallel state has no peer buffers attached (peer.connect)")
+        g.tp.size, g.tp.rank, g.tp.num_chunks = tp.size, tp.rank, tp.num_chunks
+        for r in range(tp.size):
+            g.tp.hidden_peers[r] = tp.hidden_ptrs[r]
+            g.tp.recv_peers[r] = tp.recv_ptrs[r]
+            g.tp.counters_peers[r] = tp.counter_ptrs[r]
+        g.tp.partial = _check_tensor("tp.partial", tp.partial, f32, 2)
+        g.tp.epoch_device = _check_tensor("tp.epoch_device", tp.epoch_device, i32)
     g.flags = MKB_FLAG_RECORD_TIMINGS if record_timings else 0
     if record_timings and timings is None:
         raise ValueError("record_timings needs the timings tensor")
@@ -301,6 +337,7 @@ def mk_llama(
     record_timings=False,
     pos_id_device=None,
     residual_scale=1.0,
+    tp=None,
 ):
     """Enqueue one decode step; positional arguments as in the reference call.
 
@@ -322,11 +359,41 @@ def mk_llama(
         record_timings=record_timings,
         pos_id_device=pos_id_device,
         residual_scale=residual_scale,
+        tp=tp,
     )
     rc = lib.mkb_launch(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
     if rc != 0:
         raise MegakernelError(rc, lib.mkb_last_error().decode())
     return g
+
+
+def peer_alloc(nbytes: int) -> tuple[int, bytes]:
+    """Zero-filled peer-visible device memory on the current device: (address, 64-byte handle)."""
+    lib = load_library()
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(MKB_PEER_HANDLE_BYTES)
+    rc = lib.mkb_peer_alloc(nbytes, ctypes.byref(ptr), handle)
+    if rc != 0:
+        raise MegakernelError(rc, lib.mkb_last_error().decode())
+    return int(ptr.value), handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    """Map another process's peer_alloc block into this process; returns the local address."""
+    lib = load_library()
+    ptr = ctypes.c_void_p()
+    rc = lib.mkb_peer_open(ctypes.create_string_buffer(handle, MKB_PEER_HANDLE_BYTES), ctypes.byref(ptr))
+    if rc != 0:
+        raise MegakernelError(rc, lib.mkb_last_error().decode())
+    return int(ptr.value)
+
+
+def peer_close(ptr: int) -> None:
+    load_library().mkb_peer_close(ctypes.c_void_p(ptr))
+
+
+def peer_free(ptr: int) -> None:
+    load_library().mkb_peer_free(ctypes.c_void_p(ptr))
 
 
 def sync_status(g: MkbGlobals, stream=None) -> MkbStatus:

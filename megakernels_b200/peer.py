@@ -1,0 +1,104 @@
+"""Peer-mapped buffers for the in-kernel tensor-parallel all-reduce.
+
+No counterpart in the reference (single GPU).  Every rank owns one block of
+peer-visible device memory laid out as::
+
+    [ hidden_states  bf16 [H]                 ]  written by chunk owners
+    [ receive buffer fp32 [tp, H]             ]  written by every rank
+    [ counters       int32 [L, 2, 1 + 32]     ]  bumped by every rank, never zeroed
+
+and maps the blocks of all other ranks (CUDA IPC through ``libmkb200.so``;
+handles travel by ``torch.distributed.all_gather_object``).  ``connect``
+attaches the block to a ``Globals`` whose ``tp`` field the schedule builder
+created, replacing ``globs.hidden_states`` by the view into the block.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from megakernels_b200.instructions import TP_MAX_CHUNKS, TensorParallelState
+
+
+class _DeviceMemory:
+    """Lets torch wrap a raw device allocation (CUDA array interface, version 2)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,),
+            "typestr": "|u1",
+            "data": (ptr, False),
+            "version": 2,
+        }
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+class PeerBlock:
+    """One rank's peer-visible block plus the mapped blocks of the other ranks."""
+
+    def __init__(self, hidden_size: int, num_layers: int, tp_size: int, tp_rank: int, device, group=None):
+        import torch.distributed as dist
+
+        from megakernels_b200.native import mk_llama as native
+
+        self._native = native
+        self.tp_size, self.tp_rank = tp_size, tp_rank
+        self.hidden_off = 0
+        self.recv_off = _round_up(hidden_size * 2, 256)
+        self.counters_off = self.recv_off + _round_up(tp_size * hidden_size * 4, 256)
+        counters_bytes = num_layers * 2 * (1 + TP_MAX_CHUNKS) * 4
+        self.nbytes = self.counters_off + _round_up(counters_bytes, 256)
+
+        torch.cuda.set_device(device)
+        self.local_ptr, handle = native.peer_alloc(self.nbytes)
+        handles: list = [None] * tp_size
+        dist.all_gather_object(handles, handle, group=group)
+        self.ptrs = [
+            self.local_ptr if r == tp_rank else native.peer_open(handles[r]) for r in range(tp_size)
+        ]
+        self._raw = torch.as_tensor(_DeviceMemory(self.local_ptr, self.nbytes), device=device)
+        self.hidden = self._raw[: hidden_size * 2].view(torch.bfloat16)
+        self.recv = self._raw[self.recv_off : self.recv_off + tp_size * hidden_size * 4].view(torch.float32).view(
+            tp_size, hidden_size
+        )
+        self.counters = (
+            self._raw[self.counters_off : self.counters_off + counters_bytes]
+            .view(torch.int32)
+            .view(num_layers, 2, 1 + TP_MAX_CHUNKS)
+        )
+        # nobody may start storing into a block before every rank has mapped every block
+        dist.barrier(group=group)
+
+    def close(self):
+        """Unmap the peers and free the local block (all ranks, after their last launch)."""
+        if self.ptrs is None:
+            return
+        torch.cuda.synchronize()
+        for r, ptr in enumerate(self.ptrs):
+            if r != self.tp_rank:
+                self._native.peer_close(ptr)
+        self.hidden = self.recv = self.counters = self._raw = None
+        self._native.peer_free(self.local_ptr)
+        self.ptrs = None
+
+
+def connect(globs, group=None) -> PeerBlock:
+    """Allocate and exchange the peer buffers for ``globs.tp`` (collective over ``group``)."""
+    tp: TensorParallelState = globs.tp
+    assert tp is not None, "build the schedule with LatencyScheduleOptions(tp_all_reduce_chunks=...)"
+    H, L = globs.hidden_size, globs.num_hidden_layers
+    block = PeerBlock(H, L, tp.size, tp.rank, globs.device, group)
+    block.hidden.copy_(globs.hidden_states)
+    globs.hidden_states = block.hidden
+    slices = max(globs.num_o_proj_col_splits(), globs.num_down_proj_col_splits())
+    tp.partial = torch.zeros(slices, H, dtype=torch.float32, device=globs.device)
+    tp.recv, tp.counters = block.recv, block.counters
+    tp.epoch_device = torch.zeros(1, dtype=torch.int32, device=globs.device)
+    tp.epoch = 0
+    tp.hidden_ptrs = [p + block.hidden_off for p in block.ptrs]
+    tp.recv_ptrs = [p + block.recv_off for p in block.ptrs]
+    tp.counter_ptrs = [p + block.counters_off for p in block.ptrs]
+    return block

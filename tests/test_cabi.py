@@ -16,7 +16,8 @@ def declared_functions():
 def test_header_declares_the_expected_entry_points():
     names = declared_functions()
     for must in ("mkb_launch", "mkb_sync_status", "mkb_validate_instructions", "mkb_last_error",
-                 "mkb_sm_count", "mkb_smem_bytes", "mkb_block_threads", "mkb_abi_version"):
+                 "mkb_sm_count", "mkb_smem_bytes", "mkb_block_threads", "mkb_abi_version",
+                 "mkb_launch_no_alloc", "mkb_peer_alloc", "mkb_peer_open", "mkb_peer_close", "mkb_peer_free"):
         assert must in names
 
 
@@ -28,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in mkb200.h but not exported"
     lib.mkb_abi_version.restype = ctypes.c_int
-    assert lib.mkb_abi_version() == 1
+    assert lib.mkb_abi_version() == 2
     lib.mkb_smem_bytes.restype = ctypes.c_int
     assert 0 < lib.mkb_smem_bytes() <= 227 * 1024
 
@@ -45,6 +46,12 @@ def test_struct_layout_matches_between_header_and_shim():
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
     names = re.findall(r"[\w\*]\s+\**(\w+);", body)
     assert names == [f[0] for f in mk_llama.MkbGlobals._fields_]
+    body = text[text.index("typedef struct MkbTensorParallel {") : text.index("} MkbTensorParallel;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = re.findall(r"[\w\*]\s+\**(\w+)(?:\[\w+\])?;", body)
+    assert names == [f[0] for f in mk_llama.MkbTensorParallel._fields_]
+    # size agreed with the compiled library: validate() compares struct_bytes with sizeof
+    assert ctypes.sizeof(mk_llama.MkbTensorParallel) == 16 + 3 * 8 * 8 + 16
 
 
 def test_host_validation_without_a_gpu():
@@ -64,3 +71,9 @@ def test_host_validation_without_a_gpu():
     buf = torch.zeros(1, 1, 32, dtype=torch.int32)
     rc = lib.mkb_validate_instructions(ctypes.byref(g), ctypes.c_void_p(buf.data_ptr()))
     assert rc == 1 and b"ABI version" in lib.mkb_last_error()
+    # with the right version the library compares struct sizes next: the ctypes layout must
+    # have the size the compiler gave the header's struct, so the complaint moves on to pointers
+    g.abi_version = mk_llama.MKB_ABI_VERSION
+    g.struct_bytes = ctypes.sizeof(mk_llama.MkbGlobals)
+    rc = lib.mkb_validate_instructions(ctypes.byref(g), ctypes.c_void_p(buf.data_ptr()))
+    assert rc == 1 and b"barriers is NULL" in lib.mkb_last_error()

@@ -7,7 +7,12 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from megakernels_b200.demos.latency.instructions import DownProjResidual, O_ProjResidual
+from megakernels_b200.demos.latency.instructions import (
+    DownProjResidual,
+    LayerNormDoubleMatVecSiLU,
+    O_ProjResidual,
+    TP_AllReduce,
+)
 from megakernels_b200.demos.latency.scheduler import (
     LatencyScheduleOptions,
     split_at_collectives,
@@ -155,3 +160,131 @@ def test_nccl_ranks_on_real_gpus(tmp_path):
     mp.spawn(_nccl_rank, args=(2, 29519, tokens, str(out)), nprocs=2, join=True)
     for a, b in zip(torch.load(out), reference_logits(tokens)):
         assert_logits_parity(a, b, "tp=2 on NCCL")
+
+
+# --------------------------------------------------------------------------- #
+# all-reduce inside the kernel (TP_AllReduce instructions, one launch per token)
+# --------------------------------------------------------------------------- #
+PEER_OPTIONS = dict(coalesce_o_proj=True, tp_all_reduce_chunks=4)
+
+
+def test_all_reduce_instructions_follow_every_row_split_projection():
+    set_sm_count_override(148)
+    model = build_model(LlamaConfig(**CFG), 64, tp_size=2, tp_rank=1)
+    sched = build_schedule(model, LatencyScheduleOptions(**PEER_OPTIONS))
+    tp = sched.globs.tp
+    assert (tp.size, tp.rank, tp.num_chunks) == (2, 1, 4)
+    ins = sched.get_linear_instructions()
+    ars = [i for i in ins if isinstance(i, TP_AllReduce)]
+    assert len(ars) == 2 * CFG["num_hidden_layers"] * 4
+    assert ars[0].serialize()[:5] == [8, 0, 0, 0, 4]
+    # topological order: each group of chunks sits between its producer and its consumer
+    kinds = [type(i) for i in ins]
+    first_ar = kinds.index(TP_AllReduce)
+    assert kinds[first_ar - 1] is O_ProjResidual
+    assert kinds[first_ar + 4] is LayerNormDoubleMatVecSiLU
+    # an unsharded model never gets them
+    plain = build_schedule(build_model(LlamaConfig(**CFG), 64), LatencyScheduleOptions(**PEER_OPTIONS))
+    assert plain.globs.tp is None
+    assert not any(isinstance(i, TP_AllReduce) for i in plain.get_linear_instructions())
+
+
+def _attach_cpu_exchange(globs):
+    """What megakernels_b200.peer.connect does on GPUs, for the CPU checker: local buffers
+    and a gloo sum standing in for the stores into peer memory."""
+    from megakernels_b200.instructions import TP_MAX_CHUNKS
+
+    tp = globs.tp
+    slices = max(globs.num_o_proj_col_splits(), globs.num_down_proj_col_splits())
+    tp.partial = torch.zeros(slices, globs.hidden_size, dtype=torch.float32)
+    tp.counters = torch.zeros(globs.num_hidden_layers, 2, 1 + TP_MAX_CHUNKS, dtype=torch.int32)
+
+    def exchange(t):
+        t = t.clone()
+        dist.all_reduce(t)
+        return t
+
+    tp.exchange = exchange
+
+
+def _gloo_peer_rank(rank, world, port, tokens, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    set_sm_count_override(148)
+    model = tp_model(rank, world)
+    sched = build_schedule(model, LatencyScheduleOptions(**PEER_OPTIONS))
+    g = sched.globs
+    _attach_cpu_exchange(g)
+    vm = PyVM_Interpreter()
+    embed = model.model.embed_tokens.embed_tokens.weight
+    logits = []
+    for i, tok in enumerate(tokens):
+        g.hidden_states[:] = embed[tok]
+        g.barriers.zero_()  # the tensor-parallel counters are NOT reset: they count up
+        g.pos_id = PREFILL + i
+        vm.interpret(g, sched.get_linear_instructions())
+        g.tp.epoch += 1
+        logits.append(g.logits.clone())
+    assert int(g.tp.counters[0, 0, 0]) == 4 * len(tokens)
+    if rank == 0:
+        torch.save(logits, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_with_in_stream_all_reduce(tmp_path):
+    """TP_AllReduce semantics (fp32 partial sums, one rounding, epoch counters) on the CPU checker."""
+    tokens = seeded_tokens(CFG["vocab_size"], 3)
+    out = tmp_path / "logits.pt"
+    mp.spawn(_gloo_peer_rank, args=(2, 29521, tokens, str(out)), nprocs=2, join=True)
+    for a, b in zip(torch.load(out), reference_logits(tokens)):
+        assert_logits_parity(a, b, "tp=2, in-stream all-reduce on gloo")
+
+
+def _peer_rank(rank, world, port, tokens, out, use_graph):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from megakernels_b200.dispatch import make_mk_interpreter
+    from megakernels_b200.generators import TP_Peer_MK_Generator
+    from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+    dev = f"cuda:{rank}"
+    set_sm_count_override(torch.cuda.get_device_properties(rank).multi_processor_count)
+    model = tp_model(rank, world, device=dev)
+    sched = build_schedule(model, LatencyScheduleOptions(**PEER_OPTIONS))
+    tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+    gen = TP_Peer_MK_Generator(model, make_mk_interpreter("latency"), sched)
+    if use_graph:
+        gen.enable_cuda_graph(warmup_pos=PREFILL)
+    logits, hidden = [], []
+    for i, tok in enumerate(tokens):
+        gen.run(torch.tensor([[tok]], device=dev), PREFILL + i)
+        gen.check()
+        logits.append(sched.globs.logits.cpu())
+        hidden.append(sched.globs.hidden_states.cpu())
+    # every rank must hold the same residual stream, bit for bit
+    gathered = [None] * world
+    dist.all_gather_object(gathered, hidden)
+    if rank == 0:
+        for other in gathered[1:]:
+            for a, b in zip(gathered[0], other):
+                assert torch.equal(a, b), "ranks disagree on the residual stream"
+        torch.save(logits, out)
+    dist.barrier()
+    gen.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_peer_ranks_on_real_gpus(tmp_path, use_graph):
+    """One launch per token and rank; the all-reduce runs inside the kernels over peer memory."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    tokens = seeded_tokens(CFG["vocab_size"], 3)
+    out = tmp_path / "logits.pt"
+    mp.spawn(_peer_rank, args=(2, 29523 + int(use_graph), tokens, str(out), use_graph), nprocs=2, join=True)
+    for a, b in zip(torch.load(out), reference_logits(tokens)):
+        assert_logits_parity(a, b, "tp=2, in-kernel all-reduce")
