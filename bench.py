@@ -74,7 +74,7 @@ def parse_args():
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
                     help="tensor-parallel workloads: all-reduce inside the kernel over peer memory "
                          "(one launch per token) or NCCL between 2L+1 launches")
-    ap.add_argument("--tp-chunks", type=int, default=0, help="chunks per in-kernel all-reduce (0 = TP degree)")
+    ap.add_argument("--tp-chunks", type=int, default=0, help="chunks per in-kernel all-reduce (0 = H / 1024)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -275,7 +275,8 @@ def build_engine(args, device, tp_size=1, tp_rank=0, group=None):
     peer = tp_size > 1 and args.tp_exchange == "peer"
     options = LatencyScheduleOptions(
         num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj, balance=balance,
-        tp_all_reduce_chunks=(args.tp_chunks or tp_size) if peer else 0,
+        # chunks of 1024 elements: one pair per consumer thread, a multiple of the TP degree
+        tp_all_reduce_chunks=(args.tp_chunks or max(tp_size, cfg.hidden_size // 1024)) if peer else 0,
     )
     if balance:
         args.sched = "hint"

@@ -58,6 +58,11 @@ enum {
     MKB_T_CONSUMER_ACT_READY = 2,  /* activation vector (and RMSNorm) in registers */
     MKB_T_CONSUMER_FIRST_STAGE = 3,/* first ring stage of the instruction has arrived */
     MKB_T_CONSUMER_DONE = 4,       /* last block handed to the storer */
+    MKB_T_ATTN_STAGES_DONE = 5,    /* partial attention: all KV stages folded, merge starts */
+    MKB_T_RMS_LOADED = 6,          /* RMS ops: hidden state loaded, partial sums of squares written */
+    MKB_T_RMS_SUMMED = 7,          /* RMS ops: block-wide sum of squares available */
+    MKB_T_TP_SENT = 5,             /* all-reduce: this rank's sums stored at the owner, arrival signalled */
+    MKB_T_TP_ARRIVED = 6,          /* all-reduce, owner only: all ranks' sums have arrived */
     MKB_T_LOADER_START = 8,        /* loader reaches the instruction */
     MKB_T_LOADER_DONE = 9,         /* last stage of the instruction issued */
     MKB_T_STORER_START = 16,       /* storer reaches the instruction */
@@ -83,21 +88,27 @@ enum {
  *   1. o-proj / down-proj store their fp32 block sums into `partial[slice][H]` (local)
  *      instead of adding them to hidden_states;
  *   2. the instruction for chunk c (elements [c*H/n, (c+1)*H/n), n = num_chunks) waits
- *      for the local projection, sums the slices and writes the result into row `rank` of
- *      the receive buffer of the chunk's owner (rank c % size), then bumps the owner's
- *      arrival counter with a system-scope release;
- *   3. on the owner the same instruction waits for `size` arrivals, adds the rows in rank
- *      order to hidden_states in fp32, rounds to bf16 once, writes the chunk into the
- *      hidden_states of EVERY rank and bumps each rank's completion counter;
- *   4. the following RMSNorm instruction waits for num_chunks completions.
+ *      for the local projection, sums the slices and stores the result into row `rank` of
+ *      the receive buffer of the chunk's owner (rank c % size).  Every pair of sums travels
+ *      as one 16-byte store {x, tag, y, tag}: each 8-byte half arrives whole, and the tag,
+ *      unique per all-reduce, marks the value next to it as this round's, so the sender
+ *      needs no fence and the receiver no separate flag;
+ *   3. on the owner the threads of the same instruction poll the pairs they reduce until all
+ *      ranks' tags are current, add the rows in rank order to the residual stream in fp32,
+ *      round to bf16 once and store {bf16x2, tag} words into the tagged residual buffer of
+ *      EVERY rank;
+ *   4. the following RMSNorm instruction reads the residual stream from that buffer, every
+ *      thread polling the words it needs until they carry the tag.
  *
- * All ranks therefore hold bit-identical residual streams.  The counters are never
- * zeroed: they count up by a fixed amount per launch and waits compare against
- * (*epoch_device + 1) * amount, so a fast rank can never race a slow rank's reset.
- * `*epoch_device` must be the number of launches completed so far on this rank group
- * (same value on all ranks; the caller increments it after every launch).
- * Every peer pointer must be valid on THIS device (cudaIpcOpenMemHandle or an
- * equivalent mapping with peer access enabled); entry `rank` is the local buffer.
+ * All ranks therefore hold bit-identical residual streams, and no step needs a fence, a
+ * counter or a reset: a tag is derived from (*epoch_device, layer, which), so every all-reduce
+ * of every launch has its own.  `*epoch_device` must be the number of launches completed so
+ * far on this rank group (same value on all ranks; the caller increments it after every
+ * launch).  hidden_states keeps its meaning as the kernel's INPUT (the token embedding); the
+ * running residual stream of a tensor-parallel launch lives in the tagged buffer.
+ * Every peer pointer must be valid on THIS device (cudaIpcOpenMemHandle or an equivalent
+ * mapping with peer access enabled); entry `rank` is the local buffer.  All buffers must be
+ * zero before the first launch.
  */
 #define MKB_MAX_TP 8
 #define MKB_TP_MAX_CHUNKS 32
@@ -106,12 +117,11 @@ typedef struct MkbTensorParallel {
     int32_t rank;
     int32_t num_chunks;  /* chunks per all-reduce: a multiple of size, <= MKB_TP_MAX_CHUNKS */
     int32_t reserved;
-    void *hidden_peers[MKB_MAX_TP];      /* bf16 [H]: hidden_states of every rank */
-    float *recv_peers[MKB_MAX_TP];       /* fp32 [size][H]: receive buffer of every rank */
-    int32_t *counters_peers[MKB_MAX_TP]; /* int32 [L][2][1 + MKB_TP_MAX_CHUNKS]: word 0 counts
-                                            completed chunks, word 1 + c arrivals for chunk c */
-    float *partial;                      /* local fp32 [max(Hq*D, I) / R][H] */
-    const int32_t *epoch_device;         /* launches completed so far */
+    void *hidden_ll_peers[MKB_MAX_TP]; /* [H/2] x {bf16x2, tag} (8 bytes): residual stream of every rank */
+    void *recv_peers[MKB_MAX_TP];      /* [size][H/2] x {f32, tag, f32, tag} (16 bytes): receive
+                                          buffer of every rank */
+    float *partial;                    /* local fp32 [max(Hq*D, I) / R][H] */
+    const int32_t *epoch_device;       /* launches completed so far */
 } MkbTensorParallel;
 
 /*

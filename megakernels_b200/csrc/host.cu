@@ -229,13 +229,11 @@ int validate(const MkbGlobals* g) {
                         "tp: num_chunks %d must be a multiple of size %d, at most %d, and divide H/2",
                         tp.num_chunks, tp.size, MKB_TP_MAX_CHUNKS);
         for (int r = 0; r < tp.size; ++r) {
-            if (!tp.hidden_peers[r] || !tp.recv_peers[r] || !tp.counters_peers[r])
+            if (!tp.hidden_ll_peers[r] || !tp.recv_peers[r])
                 return fail(MKB_ERR_INVALID_ARGUMENT, "tp: peer pointers of rank %d are NULL", r);
-            if (!aligned16(tp.hidden_peers[r]) || !aligned16(tp.recv_peers[r]) || !aligned16(tp.counters_peers[r]))
+            if (!aligned16(tp.hidden_ll_peers[r]) || !aligned16(tp.recv_peers[r]))
                 return fail(MKB_ERR_INVALID_ARGUMENT, "tp: peer pointers of rank %d must be 16-byte aligned", r);
         }
-        if (tp.hidden_peers[tp.rank] != g->hidden_states)
-            return fail(MKB_ERR_INVALID_ARGUMENT, "tp: hidden_peers[rank] must be hidden_states");
         if (!tp.partial || !aligned16(tp.partial)) return fail(MKB_ERR_INVALID_ARGUMENT, "tp: partial buffer is NULL or unaligned");
         if (!tp.epoch_device) return fail(MKB_ERR_INVALID_ARGUMENT, "tp: epoch_device is NULL");
     }
@@ -325,9 +323,8 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
         p.tp_epoch_ptr = g->tp.epoch_device;
         p.tp_partial = g->tp.partial;
         for (int r = 0; r < g->tp.size; ++r) {
-            p.tp_hidden[r] = (__nv_bfloat16*)g->tp.hidden_peers[r];
-            p.tp_recv[r] = g->tp.recv_peers[r];
-            p.tp_counters[r] = g->tp.counters_peers[r];
+            p.tp_hidden_ll[r] = (uint2*)g->tp.hidden_ll_peers[r];
+            p.tp_recv[r] = (float*)g->tp.recv_peers[r];
         }
     }
     p.attn_scale_log2e = g->attn_scale * 1.4426950408889634f;

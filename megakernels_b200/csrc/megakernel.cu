@@ -124,13 +124,12 @@ __device__ __forceinline__ bool warp_mbar_wait(const Ctx& c, uint32_t bar, uint3
 }
 
 // Bounded wait for `*addr >= threshold` with acquire semantics.
-// `sys`: the counter is bumped by other GPUs (system-scope acquire).
 __device__ __noinline__ bool wait_counter(const Ctx& c, const int* addr, int threshold, int layer,
-                                          int row, int slot, bool sys = false) {
+                                          int row, int slot) {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
-        int v = sys ? ld_acquire_sys(addr) : ld_acquire_gpu(addr);
+        int v = ld_acquire_gpu(addr);
         if (v >= threshold) return true;
         if ((++spins & 63u) == 0) {
             if (*c.cta_abort) return false;
@@ -187,6 +186,35 @@ __device__ __noinline__ bool warp_wait_counters(const Ctx& c, const int* addr, i
 __device__ __forceinline__ int* bar_addr(const KParams& p, int layer, int row, int slot) {
     return p.barriers + ((size_t)layer * p.barrier_ops + row) * p.barrier_width + slot;
 }
+
+// ---- tensor-parallel exchange: tagged values ------------------------------- //
+// Values that cross GPUs travel as 8-byte {value, tag} words (two per 16-byte store).  The
+// tag names the all-reduce (launch, layer, which) the value belongs to, so a reader that
+// sees the expected tag knows the value beside it is current: no fence on the sender, no
+// flag or counter on the receiver, and nothing is ever reset.
+__device__ __forceinline__ uint32_t tp_tag(const Ctx& c, int layer, int which) {
+    return ((uint32_t)c.epoch * (uint32_t)c.p->L * 2u + (uint32_t)(layer * 2 + which)) % 0x7fffffffu + 1u;
+}
+// Bookkeeping of a bounded poll loop; tick() returns false when the thread must give up.
+struct TpPoll {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    __device__ __forceinline__ bool tick(const Ctx& c, int layer, int what, int index, int observed) {
+        if ((++spins & 63u) != 0) return true;
+        if (*c.cta_abort) return false;
+        if (global_abort(c)) {
+            *c.cta_abort = 1;
+            return false;
+        }
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > c.p->timeout_ns) {
+            report_error(c, MKB_ERR_DEVICE_TIMEOUT, layer, what, index, observed);
+            return false;
+        }
+        return true;
+    }
+};
 
 // --------------------------------------------------------------------------- //
 // matvec geometry
@@ -620,14 +648,45 @@ __device__ __forceinline__ void rms_prefetch(const Ctx& c, const __nv_bfloat16* 
         if (pf.chs[k] >= 0) pf.wv[k] = ld_nc_v4(norm_w + (size_t)pf.chs[k] * 8);
     }
 }
-__device__ __forceinline__ void rms_activation(const Ctx& c, const RmsPrefetch& pf) {
+// LL: the residual stream is read from this rank's tagged buffer (tensor parallelism), each
+// thread polling its own chunks until they carry `tag`; returns false if the wait was abandoned.
+template <bool LL>
+__device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& pf, uint32_t tag = 0,
+                                               int layer = 0, int which = 0) {
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint4 xv[2];
     float ss = 0.f;
+    bool ok = true;
+    if constexpr (LL) {
+        // 8 bf16 = four {bf16x2, tag} words = two 16-byte loads
+        const uint4* ll = reinterpret_cast<const uint4*>(p.tp_hidden_ll[p.tp_rank]);
+        TpPoll poll;
+        if (tid == 0) c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
 #pragma unroll
-    for (int k = 0; k < 2; ++k)
-        if (pf.chs[k] >= 0) xv[k] = ld_cg_v4(p.hidden + (size_t)pf.chs[k] * 8);
+        for (int k = 0; k < 2; ++k) {
+            if (pf.chs[k] < 0) continue;
+            uint4 a, b;
+            while (true) {
+                a = ld_volatile_v4(ll + (size_t)pf.chs[k] * 2);
+                b = ld_volatile_v4(ll + (size_t)pf.chs[k] * 2 + 1);
+                if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+                if (!poll.tick(c, layer, 100 + which, pf.chs[k], (int)a.y)) {
+                    ok = false;
+                    break;
+                }
+            }
+            xv[k] = make_uint4(a.x, a.z, b.x, b.z);
+        }
+        if (tid == 0) {
+            c.cta_abort[4] = 0;
+            rec(c, MKB_T_CONSUMER_WAIT_DONE);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+            if (pf.chs[k] >= 0) xv[k] = ld_cg_v4(p.hidden + (size_t)pf.chs[k] * 8);
+    }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         if (pf.chs[k] >= 0) {
@@ -641,9 +700,13 @@ __device__ __forceinline__ void rms_activation(const Ctx& c, const RmsPrefetch& 
     for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     float* red = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemRed));
     if (lane == 0) red[warp] = ss;
-    if (tid == 0) rec(c, 6);
-    consumer_sync();
-    if (tid == 0) rec(c, 7);
+    if (tid == 0) rec(c, MKB_T_RMS_LOADED);
+    if constexpr (LL) {
+        if (!consumer_all(ok)) return false;
+    } else {
+        consumer_sync();
+    }
+    if (tid == 0) rec(c, MKB_T_RMS_SUMMED);
     float tot = 0.f;
 #pragma unroll
     for (int k = 0; k < kConsumerWarps; ++k) tot += red[k];
@@ -663,19 +726,20 @@ __device__ __forceinline__ void rms_activation(const Ctx& c, const RmsPrefetch& 
         }
     }
     __syncwarp();
+    return true;
 }
 
 // Consumer thread 0 waits for a counter; the verdict reaches all 512 consumer
 // threads through shared memory so that they leave the instruction together.
-__device__ __forceinline__ bool consumers_wait_addr(const Ctx& c, ConsumerState& cs, const int* addr,
-                                                    int threshold, bool sys, int layer, int row,
-                                                    int slot, bool needed) {
+__device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerState& cs, int layer,
+                                                       int row, int slot, int threshold,
+                                                       bool needed) {
     volatile int* verdict = verdict_word(c, cs);
     if (threadIdx.x == 0) {
         bool ok = !*c.cta_abort;
         if (ok && needed) {
             c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
-            ok = wait_counter(c, addr, threshold, layer, row, slot, sys);
+            ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
             c.cta_abort[4] = 0;
         }
         rec(c, MKB_T_CONSUMER_WAIT_DONE);
@@ -684,30 +748,6 @@ __device__ __forceinline__ bool consumers_wait_addr(const Ctx& c, ConsumerState&
     consumer_sync();
     return *verdict != 0;
 }
-__device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerState& cs, int layer,
-                                                       int row, int slot, int threshold,
-                                                       bool needed) {
-    return consumers_wait_addr(c, cs, bar_addr(*c.p, layer, row, slot), threshold, false, layer, row,
-                               slot, needed);
-}
-
-// Tensor-parallel counters of rank r: word 0 of (layer, which) counts chunks whose reduced
-// values have reached this rank's hidden_states, word 1 + chunk the ranks whose partial sums
-// have reached this rank's receive buffer.  They only ever count up (see MkbTensorParallel).
-__device__ __forceinline__ int* tp_counter(const KParams& p, int r, int layer, int which, int word) {
-    return p.tp_counters[r] + ((size_t)layer * 2 + which) * (1 + MKB_TP_MAX_CHUNKS) + word;
-}
-// In tensor-parallel mode the residual stream is complete once every chunk of the
-// all-reduce after (layer, which) has been written here by its owner.
-__device__ __forceinline__ bool consumers_wait_residual(const Ctx& c, ConsumerState& cs, int layer,
-                                                        int which, int row, int threshold,
-                                                        bool needed) {
-    const KParams& p = *c.p;
-    if (p.tp_size > 1)
-        return consumers_wait_addr(c, cs, tp_counter(p, p.tp_rank, layer, which, 0),
-                                   p.tp_chunks * (c.epoch + 1), true, layer, 100 + which, 0, needed);
-    return consumers_wait_counter(c, cs, layer, row, 0, threshold, needed);
-}
 
 __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
                                                     const __nv_bfloat16* norm_w, int nblocks,
@@ -715,9 +755,14 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
                                                     bool needed) {
     RmsPrefetch pf;
     rms_prefetch(c, norm_w, pf);
-    const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
-    if (!consumers_wait_residual(c, cs, wait_layer, which, wait_row, threshold, needed)) return false;
-    rms_activation(c, pf);
+    if (c.p->tp_size > 1 && needed) {
+        // tensor parallel: the residual stream arrives as tagged values from the chunk owners
+        const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
+        if (!rms_activation<true>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which)) return false;
+    } else {
+        if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
+        rms_activation<false>(c, pf);
+    }
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->H);
     return true;
@@ -943,7 +988,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         // the last KV stage stays ours: its 32 KiB become the merge scratch below
         if (s + 1 < r.n_stages) consumer_release_stage(c, cs, lane);
     }
-    if (tid == 0) rec(c, 5);
+    if (tid == 0) rec(c, MKB_T_ATTN_STAGES_DONE);
 
     // score of the token being decoded (warp 0, fp32): one more entry for the merge
     float s_cur[GQA];
@@ -1167,10 +1212,11 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
 // --------------------------------------------------------------------------- //
 // consumers: tensor-parallel all-reduce of one chunk of the residual stream
 // --------------------------------------------------------------------------- //
-// Reduce-scatter then all-gather over peer memory with plain stores and one counter
-// bump per peer (protocol in MkbTensorParallel).  No thread ever waits without a budget:
-// a rank that never arrives turns into MKB_ERR_DEVICE_TIMEOUT on the others.
-__device__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState& cs, const int* w) {
+// Reduce-scatter and all-gather over peer memory with tagged stores only (protocol in
+// MkbTensorParallel).  No thread ever waits without a budget: a rank that never arrives turns
+// into MKB_ERR_DEVICE_TIMEOUT on the others.
+constexpr int kTpBatch = 8;  // column slices loaded per round trip
+__device__ __noinline__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState& cs, const int* w) {
     const KParams& p = *c.p;
     const int tid = threadIdx.x;
     const int layer = __ldg(w + 1), which = __ldg(w + 2), chunk = __ldg(w + 3), nchunks = __ldg(w + 4);
@@ -1179,46 +1225,81 @@ __device__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState& cs, const in
     const int slices = (which == 0 ? p.o_in : p.I) / p.R;
     const int row = (which == 0 ? MKB_OP_O_PROJ_RESIDUAL : MKB_OP_DOWN_PROJ_RESIDUAL) - 1;
     const int thr = which == 0 ? p.thr_upgate_waits_oproj : p.thr_qkv_waits_down;
+    const uint32_t tag = tp_tag(c, layer, which);
 
-    // 1. this rank's projection is complete: sum its column slices, send to the owner
+    // 1. this rank's projection is complete: sum its column slices, send the sums to the owner
     if (!consumers_wait_counter(c, cs, layer, row, 0, thr, true)) return false;
     {
-        float* dst = p.tp_recv[owner] + (size_t)p.tp_rank * p.H + e0;
+        uint4* dst = reinterpret_cast<uint4*>(p.tp_recv[owner]) + ((size_t)p.tp_rank * p.H + e0) / 2;
         for (int e = tid * 2; e < E; e += kConsumerThreads * 2) {
             float sx = 0.f, sy = 0.f;
-            for (int sl = 0; sl < slices; ++sl) {
-                const uint2 v = ldv_cg_v2(p.tp_partial + (size_t)sl * p.H + e0 + e);
-                sx += __uint_as_float(v.x);
-                sy += __uint_as_float(v.y);
+            for (int s0 = 0; s0 < slices; s0 += kTpBatch) {  // all loads of a batch in flight at once
+                uint2 v[kTpBatch];
+#pragma unroll
+                for (int k = 0; k < kTpBatch; ++k) {
+                    v[k] = make_uint2(0u, 0u);
+                    if (s0 + k < slices) v[k] = ldv_cg_v2(p.tp_partial + (size_t)(s0 + k) * p.H + e0 + e);
+                }
+#pragma unroll
+                for (int k = 0; k < kTpBatch; ++k) {
+                    sx += __uint_as_float(v[k].x);
+                    sy += __uint_as_float(v[k].y);
+                }
             }
-            st_global_v2_f32(dst + e, sx, sy);
+            st_volatile_v4(dst + e / 2, __float_as_uint(sx), tag, __float_as_uint(sy), tag);
         }
     }
-    consumer_sync();
-    if (tid == 0) red_release_sys_add(tp_counter(p, owner, layer, which, 1 + chunk), 1);
+    if (tid == 0) rec(c, MKB_T_TP_SENT);
     if (owner != p.tp_rank) return true;
 
-    // 2. owner: all ranks' sums have arrived; reduce in rank order, round once, broadcast
-    if (!consumers_wait_addr(c, cs, tp_counter(p, p.tp_rank, layer, which, 1 + chunk),
-                             p.tp_size * (c.epoch + 1), true, layer, 200 + which, chunk, true))
-        return false;
-    {
-        const float* src = p.tp_recv[p.tp_rank] + e0;
-        for (int e = tid * 2; e < E; e += kConsumerThreads * 2) {
-            float sx = 0.f, sy = 0.f;
-            for (int r = 0; r < p.tp_size; ++r) {
-                const uint2 v = ldv_cg_v2(src + (size_t)r * p.H + e);
-                sx += __uint_as_float(v.x);
-                sy += __uint_as_float(v.y);
+    // 2. owner: every thread polls the pairs it reduces until all ranks' tags are current, adds
+    // them in rank order to the residual stream in fp32, rounds once and sends the new values
+    // (tagged again) to every rank.  The old residual value is the previous all-reduce's result
+    // in this rank's own tagged buffer, or the token embedding for the first one of a launch.
+    const bool first = layer == 0 && which == 0;
+    const uint32_t prev_tag = first ? 0u : (which == 1 ? tp_tag(c, layer, 0) : tp_tag(c, layer - 1, 1));
+    const uint4* src = reinterpret_cast<const uint4*>(p.tp_recv[p.tp_rank]) + e0 / 2;
+    const uint2* old = p.tp_hidden_ll[p.tp_rank] + e0 / 2;
+    bool ok = true;
+    TpPoll poll;
+    for (int e = tid * 2; e < E && ok; e += kConsumerThreads * 2) {
+        uint4 v[MKB_MAX_TP];
+        uint2 h = make_uint2(0u, prev_tag);
+        if (first) h.x = ldv_cg_u32(p.hidden + e0 + e);
+        while (true) {
+            bool all = true;
+            int late = -1;
+#pragma unroll
+            for (int r = 0; r < MKB_MAX_TP; ++r) {
+                if (r < p.tp_size) {
+                    v[r] = ld_volatile_v4(src + ((size_t)r * p.H + e) / 2);
+                    if (v[r].y != tag || v[r].w != tag) {
+                        all = false;
+                        late = r;
+                    }
+                }
             }
-            const uint32_t h = ldv_cg_u32(p.hidden + e0 + e);
-            const uint32_t out = pack_bf16x2(bf16_lo(h) + sx, bf16_hi(h) + sy);
-            for (int r = 0; r < p.tp_size; ++r) st_global_u32(p.tp_hidden[r] + e0 + e, out);
+            if (!first) h = ld_volatile_v2(old + e / 2);
+            if (all && h.y == prev_tag) break;
+            if (!poll.tick(c, layer, 200 + which, chunk, late)) {
+                ok = false;
+                break;
+            }
         }
+        if (!ok) break;
+        float sx = 0.f, sy = 0.f;
+#pragma unroll
+        for (int r = 0; r < MKB_MAX_TP; ++r) {  // rank order: the same sum whoever owns the chunk
+            if (r < p.tp_size) {
+                sx += __uint_as_float(v[r].x);
+                sy += __uint_as_float(v[r].z);
+            }
+        }
+        const uint32_t out = pack_bf16x2(bf16_lo(h.x) + sx, bf16_hi(h.x) + sy);
+        for (int r = 0; r < p.tp_size; ++r) st_volatile_v2(p.tp_hidden_ll[r] + (e0 + e) / 2, out, tag);
     }
-    consumer_sync();
-    if (tid < p.tp_size) red_release_sys_add(tp_counter(p, tid, layer, which, 0), 1);
-    return true;
+    if (tid == 0) rec(c, MKB_T_TP_ARRIVED);
+    return consumer_all(ok);
 }
 
 // --------------------------------------------------------------------------- //

@@ -87,9 +87,8 @@ struct KParams {
     // in-kernel tensor-parallel all-reduce (MkbTensorParallel); tp_size <= 1: off
     int tp_size, tp_rank, tp_chunks;
     const int* tp_epoch_ptr;
-    __nv_bfloat16* tp_hidden[MKB_MAX_TP];
-    float* tp_recv[MKB_MAX_TP];
-    int* tp_counters[MKB_MAX_TP];
+    uint2* tp_hidden_ll[MKB_MAX_TP];  // [H/2] x {bf16x2, tag} of every rank
+    float* tp_recv[MKB_MAX_TP];       // [size][H/2] x {f32, tag, f32, tag} of every rank
     float* tp_partial;
     // barrier thresholds, derived on the host from the shapes
     int thr_qkv_waits_down;     // (H/16) * (I/R)
@@ -165,15 +164,6 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// system scope: the counter lives in (or is written from) another GPU's memory
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
-    asm volatile("fence.acq_rel.sys;\n\tred.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 // ordered variants (volatile, memory clobber) for data another GPU wrote or will read
 __device__ __forceinline__ uint2 ldv_cg_v2(const void* p) {
     uint2 v;
@@ -185,11 +175,40 @@ __device__ __forceinline__ uint32_t ldv_cg_u32(const void* p) {
     asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_global_v2_f32(float* p, float a, float b) {
-    asm volatile("st.global.v2.f32 [%0], {%1,%2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+// 16-byte accesses whose two 8-byte halves {value, tag} each arrive whole: the receiver
+// needs no separate flag (and the sender no fence) to know that a value is valid
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
 }
-__device__ __forceinline__ void st_global_u32(void* p, uint32_t v) {
-    asm volatile("st.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_volatile_v2(void* p, uint32_t a, uint32_t b) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, uint32_t a, uint32_t b, uint32_t c2, uint32_t d) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c2), "r"(d)
+                 : "memory");
+}
+// AND of a predicate over the 512 consumer threads (one barrier)
+__device__ __forceinline__ bool consumer_all(bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "bar.red.and.pred q, 1, %2, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(out)
+        : "r"((uint32_t)pred), "n"(kConsumerThreads)
+        : "memory");
+    return out != 0;
 }
 __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
     asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -37,12 +37,12 @@ class TensorParallelState:
     num_chunks: int
     epoch: int = 0  # launches completed so far; mirrors ``epoch_device``
     partial: Tensor | None = None  # fp32 [max slices, H], local
-    recv: Tensor | None = None  # fp32 [size, H], written by peers
-    counters: Tensor | None = None  # int32 [L, 2, 1 + TP_MAX_CHUNKS], written by peers, never zeroed
+    recv: Tensor | None = None  # int32 [size, H/2, 4] = {f32, tag, f32, tag}, written by peers
+    hidden_tagged: Tensor | None = None  # int32 [H/2, 2] = {bf16x2, tag}: the running residual stream
+    counters: Tensor | None = None  # CPU checker only: int32 [L, 2, 1 + TP_MAX_CHUNKS] arrival counts
     epoch_device: Tensor | None = None  # int32 [1]
-    hidden_ptrs: list[int] | None = None  # device address of hidden_states on every rank
+    hidden_ptrs: list[int] | None = None  # device address of the tagged residual buffer on every rank
     recv_ptrs: list[int] | None = None
-    counter_ptrs: list[int] | None = None
     exchange: Any = None  # CPU checker only: fp32 tensor -> sum over ranks
 
     def __post_init__(self):

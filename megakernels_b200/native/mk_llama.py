@@ -41,9 +41,8 @@ class MkbTensorParallel(ctypes.Structure):
         ("rank", ctypes.c_int32),
         ("num_chunks", ctypes.c_int32),
         ("reserved", ctypes.c_int32),
-        ("hidden_peers", ctypes.c_void_p * MKB_MAX_TP),
+        ("hidden_ll_peers", ctypes.c_void_p * MKB_MAX_TP),
         ("recv_peers", ctypes.c_void_p * MKB_MAX_TP),
-        ("counters_peers", ctypes.c_void_p * MKB_MAX_TP),
         ("partial", ctypes.c_void_p),
         ("epoch_device", ctypes.c_void_p),
     ]
@@ -307,9 +306,8 @@ def pack_globals(
             raise ValueError("tensor-parallel state has no peer buffers attached (peer.connect)")
         g.tp.size, g.tp.rank, g.tp.num_chunks = tp.size, tp.rank, tp.num_chunks
         for r in range(tp.size):
-            g.tp.hidden_peers[r] = tp.hidden_ptrs[r]
+            g.tp.hidden_ll_peers[r] = tp.hidden_ptrs[r]
             g.tp.recv_peers[r] = tp.recv_ptrs[r]
-            g.tp.counters_peers[r] = tp.counter_ptrs[r]
         g.tp.partial = _check_tensor("tp.partial", tp.partial, f32, 2)
         g.tp.epoch_device = _check_tensor("tp.epoch_device", tp.epoch_device, i32)
     g.flags = MKB_FLAG_RECORD_TIMINGS if record_timings else 0

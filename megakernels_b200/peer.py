@@ -3,21 +3,20 @@
 No counterpart in the reference (single GPU).  Every rank owns one block of
 peer-visible device memory laid out as::
 
-    [ hidden_states  bf16 [H]                 ]  written by chunk owners
-    [ receive buffer fp32 [tp, H]             ]  written by every rank
-    [ counters       int32 [L, 2, 1 + 32]     ]  bumped by every rank, never zeroed
+    [ residual stream [H/2] x {bf16x2, tag}           ]  written by chunk owners
+    [ receive buffer  [tp, H/2] x {f32, tag, f32, tag} ]  written by every rank
 
 and maps the blocks of all other ranks (CUDA IPC through ``libmkb200.so``;
 handles travel by ``torch.distributed.all_gather_object``).  ``connect``
 attaches the block to a ``Globals`` whose ``tp`` field the schedule builder
-created, replacing ``globs.hidden_states`` by the view into the block.
+created.  Nothing in the block is ever reset: values carry tags (include/mkb200.h).
 """
 
 from __future__ import annotations
 
 import torch
 
-from megakernels_b200.instructions import TP_MAX_CHUNKS, TensorParallelState
+from megakernels_b200.instructions import TensorParallelState
 
 
 class _DeviceMemory:
@@ -47,10 +46,10 @@ class PeerBlock:
         self._native = native
         self.tp_size, self.tp_rank = tp_size, tp_rank
         self.hidden_off = 0
-        self.recv_off = _round_up(hidden_size * 2, 256)
-        self.counters_off = self.recv_off + _round_up(tp_size * hidden_size * 4, 256)
-        counters_bytes = num_layers * 2 * (1 + TP_MAX_CHUNKS) * 4
-        self.nbytes = self.counters_off + _round_up(counters_bytes, 256)
+        hidden_bytes = hidden_size * 4  # every bf16 pair travels with a 4-byte tag
+        self.recv_off = _round_up(hidden_bytes, 256)
+        recv_bytes = tp_size * hidden_size * 8  # every fp32 pair travels with two 4-byte tags
+        self.nbytes = self.recv_off + _round_up(recv_bytes, 256)
 
         torch.cuda.set_device(device)
         self.local_ptr, handle = native.peer_alloc(self.nbytes)
@@ -60,14 +59,9 @@ class PeerBlock:
             self.local_ptr if r == tp_rank else native.peer_open(handles[r]) for r in range(tp_size)
         ]
         self._raw = torch.as_tensor(_DeviceMemory(self.local_ptr, self.nbytes), device=device)
-        self.hidden = self._raw[: hidden_size * 2].view(torch.bfloat16)
-        self.recv = self._raw[self.recv_off : self.recv_off + tp_size * hidden_size * 4].view(torch.float32).view(
-            tp_size, hidden_size
-        )
-        self.counters = (
-            self._raw[self.counters_off : self.counters_off + counters_bytes]
-            .view(torch.int32)
-            .view(num_layers, 2, 1 + TP_MAX_CHUNKS)
+        self.hidden_tagged = self._raw[:hidden_bytes].view(torch.int32).view(hidden_size // 2, 2)
+        self.recv = self._raw[self.recv_off : self.recv_off + recv_bytes].view(torch.int32).view(
+            tp_size, hidden_size // 2, 4
         )
         # nobody may start storing into a block before every rank has mapped every block
         dist.barrier(group=group)
@@ -80,7 +74,7 @@ class PeerBlock:
         for r, ptr in enumerate(self.ptrs):
             if r != self.tp_rank:
                 self._native.peer_close(ptr)
-        self.hidden = self.recv = self.counters = self._raw = None
+        self.hidden_tagged = self.recv = self._raw = None
         self._native.peer_free(self.local_ptr)
         self.ptrs = None
 
@@ -91,14 +85,11 @@ def connect(globs, group=None) -> PeerBlock:
     assert tp is not None, "build the schedule with LatencyScheduleOptions(tp_all_reduce_chunks=...)"
     H, L = globs.hidden_size, globs.num_hidden_layers
     block = PeerBlock(H, L, tp.size, tp.rank, globs.device, group)
-    block.hidden.copy_(globs.hidden_states)
-    globs.hidden_states = block.hidden
     slices = max(globs.num_o_proj_col_splits(), globs.num_down_proj_col_splits())
     tp.partial = torch.zeros(slices, H, dtype=torch.float32, device=globs.device)
-    tp.recv, tp.counters = block.recv, block.counters
+    tp.recv, tp.hidden_tagged = block.recv, block.hidden_tagged
     tp.epoch_device = torch.zeros(1, dtype=torch.int32, device=globs.device)
     tp.epoch = 0
     tp.hidden_ptrs = [p + block.hidden_off for p in block.ptrs]
     tp.recv_ptrs = [p + block.recv_off for p in block.ptrs]
-    tp.counter_ptrs = [p + block.counters_off for p in block.ptrs]
     return block

@@ -25,6 +25,7 @@ OP_NAMES = {
     5: "upgate_silu",
     6: "down_proj_residual",
     7: "lm_head",
+    8: "tp_all_reduce",
 }
 
 
@@ -63,6 +64,11 @@ def summarize(globs) -> dict:
             elif op == 2:
                 d["stages"].append(us(5) - us(T_WAIT_DONE))
                 d["merge_store"].append(us(T_CONSUMER_DONE) - us(5))
+            elif op == 8:
+                d["send"].append(us(5) - us(T_WAIT_DONE))
+                if int(t[6]) != 0:  # only the chunk's owner waits for arrivals and broadcasts
+                    d["arrivals"].append(us(6) - us(5))
+                    d["reduce_bcast"].append(us(T_CONSUMER_DONE) - us(6))
             else:
                 d["work"].append(us(T_CONSUMER_DONE) - us(T_WAIT_DONE))
             key = (_layer_of(ins[sm, i]), op)
@@ -84,7 +90,7 @@ def format_summary(summary: dict, layers=(1,)) -> str:
     lines.append("per opcode: phase mean / max (us) over instructions")
     for name, d in summary["stats"].items():
         parts = [f"{k} {m:.2f}/{mx:.2f}" for k, (m, mx, _) in d.items()]
-        n = next(iter(d.values()))[2]
+        n = max(v[2] for v in d.values())
         lines.append(f"  {name:20s} n={n:5d}  " + "  ".join(parts))
     for layer in layers:
         lines.append(f"layer {layer}: first start .. last done | barrier satisfied first .. last (us)")

@@ -51,7 +51,7 @@ def test_struct_layout_matches_between_header_and_shim():
     names = re.findall(r"[\w\*]\s+\**(\w+)(?:\[\w+\])?;", body)
     assert names == [f[0] for f in mk_llama.MkbTensorParallel._fields_]
     # size agreed with the compiled library: validate() compares struct_bytes with sizeof
-    assert ctypes.sizeof(mk_llama.MkbTensorParallel) == 16 + 3 * 8 * 8 + 16
+    assert ctypes.sizeof(mk_llama.MkbTensorParallel) == 16 + 2 * 8 * 8 + 16
 
 
 def test_host_validation_without_a_gpu():

@@ -263,7 +263,7 @@ def _peer_rank(rank, world, port, tokens, out, use_graph):
         gen.run(torch.tensor([[tok]], device=dev), PREFILL + i)
         gen.check()
         logits.append(sched.globs.logits.cpu())
-        hidden.append(sched.globs.hidden_states.cpu())
+        hidden.append(sched.globs.tp.hidden_tagged[:, 0].cpu())  # the residual stream's bf16 pairs
     # every rank must hold the same residual stream, bit for bit
     gathered = [None] * world
     dist.all_gather_object(gathered, hidden)
