@@ -40,10 +40,10 @@ UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
 
 # DRAM traffic of one megakernel launch relative to its algorithmic bytes, from the ncu capture
-# summarised in profiles/megakernel_llama8b_4layers_ncu_full.md: (2.839 GB read + 0.030 GB written)
+# summarised in profiles/megakernel_llama8b_4layers_ncu_full.md: (2.855 GB read + 0.034 GB written)
 # against 2.796 GB algorithmic on the 4-layer case; traffic grows in proportion to the layers
 # streamed, so the full launch is scaled by the same ratio.
-NCU_TRAFFIC_RATIO = (2.8390e9 + 0.0295e9) / 2.7955e9
+NCU_TRAFFIC_RATIO = (2.8553e9 + 0.0336e9) / 2.7955e9
 
 WORKLOADS = {
     # tp=False: every rank runs an independent replica; tp=True: the ranks shard one model
