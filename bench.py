@@ -372,7 +372,7 @@ def run_ours(args):
             launch_events.append((e0, e1))
             if globs.tp is not None:
                 globs.tp.epoch_device.add_(1)  # as TP_Peer_MK_Generator._step does
-            torch.argmax(globs.logits, dim=-1)
+            gen._next_token()  # the kernel's own argmax word (torch.argmax if that is switched off)
     end.record()
     torch.cuda.profiler.stop()
     log("timed steps enqueued")

@@ -199,6 +199,12 @@ typedef struct MkbGlobals {
                                      TP degree and average their residual streams afterwards */
 
     MkbTensorParallel tp;         /* in-kernel tensor-parallel all-reduce; tp.size <= 1: off */
+    int32_t *argmax_out;          /* if not NULL: device int32 that receives argmax(logits) (smallest
+                                     index among equal bf16 maxima, as torch.argmax), computed by the
+                                     LM-head epilogue so that the host needs no reduction kernel
+                                     (the reference calls torch.argmax, megakernels/generators.py:143).
+                                     Valid only for schedules that hold the LM head; ignored by
+                                     mkb_launch_no_alloc */
 
     /* ---- options ---- */
     uint32_t flags;           /* MKB_FLAG_* */

@@ -13,6 +13,7 @@
 
 namespace mkb {
 __global__ void megakernel(const __grid_constant__ KParams p);
+__global__ void megakernel_tp(const __grid_constant__ KParams p);
 }
 
 using namespace mkb;
@@ -252,8 +253,11 @@ int device_state(DeviceState** out) {
             return fail(MKB_ERR_UNSUPPORTED, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
         ds.sm_count = prop.multiProcessorCount;
         MKB_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc));
-        MKB_CUDA(cudaMalloc(&ds.status, MKB_STATUS_WORDS * sizeof(int)));
-        MKB_CUDA(cudaMemset(ds.status, 0, MKB_STATUS_WORDS * sizeof(int)));
+        MKB_CUDA(cudaFuncSetAttribute(megakernel_tp, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc));
+        // status record, then the fused-argmax scratch: arrival counter + {value, index} per CTA
+        const size_t words = MKB_STATUS_WORDS + 2 + 2 * (size_t)ds.sm_count;
+        MKB_CUDA(cudaMalloc(&ds.status, words * sizeof(int)));
+        MKB_CUDA(cudaMemset(ds.status, 0, words * sizeof(int)));
         ds.attr_set = true;
     }
     *out = &ds;
@@ -316,6 +320,10 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     p.pos_id = g->pos_id;
     p.pos_id_ptr = g->pos_id_device;
     p.residual_scale = g->residual_scale > 0.f ? g->residual_scale : 1.f;
+    if (g->argmax_out && ds) {  // the scratch sits behind the library's own status record
+        p.argmax_out = g->argmax_out;
+        p.argmax_scratch = ds->status + MKB_STATUS_WORDS;
+    }
     if (g->tp.size > 1) {
         p.tp_size = g->tp.size;
         p.tp_rank = g->tp.rank;
@@ -388,7 +396,10 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     KParams p;
     rc = prepare_launch(g, ds, (g && g->status) ? g->status : ds->status, ds->sm_count, p);
     if (rc) return rc;
-    megakernel<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
+    if (p.tp_size > 1)
+        megakernel_tp<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
+    else
+        megakernel<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     MKB_CUDA(cudaGetLastError());
     return MKB_OK;
 }
@@ -408,6 +419,8 @@ int mkb_sync_status(const MkbGlobals* g, void* cuda_stream, MkbStatus* out) {
     memcpy(out, words, sizeof(MkbStatus));
     if (words[0] != MKB_OK || words[kStatusAbortWord] != 0) {
         MKB_CUDA(cudaMemset(st, 0, sizeof(words)));  // re-arm for the next launch
+        // an aborted launch may have left the fused-argmax arrival counter short of a full round
+        MKB_CUDA(cudaMemset(ds->status + MKB_STATUS_WORDS, 0, sizeof(int)));
         static const char* roles[] = {"loader", "consumer", "storer"};
         const char* role = (out->role >= 0 && out->role < 3) ? roles[out->role] : "?";
         return fail(out->code ? out->code : MKB_ERR_DEVICE_TIMEOUT,

@@ -27,7 +27,6 @@ struct Ctx {
     uint32_t base;            // shared-window address of the aligned smem base
     volatile int* cta_abort;  // generic pointer to the CTA-wide abort word
     int pos;                  // position of the token being decoded
-    int epoch;                // launches completed before this one (tensor-parallel counters)
     int instr;                // instruction index being executed (for reports)
     int opcode;
     int role;
@@ -193,7 +192,10 @@ __device__ __forceinline__ int* bar_addr(const KParams& p, int layer, int row, i
 // sees the expected tag knows the value beside it is current: no fence on the sender, no
 // flag or counter on the receiver, and nothing is ever reset.
 __device__ __forceinline__ uint32_t tp_tag(const Ctx& c, int layer, int which) {
-    return ((uint32_t)c.epoch * (uint32_t)c.p->L * 2u + (uint32_t)(layer * 2 + which)) % 0x7fffffffu + 1u;
+    // the launch counter is read where it is needed (only tensor-parallel paths get here) so
+    // that it does not occupy a register in everybody else's code
+    const uint32_t epoch = (uint32_t)__ldg(c.p->tp_epoch_ptr);
+    return (epoch * (uint32_t)c.p->L * 2u + (uint32_t)(layer * 2 + which)) % 0x7fffffffu + 1u;
 }
 // Bookkeeping of a bounded poll loop; tick() returns false when the thread must give up.
 struct TpPoll {
@@ -749,17 +751,26 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     return *verdict != 0;
 }
 
+// kTP selects the tensor-parallel build of the kernel.  It is a compile-time switch and the two
+// builds are separate kernels: merely having the exchange code in the same kernel cost the
+// single-GPU path 4 % (measured; the compiler's register allocation for the whole kernel moves).
+template <bool kTP>
 __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
                                                     const __nv_bfloat16* norm_w, int nblocks,
                                                     int wait_layer, int wait_row, int threshold,
                                                     bool needed) {
     RmsPrefetch pf;
     rms_prefetch(c, norm_w, pf);
-    if (c.p->tp_size > 1 && needed) {
-        // tensor parallel: the residual stream arrives as tagged values from the chunk owners
-        const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
-        if (!rms_activation<true>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which)) return false;
-    } else {
+    bool tagged = false;
+    if constexpr (kTP) {
+        // the residual stream arrives as tagged values from the chunk owners
+        if (needed) {
+            const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
+            if (!rms_activation<true>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which)) return false;
+            tagged = true;
+        }
+    }
+    if (!tagged) {
         if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
         rms_activation<false>(c, pf);
     }
@@ -1305,22 +1316,23 @@ __device__ __noinline__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState&
 // --------------------------------------------------------------------------- //
 // consumer dispatch
 // --------------------------------------------------------------------------- //
+template <bool kTP>
 __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
     const KParams& p = *c.p;
     switch (op) {
         case MKB_OP_RMS_QKV_ROPE_APPEND: {
             const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
-            return consumer_rms_matvec(c, cs, p.attn_ln_w + (size_t)layer * p.H, eb - sb, layer - 1,
+            return consumer_rms_matvec<kTP>(c, cs, p.attn_ln_w + (size_t)layer * p.H, eb - sb, layer - 1,
                                        MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, layer > 0);
         }
         case MKB_OP_RMS_UPGATE_SILU: {
             const int layer = __ldg(w + 1), n = __ldg(w + 2);
-            return consumer_rms_matvec(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
+            return consumer_rms_matvec<kTP>(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
                                        MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true);
         }
         default: {  // MKB_OP_RMS_LM_HEAD
             const int sb = __ldg(w + 1), eb = __ldg(w + 2);
-            return consumer_rms_matvec(c, cs, p.lm_norm_w, eb - sb, p.L - 1,
+            return consumer_rms_matvec<kTP>(c, cs, p.lm_norm_w, eb - sb, p.L - 1,
                                        MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true);
         }
     }
@@ -1336,6 +1348,7 @@ __device__ bool consumer_residual_op(const Ctx& c, ConsumerState& cs, int op, co
                                  MKB_OP_RMS_UPGATE_SILU - 1, rb, p.thr_down_waits_upgate);
 }
 
+template <bool kTP>
 __device__ void consumer_main(Ctx c) {
     const KParams& p = *c.p;
     ConsumerState cs;
@@ -1354,7 +1367,7 @@ __device__ void consumer_main(Ctx c) {
             case MKB_OP_RMS_QKV_ROPE_APPEND:
             case MKB_OP_RMS_UPGATE_SILU:
             case MKB_OP_RMS_LM_HEAD:
-                ok = consumer_rms_op(c, cs, op, w);
+                ok = consumer_rms_op<kTP>(c, cs, op, w);
                 break;
             case MKB_OP_O_PROJ_RESIDUAL:
             case MKB_OP_DOWN_PROJ_RESIDUAL:
@@ -1371,7 +1384,7 @@ __device__ void consumer_main(Ctx c) {
                 else ok = consumer_attn_reduction<128>(c, cs, w);
                 break;
             case MKB_OP_TP_ALL_REDUCE:
-                if (p.tp_size > 1) {
+                if constexpr (kTP) {
                     ok = consumer_tp_all_reduce(c, cs, w);
                     break;
                 }
@@ -1396,7 +1409,51 @@ struct StorerState {
     int* my_addr = nullptr;
     int my_count = 0;
     int n_entries = 0;
+    // running argmax of the logits this lane has stored (bf16-rounded value, vocabulary index)
+    float best_val = -INFINITY;
+    int best_idx = 0x7fffffff;
 };
+
+// (value, index) ordering of torch.argmax: larger value wins, then the smaller index
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) {
+        v = ov;
+        i = oi;
+    }
+}
+
+// End of the storer's queue: publish this CTA's best logit; the CTA that arrives last merges
+// all of them, writes the token id and re-arms the arrival counter for the next launch.
+__device__ __noinline__ void storer_finish_argmax(const Ctx& c, StorerState& ss, int lane) {
+    const KParams& p = *c.p;
+    float v = ss.best_val;
+    int i = ss.best_idx;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1)
+        argmax_merge(v, i, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, i, o));
+    int* slots = p.argmax_scratch + 2;
+    int old = 0;
+    if (lane == 0) {
+        slots[2 * blockIdx.x] = __float_as_int(v);
+        slots[2 * blockIdx.x + 1] = i;
+        __threadfence();
+        old = atomicAdd(p.argmax_scratch, 1);
+    }
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old != (int)gridDim.x - 1) return;
+    __threadfence();
+    v = -INFINITY;
+    i = 0x7fffffff;
+    for (int k = lane; k < (int)gridDim.x; k += 32)
+        argmax_merge(v, i, __int_as_float((int)ld_cg_u32(slots + 2 * k)), (int)ld_cg_u32(slots + 2 * k + 1));
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1)
+        argmax_merge(v, i, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, i, o));
+    if (lane == 0) {
+        *p.argmax_out = i;
+        *p.argmax_scratch = 0;
+    }
+}
 
 // sum the per-warp partials of the next finished block; lane r < 16 gets row r
 __device__ __forceinline__ float storer_take_block(const Ctx& c, StorerState& ss, int lane,
@@ -1445,6 +1502,7 @@ __device__ __forceinline__ void storer_signal(StorerState& ss, int lane, int* ad
     ss.n_entries++;
 }
 
+template <bool kTP>
 __device__ void storer_main(Ctx c) {
     const KParams& p = *c.p;
     StorerState ss;
@@ -1502,7 +1560,7 @@ __device__ void storer_main(Ctx c) {
             case MKB_OP_O_PROJ_RESIDUAL:
             case MKB_OP_DOWN_PROJ_RESIDUAL: {
                 const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
-                if (p.tp_size > 1) {
+                if constexpr (kTP) {
                     // in-kernel tensor parallelism: the fp32 block sums of this column slice
                     // go to the rank's partial buffer; MKB_OP_TP_ALL_REDUCE adds them up
                     float* part = p.tp_partial + (size_t)__ldg(w + 4) * p.H;
@@ -1545,6 +1603,7 @@ __device__ void storer_main(Ctx c) {
                     const float hi = __shfl_down_sync(0xffffffffu, v, 1);
                     if (lane < 16 && (lane & 1) == 0)
                         *reinterpret_cast<uint32_t*>(p.logits + b * kBlockRows + row) = pack_bf16x2(v, hi);
+                    if (lane < 16) argmax_merge(ss.best_val, ss.best_idx, bf16_round(v), b * kBlockRows + row);
                 }
             } break;
             default:
@@ -1552,12 +1611,14 @@ __device__ void storer_main(Ctx c) {
         }
         if (lane == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_STORER_DONE);
     }
+    if (p.argmax_out != nullptr) storer_finish_argmax(c, ss, lane);
 }
 
 // --------------------------------------------------------------------------- //
 // kernel
 // --------------------------------------------------------------------------- //
-__global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_constant__ KParams p) {
+template <bool kTP>
+__device__ __forceinline__ void megakernel_body(const KParams& p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -1571,7 +1632,6 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
     c.opcode = -1;
     c.role = -1;
     c.pos = p.pos_id_ptr ? __ldg(p.pos_id_ptr) : p.pos_id;
-    c.epoch = (p.tp_size > 1 && p.tp_epoch_ptr) ? __ldg(p.tp_epoch_ptr) : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kNumStages; ++s) {
@@ -1594,11 +1654,11 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
 
     const int warp = threadIdx.x >> 5;
     if (warp < kConsumerWarps) {
-        consumer_main(c);
+        consumer_main<kTP>(c);
     } else if (warp == kLoaderWarp) {
         if ((threadIdx.x & 31) == 0) loader_main(c);
     } else {
-        storer_main(c);
+        storer_main<kTP>(c);
     }
     __syncthreads();
 
@@ -1614,6 +1674,15 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
             if (!mbar_try_wait(bar, parity)) mbar_wait_slow(c, bar, parity, false);
         }
     }
+}
+
+// Two kernels from one body: the single-GPU one, and the one that can exchange partial sums
+// with peer GPUs (MkbTensorParallel), launched when tp.size > 1.
+__global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_constant__ KParams p) {
+    megakernel_body<false>(p);
+}
+__global__ void __launch_bounds__(kBlockThreads, 1) megakernel_tp(const __grid_constant__ KParams p) {
+    megakernel_body<true>(p);
 }
 
 }  // namespace mkb

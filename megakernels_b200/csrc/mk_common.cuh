@@ -84,6 +84,10 @@ struct KParams {
     float attn_scale_log2e;  // attn_scale * log2(e)
     float rms_eps;
     int skip_attn_reduction;
+    // fused argmax over the logits: result word, and library-owned scratch
+    // [0] = CTAs finished, then {value bits, index} per CTA
+    int* argmax_out;
+    int* argmax_scratch;
     // in-kernel tensor-parallel all-reduce (MkbTensorParallel); tp_size <= 1: off
     int tp_size, tp_rank, tp_chunks;
     const int* tp_epoch_ptr;

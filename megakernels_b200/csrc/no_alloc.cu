@@ -73,6 +73,8 @@ extern "C" int mkb_launch_no_alloc(const MkbGlobals* g, void* cuda_stream) {
     int rc = setup_device(dev, &pd);
     if (rc) return rc;
 
+    if (g->tp.size > 1)
+        return set_error(MKB_ERR_UNSUPPORTED, "mkb_launch_no_alloc has no tensor-parallel variant");
     if (g->num_attention_heads < 1 || g->max_partials < 1 || g->head_dim < 1)
         return set_error(MKB_ERR_INVALID_ARGUMENT,
                          "num_attention_heads, max_partials and head_dim must be positive");

@@ -54,6 +54,7 @@ def interpret_with_mk(globs: Globals, mk_func, stream=None, **kwargs):
         residual_scale=globs.residual_scale,
         pos_id_device=globs.pos_id_device,
         tp=globs.tp,
+        argmax_out=globs.argmax_out,
         **kwargs,
     )
 

@@ -65,6 +65,7 @@ class MK_Generator(Generator):
         barrier_fill_val: int = 0,
         skip_mk: bool = False,
         skip_rest: bool = False,
+        fused_argmax: bool = True,
     ):
         self.model = model
         self.interpreter = interpreter
@@ -74,6 +75,13 @@ class MK_Generator(Generator):
         self.skip_rest = skip_rest
         self.last_call = None
         self.fill()
+        # The kernel's LM-head epilogue can deliver argmax(logits) itself (the reference runs
+        # torch.argmax over the 128k logits after the kernel, generators.py:143).  Only for
+        # schedules that contain the LM head and when the megakernel actually runs.
+        globs = schedule.globs
+        has_head = globs.instructions is not None and bool((globs.instructions[:, :, 0] == 7).any())
+        if fused_argmax and has_head and not skip_mk and globs.hidden_states.is_cuda:
+            globs.argmax_out = torch.zeros(1, dtype=torch.int32, device=globs.hidden_states.device)
 
     def fill(self):
         self.schedule.globs.barriers.fill_(self.barrier_fill_val)
@@ -116,6 +124,12 @@ class MK_Generator(Generator):
         globs.hidden_states[:] = post.hidden_states.reshape(-1)
         self.fill()
         self.last_call = self.interpreter.interpret(globs)
+        return self._next_token()
+
+    def _next_token(self) -> Tensor:
+        globs = self.schedule.globs
+        if globs.argmax_out is not None:
+            return globs.argmax_out.to(torch.long)
         return torch.argmax(globs.logits, dim=-1)
 
     def _replay(self, input_ids: Tensor, pos_id: int) -> Tensor:
@@ -138,7 +152,7 @@ class MK_Generator(Generator):
             self.last_call = self.interpreter.interpret(globs)
         if self.skip_rest:
             return input_ids
-        return torch.argmax(globs.logits, dim=-1)
+        return self._next_token()
 
     def generate(
         self,

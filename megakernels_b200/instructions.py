@@ -97,6 +97,7 @@ class BaseGlobals:
         self.residual_scale: float = 1.0  # tensor-parallel degree (see generators.TP_MK_Generator)
         self.pos_id_device: Tensor | None = None  # int32[1]; overrides pos_id when set
         self.tp: TensorParallelState | None = None  # in-kernel tensor-parallel all-reduce
+        self.argmax_out: Tensor | None = None  # int32[1]: the kernel's own argmax over the logits
 
     def sm_count(self) -> int:
         return get_sm_count(self.device)

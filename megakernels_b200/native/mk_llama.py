@@ -97,6 +97,7 @@ class MkbGlobals(ctypes.Structure):
         ("pos_id_device", ctypes.c_void_p),
         ("residual_scale", ctypes.c_float),
         ("tp", MkbTensorParallel),
+        ("argmax_out", ctypes.c_void_p),
         ("flags", ctypes.c_uint32),
         ("wait_timeout_ms", ctypes.c_uint32),
         ("status", ctypes.c_void_p),
@@ -214,6 +215,7 @@ def pack_globals(
     pos_id_device=None,
     residual_scale=1.0,
     tp=None,
+    argmax_out=None,
 ) -> MkbGlobals:
     """Fill the C struct from tensors; every dimension is read off the shapes."""
     bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
@@ -310,6 +312,8 @@ def pack_globals(
             g.tp.recv_peers[r] = tp.recv_ptrs[r]
         g.tp.partial = _check_tensor("tp.partial", tp.partial, f32, 2)
         g.tp.epoch_device = _check_tensor("tp.epoch_device", tp.epoch_device, i32)
+    if argmax_out is not None:
+        g.argmax_out = _check_tensor("argmax_out", argmax_out, i32)
     g.flags = MKB_FLAG_RECORD_TIMINGS if record_timings else 0
     if record_timings and timings is None:
         raise ValueError("record_timings needs the timings tensor")
@@ -336,6 +340,7 @@ def mk_llama(
     pos_id_device=None,
     residual_scale=1.0,
     tp=None,
+    argmax_out=None,
 ):
     """Enqueue one decode step; positional arguments as in the reference call.
 
@@ -358,6 +363,7 @@ def mk_llama(
         pos_id_device=pos_id_device,
         residual_scale=residual_scale,
         tp=tp,
+        argmax_out=argmax_out,
     )
     rc = lib.mkb_launch(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
     if rc != 0:

@@ -257,6 +257,43 @@ def test_greedy_generation_matches_oracle():
             logits = ref.decode_token(got[i], prompt.numel() + i)
 
 
+def test_fused_argmax_equals_torch_argmax_of_the_logits():
+    """The LM-head epilogue's own argmax (all CTAs merge through the last one to finish) must be
+    exactly torch.argmax of the logits the same launch wrote, launch after launch, also when
+    ties exist (smallest index wins) and in CUDA-graph replay."""
+    from megakernels_b200.generators import MK_Generator
+
+    cfg = small_1b()
+    _, _, gpu_model, gpu_sched = make_pair(cfg, 64, 0, poison=False)
+    gen = MK_Generator(gpu_model, interpreter(), gpu_sched)
+    globs = gpu_sched.globs
+    assert globs.argmax_out is not None
+    toks = seeded_tokens(cfg.vocab_size, 6, seed=5)
+    for pos, tok in enumerate(toks):
+        got = gen.run(torch.tensor([[tok]], device="cuda:0"), pos)
+        gen.check()
+        assert int(got) == int(torch.argmax(globs.logits)), f"position {pos}"
+    # ties: a zero LM head makes every logit equal, so index 0 must win
+    head = globs.lm_head_weights.data
+    saved = head.clone()
+    head.zero_()
+    got = gen.run(torch.tensor([[toks[0]]], device="cuda:0"), len(toks))
+    gen.check()
+    assert int(got) == 0 == int(torch.argmax(globs.logits))
+    head.copy_(saved)
+    gen.enable_cuda_graph(warmup_pos=len(toks))
+    for i, tok in enumerate(toks[:3]):
+        got = gen.run(torch.tensor([[tok]], device="cuda:0"), len(toks) + 1 + i)
+        gen.check()
+        assert int(got) == int(torch.argmax(globs.logits)), f"graph replay {i}"
+    # opting out restores the reference's host-side reduction
+    _, _, gpu_model2, gpu_sched2 = make_pair(cfg, 64, 0, poison=False)
+    gen2 = MK_Generator(gpu_model2, interpreter(), gpu_sched2, fused_argmax=False)
+    assert gpu_sched2.globs.argmax_out is None
+    got = gen2.run(torch.tensor([[toks[0]]], device="cuda:0"), 0)
+    assert int(got) == int(torch.argmax(gpu_sched2.globs.logits))
+
+
 @pytest.mark.parametrize("shape", ["1b", "8b"])
 def test_balanced_schedule_matches_oracle(shape):
     """The timeline-model builder (pinned SMs, overlapping up/gate and down-proj)."""
