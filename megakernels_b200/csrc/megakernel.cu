@@ -751,6 +751,12 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     return *verdict != 0;
 }
 
+// Out of line: the polling loops would otherwise be inlined three times into the consumer loop.
+__device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefetch& pf, int wait_layer,
+                                                   int which) {
+    return rms_activation<true>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
+}
+
 // kTP selects the tensor-parallel build of the kernel.  It is a compile-time switch and the two
 // builds are separate kernels: merely having the exchange code in the same kernel cost the
 // single-GPU path 4 % (measured; the compiler's register allocation for the whole kernel moves).
@@ -766,7 +772,7 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
         // the residual stream arrives as tagged values from the chunk owners
         if (needed) {
             const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
-            if (!rms_activation<true>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which)) return false;
+            if (!rms_activation_tagged(c, pf, wait_layer, which)) return false;
             tagged = true;
         }
     }
