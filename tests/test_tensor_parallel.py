@@ -288,3 +288,62 @@ def test_peer_ranks_on_real_gpus(tmp_path, use_graph):
     mp.spawn(_peer_rank, args=(2, 29523 + int(use_graph), tokens, str(out), use_graph), nprocs=2, join=True)
     for a, b in zip(torch.load(out), reference_logits(tokens)):
         assert_logits_parity(a, b, "tp=2, in-kernel all-reduce")
+
+
+def _peer_rank_with_a_silent_peer(rank, world, port, tokens, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from megakernels_b200.dispatch import make_mk_interpreter
+    from megakernels_b200.generators import TP_Peer_MK_Generator
+    from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+
+    dev = f"cuda:{rank}"
+    set_sm_count_override(torch.cuda.get_device_properties(rank).multi_processor_count)
+    model = tp_model(rank, world, device=dev)
+    sched = build_schedule(model, LatencyScheduleOptions(**PEER_OPTIONS))
+    tensorize_instructions(sched.globs, assign_to_sms("rr", schedule=sched))
+    gen = TP_Peer_MK_Generator(model, make_mk_interpreter("latency"), sched)
+    import mk_llama  # the module make_mk_interpreter put on the path
+
+    g = sched.globs
+    verdict = "not run"
+    if rank == 0:
+        # rank 1 never launches: rank 0's waits for its partial sums must run out (50 ms
+        # budget) and come back as a status record, not as a hang
+        g.hidden_states[:] = model.model.embed_tokens.embed_tokens.weight[tokens[0]]
+        g.barriers.zero_()
+        g.pos_id = PREFILL
+        call = gen.interpreter.interpret(g, wait_timeout_ms=50)
+        try:
+            mk_llama.sync_status(call)
+            verdict = "no error"
+        except mk_llama.MegakernelError as err:
+            verdict = f"code {err.code} opcode {err.status.opcode}"
+    dist.barrier()  # rank 1 sat here on the host the whole time, nothing of it in flight
+    # the context is still usable and the exchange recovers: a normal step on both ranks
+    logits = []
+    for i, tok in enumerate(tokens):
+        gen.run(torch.tensor([[tok]], device=dev), PREFILL + i)
+        gen.check()
+        logits.append(g.logits.cpu())
+    if rank == 0:
+        torch.save((verdict, logits), out)
+    dist.barrier()
+    gen.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_peer_rank_that_never_launches_is_reported_not_hung(tmp_path):
+    """Failure detection across GPUs without faulting one: the missing rank is simulated on the
+    host (it simply does not launch); the waiting rank's polls are bounded."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    tokens = seeded_tokens(CFG["vocab_size"], 2)
+    out = tmp_path / "result.pt"
+    mp.spawn(_peer_rank_with_a_silent_peer, args=(2, 29527, tokens, str(out)), nprocs=2, join=True)
+    verdict, logits = torch.load(out)
+    assert verdict.startswith("code 3"), verdict  # MKB_ERR_DEVICE_TIMEOUT
+    for a, b in zip(logits, reference_logits(tokens)):
+        assert_logits_parity(a, b, "tp=2 after a timed-out launch")
