@@ -396,7 +396,10 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     KParams p;
     rc = prepare_launch(g, ds, (g && g->status) ? g->status : ds->status, ds->sm_count, p);
     if (rc) return rc;
-    if (p.tp_size > 1)
+    // MKB_FORCE_TP_KERNEL: run single-GPU work through the tensor-parallel build (to measure what
+    // carrying the exchange code costs the streaming path)
+    static const bool force_tp_kernel = getenv("MKB_FORCE_TP_KERNEL") != nullptr;
+    if (p.tp_size > 1 || force_tp_kernel)
         megakernel_tp<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     else
         megakernel<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);

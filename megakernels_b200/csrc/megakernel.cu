@@ -752,7 +752,7 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
 }
 
 // Out of line: the polling loops would otherwise be inlined three times into the consumer loop.
-__device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefetch& pf, int wait_layer,
+__device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefetch pf, int wait_layer,
                                                    int which) {
     return rms_activation<true>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
 }
@@ -770,7 +770,7 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
     bool tagged = false;
     if constexpr (kTP) {
         // the residual stream arrives as tagged values from the chunk owners
-        if (needed) {
+        if (needed && c.p->tp_size > 1) {
             const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
             if (!rms_activation_tagged(c, pf, wait_layer, which)) return false;
             tagged = true;
@@ -1232,8 +1232,8 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
 // Reduce-scatter and all-gather over peer memory with tagged stores only (protocol in
 // MkbTensorParallel).  No thread ever waits without a budget: a rank that never arrives turns
 // into MKB_ERR_DEVICE_TIMEOUT on the others.
-constexpr int kTpBatch = 8;  // column slices loaded per round trip
-__device__ __noinline__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState& cs, const int* w) {
+constexpr int kTpBatch = 4;  // column slices loaded per round trip
+__device__ __forceinline__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState& cs, const int* w) {
     const KParams& p = *c.p;
     const int tid = threadIdx.x;
     const int layer = __ldg(w + 1), which = __ldg(w + 2), chunk = __ldg(w + 3), nchunks = __ldg(w + 4);
@@ -1280,38 +1280,49 @@ __device__ __noinline__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerState&
     bool ok = true;
     TpPoll poll;
     for (int e = tid * 2; e < E && ok; e += kConsumerThreads * 2) {
-        uint4 v[MKB_MAX_TP];
+        // old residual value: plain embedding for the first all-reduce of a launch, else the
+        // previous all-reduce's tagged result
         uint2 h = make_uint2(0u, prev_tag);
-        if (first) h.x = ldv_cg_u32(p.hidden + e0 + e);
-        while (true) {
-            bool all = true;
-            int late = -1;
-#pragma unroll
-            for (int r = 0; r < MKB_MAX_TP; ++r) {
-                if (r < p.tp_size) {
-                    v[r] = ld_volatile_v4(src + ((size_t)r * p.H + e) / 2);
-                    if (v[r].y != tag || v[r].w != tag) {
-                        all = false;
-                        late = r;
-                    }
+        if (first) {
+            h.x = ldv_cg_u32(p.hidden + e0 + e);
+        } else {
+            while (true) {
+                h = ld_volatile_v2(old + e / 2);
+                if (h.y == prev_tag) break;
+                if (!poll.tick(c, layer, 300 + which, chunk, (int)h.y)) {
+                    ok = false;
+                    break;
                 }
             }
-            if (!first) h = ld_volatile_v2(old + e / 2);
-            if (all && h.y == prev_tag) break;
-            if (!poll.tick(c, layer, 200 + which, chunk, late)) {
-                ok = false;
-                break;
+        }
+        // ranks in groups of four (keeps the registers of this rarely-run path few), in rank
+        // order: the same sum whoever owns the chunk
+        float sx = 0.f, sy = 0.f;
+        for (int r0 = 0; r0 < p.tp_size && ok; r0 += 4) {
+            uint4 v[4];
+            while (true) {
+                int late = -1;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    v[k] = make_uint4(0u, tag, 0u, tag);
+                    if (r0 + k < p.tp_size) {
+                        v[k] = ld_volatile_v4(src + ((size_t)(r0 + k) * p.H + e) / 2);
+                        if (v[k].y != tag || v[k].w != tag) late = r0 + k;
+                    }
+                }
+                if (late < 0) break;
+                if (!poll.tick(c, layer, 200 + which, chunk, late)) {
+                    ok = false;
+                    break;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                sx += __uint_as_float(v[k].x);
+                sy += __uint_as_float(v[k].z);
             }
         }
         if (!ok) break;
-        float sx = 0.f, sy = 0.f;
-#pragma unroll
-        for (int r = 0; r < MKB_MAX_TP; ++r) {  // rank order: the same sum whoever owns the chunk
-            if (r < p.tp_size) {
-                sx += __uint_as_float(v[r].x);
-                sy += __uint_as_float(v[r].z);
-            }
-        }
         const uint32_t out = pack_bf16x2(bf16_lo(h.x) + sx, bf16_hi(h.x) + sy);
         for (int r = 0; r < p.tp_size; ++r) st_volatile_v2(p.tp_hidden_ll[r] + (e0 + e) / 2, out, tag);
     }
@@ -1390,7 +1401,7 @@ __device__ void consumer_main(Ctx c) {
                 else ok = consumer_attn_reduction<128>(c, cs, w);
                 break;
             case MKB_OP_TP_ALL_REDUCE:
-                if constexpr (kTP) {
+                if (kTP && p.tp_size > 1) {
                     ok = consumer_tp_all_reduce(c, cs, w);
                     break;
                 }
@@ -1566,7 +1577,7 @@ __device__ void storer_main(Ctx c) {
             case MKB_OP_O_PROJ_RESIDUAL:
             case MKB_OP_DOWN_PROJ_RESIDUAL: {
                 const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
-                if constexpr (kTP) {
+                if (kTP && p.tp_size > 1) {
                     // in-kernel tensor parallelism: the fp32 block sums of this column slice
                     // go to the rank's partial buffer; MKB_OP_TP_ALL_REDUCE adds them up
                     float* part = p.tp_partial + (size_t)__ldg(w + 4) * p.H;
