@@ -922,14 +922,31 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
     float k_cur[DPL], v_cur[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) k_cur[i] = v_cur[i] = 0.f;
-    float q_cur[GQA][DPL];
+    // its score is taken right away (these loads return together with the Q fragments, which
+    // the first stage needs anyway), so that only GQA scores and the V row stay in registers
+    float s_cur[GQA];
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) s_cur[h] = -INFINITY;
     if (warp == 0 && r.has_cur) {
         const size_t off = (((size_t)layer * p.B) * p.T + c.pos) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
         load_row_gmem<DPL>(p.k_cache + off, k_cur);
         load_row_gmem<DPL>(p.v_cache + off, v_cur);
 #pragma unroll
-        for (int h = 0; h < GQA; ++h)
-            load_row_gmem<DPL>(p.q_rope + (size_t)(kvh * GQA + h) * D + lane * DPL, q_cur[h]);
+        for (int h = 0; h < GQA; ++h) {
+            float q_cur[DPL];
+            load_row_gmem<DPL>(p.q_rope + (size_t)(kvh * GQA + h) * D + lane * DPL, q_cur);
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) d = fmaf(q_cur[i], k_cur[i], d);
+            s_cur[h] = d;
+        }
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+            float d = s_cur[h];
+#pragma unroll
+            for (int o2 = 16; o2 >= 1; o2 >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o2);
+            s_cur[h] = d * p.attn_scale_log2e;
+        }
     }
 
     float m_run = -INFINITY, l_run = 0.f;  // head g, replicated over t
@@ -1006,22 +1023,6 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         if (s + 1 < r.n_stages) consumer_release_stage(c, cs, lane);
     }
     if (tid == 0) rec(c, MKB_T_ATTN_STAGES_DONE);
-
-    // score of the token being decoded (warp 0, fp32): one more entry for the merge
-    float s_cur[GQA];
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) s_cur[h] = -INFINITY;
-    if (warp == 0 && r.has_cur) {
-#pragma unroll
-        for (int h = 0; h < GQA; ++h) {
-            float d = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) d = fmaf(q_cur[h][i], k_cur[i], d);
-#pragma unroll
-            for (int o2 = 16; o2 >= 1; o2 >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o2);
-            s_cur[h] = d * p.attn_scale_log2e;
-        }
-    }
 
     if (r.n_stages == 0) {
         // no cached positions in this slice: at most the current token, whose softmax weight is 1
@@ -1129,9 +1130,10 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
 }
 
 // AttentionReduction: merge `n` partial (O, LSE) pairs for 4 consecutive heads.
+// One output element per thread (thread = head * D + dim), so a batch of 12 partial rows costs 12
+// registers and all its loads are in flight together: one L2 round trip for up to 12 partials.
 template <int D>
 __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const int* w) {
-    constexpr int DPL = D / 32;
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int layer = __ldg(w + 1), h0 = __ldg(w + 2), num_partials = __ldg(w + 3);
@@ -1150,78 +1152,63 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
     }
     consumer_sync();
     if (*verdict == 0) return false;
-    if (warp >= 4) return true;
 
-    const int head = h0 + warp;
-    int idx = 0;
-    float lse = -INFINITY;
-    if (lane < n) {
-        idx = __ldg(w + 6 + lane);
-        lse = ld_cg_f32(p.attn_lse + (size_t)head * p.max_partials + idx);
-    }
-    // Batches of 12 partial rows: all loads of a batch are issued before the first value
-    // (the LSEs included) is used, so the L2 round trips overlap instead of adding up.
-    constexpr int NB = 12;
-    float o_acc[DPL];
+    const bool active = tid < 4 * D;  // whole warps: D is a multiple of 32
+    if (active) {
+        const int head = h0 + tid / D, dim = tid % D;
+        int idx = 0;
+        float lse = -INFINITY;
+        if (lane < n) {
+            idx = __ldg(w + 6 + lane);
+            lse = ld_cg_f32(p.attn_lse + (size_t)head * p.max_partials + idx);
+        }
+        constexpr int NB = 12;
+        const float* base = p.attn_o + (size_t)head * p.max_partials * D + dim;
+        float acc = 0.f, mx = 0.f, wgt = 0.f, denom = 0.f;
+        for (int j0 = 0; j0 < n; j0 += NB) {
+            float part[NB];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) o_acc[i] = 0.f;
-    float mx = 0.f, wgt = 0.f, denom = 0.f;
-    for (int j0 = 0; j0 < n; j0 += NB) {
-        float part[NB][DPL];
+            for (int jj = 0; jj < NB; ++jj) {
+                const int j = j0 + jj;
+                const int ij = __shfl_sync(0xffffffffu, idx, j & 31);
+                part[jj] = ld_cg_f32(base + (size_t)(j < n ? ij : 0) * D);
+            }
+            if (j0 == 0) {
+                mx = lse;
 #pragma unroll
-        for (int jj = 0; jj < NB; ++jj) {
-            const int j = j0 + jj;
-            const int ij = __shfl_sync(0xffffffffu, idx, j & 31);
-            const float* src = p.attn_o + ((size_t)head * p.max_partials + (j < n ? ij : 0)) * D + lane * DPL;
-            if constexpr (DPL == 4) {
-                const uint4 v = ld_cg_v4(src);
-                part[jj][0] = __uint_as_float(v.x); part[jj][1] = __uint_as_float(v.y);
-                part[jj][2] = __uint_as_float(v.z); part[jj][3] = __uint_as_float(v.w);
-            } else {
-                const uint2 v = ld_cg_v2(src);
-                part[jj][0] = __uint_as_float(v.x); part[jj][1] = __uint_as_float(v.y);
+                for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                const float ms = (mx == -INFINITY) ? 0.f : mx;
+                wgt = exp2f(lse - ms);
+                denom = wgt;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+            }
+#pragma unroll
+            for (int jj = 0; jj < NB; ++jj) {
+                const int j = j0 + jj;
+                const float wj = (j < n) ? __shfl_sync(0xffffffffu, wgt, j & 31) : 0.f;
+                acc = fmaf(wj, part[jj], acc);
             }
         }
-        if (j0 == 0) {
-            mx = lse;
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float ms = (mx == -INFINITY) ? 0.f : mx;
-            wgt = exp2f(lse - ms);
-            denom = wgt;
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
-        }
-#pragma unroll
-        for (int jj = 0; jj < NB; ++jj) {
-            const int j = j0 + jj;
-            const float wj = (j < n) ? __shfl_sync(0xffffffffu, wgt, j & 31) : 0.f;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) o_acc[i] = fmaf(wj, part[jj][i], o_acc[i]);
+        const float val = acc * (denom > 0.f ? 1.f / denom : 0.f);
+        if (is_terminal) {
+            const float hi = __shfl_down_sync(0xffffffffu, val, 1);
+            if ((dim & 1) == 0)
+                *reinterpret_cast<uint32_t*>(p.attn_out + (size_t)head * D + dim) = pack_bf16x2(val, hi);
+        } else {
+            p.attn_o[((size_t)head * p.max_partials + out_idx) * D + dim] = val;
+            if (dim == 0)
+                p.attn_lse[(size_t)head * p.max_partials + out_idx] =
+                    denom > 0.f ? mx + log2f(denom) : -INFINITY;
         }
     }
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    if (is_terminal) {
-        __nv_bfloat16* dst = p.attn_out + (size_t)head * D + lane * DPL;
-        if constexpr (DPL == 4) {
-            uint2 v;
-            v.x = pack_bf16x2(o_acc[0] * inv, o_acc[1] * inv);
-            v.y = pack_bf16x2(o_acc[2] * inv, o_acc[3] * inv);
-            *reinterpret_cast<uint2*>(dst) = v;
-        } else {
-            *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(o_acc[0] * inv, o_acc[1] * inv);
+    consumer_sync();  // every thread's stores precede the signal below
+    if (warp == 0) {
+        if (is_terminal) {
+            if (lane == 0) red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), 4);
+        } else if (lane < 4) {
+            red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, h0 + lane), 1);
         }
-        __syncwarp();
-        if (lane == 0) red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), 1);
-    } else {
-        float* dst = p.attn_o + ((size_t)head * p.max_partials + out_idx) * D + lane * DPL;
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) dst[i] = o_acc[i] * inv;
-        if (lane == 0)
-            p.attn_lse[(size_t)head * p.max_partials + out_idx] =
-                denom > 0.f ? mx + log2f(denom) : -INFINITY;
-        __syncwarp();
-        if (lane == 0) red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, head), 1);
     }
     return true;
 }

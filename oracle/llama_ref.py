@@ -19,6 +19,8 @@ the build container (tests/golden/torch_*.pt).
 
 from __future__ import annotations
 
+import math
+
 import torch
 import torch.nn.functional as F
 from torch import Tensor
@@ -105,10 +107,13 @@ def parity_metrics(test: Tensor, ref: Tensor) -> dict:
     """
     a, b = test.float().flatten().cpu(), ref.float().flatten().cpu()
     top2 = torch.topk(b, 2).values
+    top = float(top2[0].abs().clamp_min(1e-30))
     return {
         "max_rel": float((a - b).abs().max() / b.abs().max().clamp_min(1e-12)),
         "cosine": float(F.cosine_similarity(a, b, dim=0)),
         "top2_margin": float(top2[0] - top2[1]),
+        # spacing of bf16 values (8 significant bits) at the largest logit
+        "top_bf16_step": 2.0 ** (math.floor(math.log2(top)) - 7),
         "argmax_equal": bool(a.argmax() == b.argmax()),
     }
 
@@ -122,6 +127,11 @@ def assert_logits_parity(test: Tensor, ref: Tensor, what: str = ""):
     m = parity_metrics(test, ref)
     assert m["max_rel"] <= MAX_REL_TOL, f"{what}: max rel err {m['max_rel']:.4g} > {MAX_REL_TOL}"
     assert m["cosine"] >= COSINE_TOL, f"{what}: cosine {m['cosine']:.6f} < {COSINE_TOL}"
-    if m["top2_margin"] > MARGIN_TOL:
+    # Logits are bf16: when the reference's two largest logits are NEIGHBOURING bf16 values (at
+    # a logit of 4..8 one step is 0.03125, above MARGIN_TOL) the winner is decided by the
+    # reference's own last rounding, and the residual stream's bf16 atomic adds, whose order
+    # varies from run to run, flip it now and then.  The argmax rule therefore applies when the
+    # margin exceeds both MARGIN_TOL and one bf16 step of the top logit.
+    if m["top2_margin"] > max(MARGIN_TOL, m["top_bf16_step"]):
         assert m["argmax_equal"], f"{what}: argmax differs with margin {m['top2_margin']:.4g}"
     return m
