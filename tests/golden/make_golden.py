@@ -1,7 +1,7 @@
 """Generate the golden fixtures by running the reference implementation itself.
 
-Run once in a container that has the reference checkout (default
-``/root/reference``; override with ``MK_REFERENCE_DIR``):
+Run once on a machine that has a checkout of the reference (point
+``MK_REFERENCE_DIR`` at it):
 
     python tests/golden/make_golden.py
 
