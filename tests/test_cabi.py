@@ -77,3 +77,54 @@ def test_host_validation_without_a_gpu():
     g.struct_bytes = ctypes.sizeof(mk_llama.MkbGlobals)
     rc = lib.mkb_validate_instructions(ctypes.byref(g), ctypes.c_void_p(buf.data_ptr()))
     assert rc == 1 and b"barriers is NULL" in lib.mkb_last_error()
+
+
+def test_host_validation_of_all_reduce_instructions():
+    """Opcode 8 is only legal with the tensor-parallel block filled in, and its chunk index
+    must stay below tp.num_chunks (pure host code: fake, aligned, non-NULL pointers suffice)."""
+    import sys
+
+    import torch
+
+    sys.path.insert(0, str(ROOT / "megakernels_b200" / "native"))
+    import mk_llama
+
+    lib = mk_llama.load_library()
+    lib.mkb_validate_instructions.argtypes = [ctypes.POINTER(mk_llama.MkbGlobals), ctypes.c_void_p]
+    lib.mkb_validate_instructions.restype = ctypes.c_int
+    g = mk_llama.MkbGlobals()
+    g.abi_version = mk_llama.MKB_ABI_VERSION
+    g.struct_bytes = ctypes.sizeof(mk_llama.MkbGlobals)
+    fake = 0x10000
+    for name, ctype in mk_llama.MkbGlobals._fields_:
+        if ctype is ctypes.c_void_p and name not in ("timings", "status", "pos_id_device", "argmax_out"):
+            setattr(g, name, fake)
+    g.num_sms, g.queue_len, g.barrier_ops, g.barrier_width = 1, 2, 10, 48
+    g.num_layers, g.hidden_size, g.intermediate_size, g.head_dim = 2, 2048, 8192, 64
+    g.num_attention_heads, g.num_kv_heads, g.vocab_size = 32, 8, 128256
+    g.kv_max_len, g.kv_batch, g.max_partials, g.matvec_reduction_size = 128, 1, 4, 2048
+    ins = torch.zeros(1, 2, 32, dtype=torch.int32)
+    ins[0, 0, :5] = torch.tensor([8, 1, 0, 3, 4])
+
+    def check():
+        rc = lib.mkb_validate_instructions(ctypes.byref(g), ctypes.c_void_p(ins.data_ptr()))
+        return rc, lib.mkb_last_error().decode()
+
+    rc, msg = check()
+    assert rc == 1 and "without tensor parallelism" in msg
+    g.tp.size, g.tp.rank, g.tp.num_chunks = 2, 1, 4
+    for r in range(2):
+        g.tp.hidden_ll_peers[r] = fake
+        g.tp.recv_peers[r] = fake
+    g.tp.partial = fake
+    rc, msg = check()
+    assert rc == 1 and "epoch_device" in msg
+    g.tp.epoch_device = fake
+    assert check()[0] == 0
+    ins[0, 0, 3] = 4  # chunk == num_chunks
+    rc, msg = check()
+    assert rc == 1 and "chunk outside" in msg
+    ins[0, 0, 3] = 0
+    g.tp.num_chunks = 3  # not a multiple of the group size
+    rc, msg = check()
+    assert rc == 1 and "num_chunks" in msg

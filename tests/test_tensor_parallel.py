@@ -189,6 +189,37 @@ def test_all_reduce_instructions_follow_every_row_split_projection():
     assert not any(isinstance(i, TP_AllReduce) for i in plain.get_linear_instructions())
 
 
+@pytest.mark.parametrize("mode", ["rr", "zz", "wave", "dag"])
+def test_every_assignment_mode_keeps_all_reduce_chunks_in_order(mode):
+    """Whatever the SM assignment, within a queue an all-reduce chunk comes after the row-split
+    projections of its layer and before the RMSNorm op that consumes it (in-order queues)."""
+    from megakernels_b200.scheduler import assign_to_sms
+
+    set_sm_count_override(148)
+    model = build_model(LlamaConfig(**CFG), 64, tp_size=2, tp_rank=0)
+    sched = build_schedule(model, LatencyScheduleOptions(**PEER_OPTIONS))
+    queues = assign_to_sms(mode, schedule=sched)
+    seen = 0
+    for q in queues:
+        stage = {}  # layer -> furthest point reached: o-proj 0, ar0 1, upgate 2, down 3, ar1 4
+        for ins in q:
+            if isinstance(ins, TP_AllReduce):
+                seen += 1
+                rank_in_layer = 1 if ins.which == 0 else 4
+            elif isinstance(ins, O_ProjResidual):
+                rank_in_layer = 0
+            elif isinstance(ins, LayerNormDoubleMatVecSiLU):
+                rank_in_layer = 2
+            elif isinstance(ins, DownProjResidual):
+                rank_in_layer = 3
+            else:
+                continue
+            layer = ins.layer_idx
+            assert stage.get(layer, -1) <= rank_in_layer, f"{mode}: {ins} after stage {stage[layer]}"
+            stage[layer] = rank_in_layer
+    assert seen == 2 * CFG["num_hidden_layers"] * 4
+
+
 def _attach_cpu_exchange(globs):
     """What megakernels_b200.peer.connect does on GPUs, for the CPU checker: local buffers
     and a gloo sum standing in for the stores into peer memory."""
