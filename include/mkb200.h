@@ -270,7 +270,9 @@ int mkb_validate_instructions(const MkbGlobals *g, const int32_t *host_instructi
  *  - the first call on each device looks up the array's device address and sets a
  *    kernel attribute; make that first call outside any stream capture;
  *  - every call shares the one array and it keeps the previous call's contents: two
- *    calls whose kernels overlap on the GPU (different streams, no ordering) race.
+ *    calls whose kernels overlap on the GPU (different streams, no ordering) race;
+ *  - `g->tp.size` > 1 returns MKB_ERR_UNSUPPORTED (the tensor-parallel exchange needs
+ *    peer-mapped buffers, which somebody has to allocate), and `g->argmax_out` is ignored.
  */
 #define MKB_NO_ALLOC_SCRATCH_BYTES (1u << 20)
 int mkb_launch_no_alloc(const MkbGlobals *g, void *cuda_stream);
