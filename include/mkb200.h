@@ -104,7 +104,12 @@ enum {
  * counter or a reset: a tag is derived from (*epoch_device, layer, which), so every all-reduce
  * of every launch has its own.  `*epoch_device` must be the number of launches completed so
  * far on this rank group (same value on all ranks; the caller increments it after every
- * launch).  hidden_states keeps its meaning as the kernel's INPUT (the token embedding); the
+ * launch).  Recovery rule: a launch that ends in an error may already have stored sums
+ * tagged with the current value, so before the next launch EVERY rank must set
+ * `*epoch_device` to a value larger than any rank has used (the maximum over ranks plus
+ * one, agreed through a host-side collective); a rank that merely increments its own
+ * counter either reuses the aborted launch's tags or drifts apart from its peers.
+ * hidden_states keeps its meaning as the kernel's INPUT (the token embedding); the
  * running residual stream of a tensor-parallel launch lives in the tagged buffer.
  * Every peer pointer must be valid on THIS device (cudaIpcOpenMemHandle or an equivalent
  * mapping with peer access enabled); entry `rank` is the local buffer.  All buffers must be
@@ -130,6 +135,10 @@ typedef struct MkbTensorParallel {
  * (megakernels/instructions.py:10-69, demos/latency/instructions.py:9-29).
  * Model dimensions are run-time values (the reference compiles them in,
  * llama.cuh:15-26); under tensor parallelism they are the per-rank values.
+ * This build instantiates its pipelines for hidden_size 2048, 4096 or 8192,
+ * head_dim 64 or 128, a GQA ratio of 4 (or 8 with head_dim 128) and
+ * matvec_reduction_size 512, 1024 or 2048; anything else is refused with
+ * MKB_ERR_UNSUPPORTED before a launch.
  */
 typedef struct MkbGlobals {
     uint32_t abi_version; /* MKB_ABI_VERSION */
@@ -159,7 +168,9 @@ typedef struct MkbGlobals {
     void *k_cache;
     void *v_cache;
 
-    /* ---- RoPE tables, fp32 [>= pos_id+1, D], interleaved pair layout ---- */
+    /* ---- RoPE tables, fp32 [>= pos_id+1, D] (>= kv_max_len rows when pos_id_device is
+     * used: the kernel checks a device-side position against kv_max_len only),
+     * interleaved pair layout ---- */
     const float *rope_cos;
     const float *rope_sin;
 
@@ -264,9 +275,11 @@ int mkb_validate_instructions(const MkbGlobals *g, const int32_t *host_instructi
  *    scratch: 256 + roundup256(Hq * max_partials * 4) + Hq * max_partials * D * 4
  *    bytes must fit MKB_NO_ALLOC_SCRATCH_BYTES (e.g. Hq 64, 24 partials, D 128),
  *    otherwise MKB_ERR_UNSUPPORTED is returned and nothing is launched;
- *  - `g->status` may point at MKB_STATUS_WORDS int32 of caller memory, which
- *    mkb_sync_status(g, ...) can then read back; with NULL the record is kept inside
- *    the static array, cleared on every call, and is not readable through this ABI;
+ *  - `g->status` may point at MKB_STATUS_WORDS int32 of caller memory; with NULL the
+ *    record is kept inside the static array and cleared on every call.  Either way
+ *    mkb_sync_status_no_alloc(g, ...) reads it back without allocating (so does
+ *    mkb_sync_status when `g->status` is caller memory; with NULL that function reads
+ *    the allocating entry point's own record, which it creates on first use);
  *  - the first call on each device looks up the array's device address and sets a
  *    kernel attribute; make that first call outside any stream capture;
  *  - every call shares the one array and it keeps the previous call's contents: two
@@ -276,6 +289,14 @@ int mkb_validate_instructions(const MkbGlobals *g, const int32_t *host_instructi
  */
 #define MKB_NO_ALLOC_SCRATCH_BYTES (1u << 20)
 int mkb_launch_no_alloc(const MkbGlobals *g, void *cuda_stream);
+
+/*
+ * mkb_sync_status for callers of mkb_launch_no_alloc (no counterpart in the reference):
+ * synchronises `cuda_stream` and copies out the record the last no-alloc launch on the
+ * current device used - `g->status` if the caller supplied one, otherwise the record in
+ * the static array.  Calls no allocator; goes through a buffer on the host stack.
+ */
+int mkb_sync_status_no_alloc(const MkbGlobals *g, void *cuda_stream, MkbStatus *out);
 
 /*
  * Peer-visible device memory for MkbTensorParallel (no counterpart in the reference).

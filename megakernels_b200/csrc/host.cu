@@ -375,6 +375,22 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     return MKB_OK;
 }
 
+// Synchronise the stream, copy the status record at `st` (device memory) into `out` through a
+// stack buffer, re-arm it when it holds an error.  Allocates nothing.
+int read_status(int* st, void* cuda_stream, MkbStatus* out) {
+    MKB_CUDA(cudaStreamSynchronize((cudaStream_t)cuda_stream));
+    int words[MKB_STATUS_WORDS];
+    MKB_CUDA(cudaMemcpy(words, st, sizeof(words), cudaMemcpyDeviceToHost));
+    memcpy(out, words, sizeof(MkbStatus));
+    if (words[0] == MKB_OK && words[kStatusAbortWord] == 0) return MKB_OK;
+    MKB_CUDA(cudaMemset(st, 0, sizeof(words)));  // re-arm for the next launch
+    static const char* roles[] = {"loader", "consumer", "storer"};
+    const char* role = (out->role >= 0 && out->role < 3) ? roles[out->role] : "?";
+    return fail(out->code ? out->code : MKB_ERR_DEVICE_TIMEOUT,
+                "device error %d on queue %d, instruction %d (opcode %d, %s): detail %d %d %d %d",
+                out->code, out->sm, out->instruction_index, out->opcode, role, out->detail[0],
+                out->detail[1], out->detail[2], out->detail[3]);
+}
 
 }  // namespace
 
@@ -384,6 +400,8 @@ int prepare_launch_uncached(const MkbGlobals* g, int* status, int sm_count, KPar
     return prepare_launch(g, nullptr, status, sm_count, p);
 }
 int set_error(int code, const char* msg) { return fail(code, "%s", msg); }
+int read_status_record(int* st, void* cuda_stream, MkbStatus* out) { return read_status(st, cuda_stream, out); }
+std::mutex& library_mutex() { return g_mutex; }
 }  // namespace mkb
 
 extern "C" {
@@ -396,10 +414,7 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     KParams p;
     rc = prepare_launch(g, ds, (g && g->status) ? g->status : ds->status, ds->sm_count, p);
     if (rc) return rc;
-    // MKB_FORCE_TP_KERNEL: run single-GPU work through the tensor-parallel build (to measure what
-    // carrying the exchange code costs the streaming path)
-    static const bool force_tp_kernel = getenv("MKB_FORCE_TP_KERNEL") != nullptr;
-    if (p.tp_size > 1 || force_tp_kernel)
+    if (p.tp_size > 1)
         megakernel_tp<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     else
         megakernel<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
@@ -412,26 +427,23 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
 int mkb_sync_status(const MkbGlobals* g, void* cuda_stream, MkbStatus* out) {
     if (!out) return fail(MKB_ERR_INVALID_ARGUMENT, "status output pointer is NULL");
     std::lock_guard<std::mutex> lock(g_mutex);
-    DeviceState* ds = nullptr;
-    int rc = device_state(&ds);
-    if (rc) return rc;
-    MKB_CUDA(cudaStreamSynchronize((cudaStream_t)cuda_stream));
-    int* st = (g && g->status) ? g->status : ds->status;
-    int words[MKB_STATUS_WORDS];
-    MKB_CUDA(cudaMemcpy(words, st, sizeof(words), cudaMemcpyDeviceToHost));
-    memcpy(out, words, sizeof(MkbStatus));
-    if (words[0] != MKB_OK || words[kStatusAbortWord] != 0) {
-        MKB_CUDA(cudaMemset(st, 0, sizeof(words)));  // re-arm for the next launch
-        // an aborted launch may have left the fused-argmax arrival counter short of a full round
-        MKB_CUDA(cudaMemset(ds->status + MKB_STATUS_WORDS, 0, sizeof(int)));
-        static const char* roles[] = {"loader", "consumer", "storer"};
-        const char* role = (out->role >= 0 && out->role < 3) ? roles[out->role] : "?";
-        return fail(out->code ? out->code : MKB_ERR_DEVICE_TIMEOUT,
-                    "device error %d on queue %d, instruction %d (opcode %d, %s): detail %d %d %d %d",
-                    out->code, out->sm, out->instruction_index, out->opcode, role, out->detail[0],
-                    out->detail[1], out->detail[2], out->detail[3]);
+    int dev = 0;
+    MKB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MKB_ERR_UNSUPPORTED, "device index %d", dev);
+    // A record in caller memory is read without touching the library's per-device state, so
+    // that this call allocates nothing (it is the read-back path of mkb_launch_no_alloc).
+    int* st = (g && g->status) ? g->status : nullptr;
+    if (!st) {
+        DeviceState* ds = nullptr;
+        int rc = device_state(&ds);
+        if (rc) return rc;
+        st = ds->status;
     }
-    return MKB_OK;
+    int rc = read_status(st, cuda_stream, out);
+    // an aborted launch may have left the fused-argmax arrival counter short of a full round
+    if (rc != MKB_OK && g_devices[dev].attr_set)
+        cudaMemset(g_devices[dev].status + MKB_STATUS_WORDS, 0, sizeof(int));
+    return rc;
 }
 
 // Host-side check of an instruction tensor (a HOST copy, [num_sms, queue_len, 32]):

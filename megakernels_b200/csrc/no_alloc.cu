@@ -11,6 +11,7 @@
 // none of that: the scratch and the status record live in one file-scope
 // `__device__` array that every GPU loading this library holds until exit.
 #include <cstring>
+#include <mutex>
 
 #include "mk_common.cuh"
 
@@ -18,6 +19,8 @@ namespace mkb {
 __global__ void megakernel(const __grid_constant__ KParams p);
 int prepare_launch_uncached(const MkbGlobals* g, int* status, int sm_count, KParams& p);
 int set_error(int code, const char* msg);
+int read_status_record(int* st, void* cuda_stream, MkbStatus* out);
+std::mutex& library_mutex();
 }  // namespace mkb
 
 using namespace mkb;
@@ -41,7 +44,8 @@ size_t round256(size_t n) { return (n + 255) & ~size_t(255); }
 
 // In host code `g_static_scratch` is only a stand-in for the symbol, not a device
 // address; the address each device uses must be asked for, once, with that device
-// current.  Nothing here allocates: the array is part of the loaded module.
+// current.  Nothing here allocates: the array is part of the loaded module.  The caller
+// holds the library mutex (two host threads may make the first call on a device together).
 int setup_device(int dev, PerDevice** out) {
     PerDevice& pd = g_per_device[dev];
     if (!pd.ready) {
@@ -66,6 +70,11 @@ int setup_device(int dev, PerDevice** out) {
 
 extern "C" int mkb_launch_no_alloc(const MkbGlobals* g, void* cuda_stream) {
     if (!g) return set_error(MKB_ERR_INVALID_ARGUMENT, "globals pointer is NULL");
+    // the two leading words say how much of *g may be read at all: check them before anything else
+    if (g->abi_version != MKB_ABI_VERSION || g->struct_bytes != sizeof(MkbGlobals))
+        return set_error(MKB_ERR_INVALID_ARGUMENT,
+                         "abi_version / struct_bytes do not match this library's MkbGlobals");
+    std::lock_guard<std::mutex> lock(library_mutex());
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
         return set_error(MKB_ERR_CUDA, "cudaGetDevice failed");
@@ -104,4 +113,23 @@ extern "C" int mkb_launch_no_alloc(const MkbGlobals* g, void* cuda_stream) {
     megakernel<<<local.num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return set_error(MKB_ERR_CUDA, "kernel launch failed");
     return MKB_OK;
+}
+
+// Read-back for mkb_launch_no_alloc, equally free of allocations: the record the last call on
+// this device wrote - `g->status` when the caller passed one, else the one inside the static
+// array (which only exists once mkb_launch_no_alloc has run on this device).
+extern "C" int mkb_sync_status_no_alloc(const MkbGlobals* g, void* cuda_stream, MkbStatus* out) {
+    if (!out) return set_error(MKB_ERR_INVALID_ARGUMENT, "status output pointer is NULL");
+    std::lock_guard<std::mutex> lock(library_mutex());
+    int* st = (g && g->status) ? g->status : nullptr;
+    if (!st) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+            return set_error(MKB_ERR_CUDA, "cudaGetDevice failed");
+        if (!g_per_device[dev].ready)
+            return set_error(MKB_ERR_INVALID_ARGUMENT,
+                             "mkb_launch_no_alloc has not run on this device: no built-in status record");
+        st = reinterpret_cast<int*>(g_per_device[dev].scratch);
+    }
+    return read_status_record(st, cuda_stream, out);
 }

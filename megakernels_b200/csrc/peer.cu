@@ -1,8 +1,9 @@
 // Peer-visible device memory for the in-kernel tensor-parallel all-reduce.
 //
-// The reference has nothing of the kind (one GPU).  The exchange needs three small
-// buffers per rank that the other ranks' kernels can store into: the residual stream,
-// a receive buffer and arrival counters.  Ranks are separate processes (one per GPU), so
+// The reference has nothing of the kind (one GPU).  The exchange needs two small
+// buffers per rank that the other ranks' kernels can store into: the tagged residual
+// stream and a receive buffer for partial sums (every value carries its own tag, so
+// there are no arrival counters).  Ranks are separate processes (one per GPU), so
 // the memory is shared with CUDA IPC handles; the 64-byte handle travels through the
 // host's own channel.  Host-only code: nothing here launches a kernel.
 #include <cuda_runtime.h>

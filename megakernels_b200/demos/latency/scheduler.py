@@ -48,9 +48,6 @@ class LatencyScheduleOptions:
 
     num_attention_partitions: int = 1
     coalesce_o_proj: bool = False
-    # block split and SM mapping from a per-SM timeline model (demos/latency/balanced.py);
-    # the resulting stream must be assigned with assign_to_sms("hint", ...)
-    balance: bool = False
     # > 0 on a tensor-parallel shard: all-reduce the residual stream inside the kernel,
     # split into this many chunks (a multiple of the TP degree); 0 leaves the exchange
     # to the host (generators.TP_MK_Generator cuts the stream and calls NCCL)
@@ -348,11 +345,6 @@ def make_dag(
     options: LatencyScheduleOptions | None = None,
 ):
     """Reference: megakernels/demos/latency/scheduler.py:235-267."""
-    if options is not None and options.balance:
-        from megakernels_b200.demos.latency.balanced import make_balanced_dag
-
-        assert stop_after_op is None, "the balanced builder emits whole layers"
-        return make_balanced_dag(globs, options, layer_limit)
     nodes: list[DAG_Node] = []
     nlayers = globs.num_hidden_layers if layer_limit is None else layer_limit
     last_outputs: list[DAG_Node] = []
@@ -391,7 +383,6 @@ class LatencyScheduleBuilder(ScheduleBuilder):
         globs = make_globals(model, skip_attn_reduction=skip)
         extra = model.extra_config
         if self.options.tp_all_reduce_chunks and extra.tp_size > 1:
-            assert not self.options.balance, "the balanced builder has no all-reduce instructions"
             globs.tp = TensorParallelState(extra.tp_size, extra.tp_rank, self.options.tp_all_reduce_chunks)
         return globs
 

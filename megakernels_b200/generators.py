@@ -273,10 +273,16 @@ class TP_Peer_MK_Generator(MK_Generator):
     (``ExtraModelConfig(tp_size, tp_rank)``), which puts ``TP_AllReduce``
     instructions after every o-proj and down-proj group; this class attaches the
     peer-mapped buffers (``megakernels_b200.peer.connect``, a collective over
-    ``group``) and keeps the launch counter the device-side protocol compares
-    its arrival counters against.  All ranks must call ``run`` the same number of
+    ``group``) and keeps the launch counter from which the device derives the tag
+    of every exchanged value.  All ranks must call ``run`` the same number of
     times; the ranks' kernels wait for each other with a time budget, so a rank
     that stops shows up as ``MegakernelError`` (device timeout) on the others.
+
+    Recovery rule (include/mkb200.h, MkbTensorParallel): a launch that was aborted
+    has already stored partial sums carrying the current launch counter's tags.
+    Before the next launch every rank must therefore move to a counter value no
+    rank has used yet: ``check`` (a collective) does that whenever any rank
+    reports an error, ``resync_epoch`` does it unconditionally.
     """
 
     def __init__(self, model, interpreter, schedule, group=None):
@@ -297,6 +303,46 @@ class TP_Peer_MK_Generator(MK_Generator):
             return self._replay(input_ids, pos_id)  # the captured step includes the increment
         self.schedule.globs.pos_id = pos_id
         return self._step(input_ids)
+
+    def resync_epoch(self) -> int:
+        """Collective: set every rank's launch counter to (max over ranks) + 1.
+
+        Tags of an aborted launch can then never match again, whatever subset of
+        the ranks took part in it.  Returns the new value.
+        """
+        import torch.distributed as dist
+
+        tp = self.schedule.globs.tp
+        top = tp.epoch_device.clone()
+        dist.all_reduce(top, op=dist.ReduceOp.MAX, group=self.group)
+        tp.epoch_device.copy_(top + 1)
+        return int(tp.epoch_device)
+
+    def check(self):
+        """Collective status check: synchronise, learn whether ANY rank's launch gave up,
+        and if so resynchronise the launch counters before raising.
+
+        Raises the rank's own ``MegakernelError``, or ``RuntimeError`` on ranks whose
+        launch ran clean while a peer's did not.
+        """
+        import torch.distributed as dist
+
+        import mk_llama
+
+        err = None
+        try:
+            status = super().check()
+        except mk_llama.MegakernelError as e:
+            status, err = None, e
+        device = self.schedule.globs.hidden_states.device
+        failed = torch.tensor([1 if err is not None else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(failed, op=dist.ReduceOp.MAX, group=self.group)
+        if int(failed):
+            self.resync_epoch()
+            if err is not None:
+                raise err
+            raise RuntimeError("a tensor-parallel peer reported a device error; launch counters resynchronised")
+        return status
 
     def close(self):
         self._graph = None

@@ -147,6 +147,8 @@ def load_library() -> ctypes.CDLL:
         ctypes.POINTER(MkbStatus),
     ]
     lib.mkb_sync_status.restype = ctypes.c_int
+    lib.mkb_sync_status_no_alloc.argtypes = lib.mkb_sync_status.argtypes
+    lib.mkb_sync_status_no_alloc.restype = ctypes.c_int
     lib.mkb_peer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
     lib.mkb_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
     lib.mkb_peer_close.argtypes = [ctypes.c_void_p]
@@ -169,6 +171,12 @@ def _check_tensor(name, t, dtype, ndim=None):
         raise TypeError(f"{name} must be a torch.Tensor")
     if not t.is_cuda:
         raise ValueError(f"{name} must live on a CUDA device")
+    # the launch goes to the current device: a tensor elsewhere would be a wild pointer there
+    if t.device.index != torch.cuda.current_device():
+        raise ValueError(
+            f"{name} lives on cuda:{t.device.index} but the current device is "
+            f"cuda:{torch.cuda.current_device()} (wrap the call in torch.cuda.device(...))"
+        )
     if t.dtype != dtype:
         raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
     if not t.is_contiguous():
@@ -287,6 +295,12 @@ def pack_globals(
         raise ValueError("rope tables must be [positions, head_dim]")
     if pos_id_device is not None:
         g.pos_id_device = _check_tensor("pos_id_device", pos_id_device, i32)
+        # the kernel bounds a device-side position by the KV length only, so the RoPE
+        # tables must cover every position the cache can hold
+        if rope_cos.shape[0] < T:
+            raise ValueError(
+                f"with pos_id_device the rope tables need >= kv_max_len = {T} rows, got {rope_cos.shape[0]}"
+            )
     elif rope_cos.shape[0] <= int(pos_id):
         raise ValueError(f"rope tables have {rope_cos.shape[0]} rows, pos_id is {pos_id}")
     if matvec_reduction_size is None:
@@ -400,11 +414,17 @@ def peer_free(ptr: int) -> None:
     load_library().mkb_peer_free(ctypes.c_void_p(ptr))
 
 
-def sync_status(g: MkbGlobals, stream=None) -> MkbStatus:
-    """Synchronise the stream and return the device status; raise on device errors."""
+def sync_status(g: MkbGlobals, stream=None, no_alloc: bool = False) -> MkbStatus:
+    """Synchronise the stream and return the device status; raise on device errors.
+
+    ``no_alloc`` selects ``mkb_sync_status_no_alloc``, the read-back that belongs to
+    :func:`mk_llama_no_alloc` (it finds the record in the library's static array when the
+    caller passed no ``status`` tensor, and never allocates).
+    """
     lib = load_library()
     st = MkbStatus()
-    rc = lib.mkb_sync_status(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)), ctypes.byref(st))
+    fn = lib.mkb_sync_status_no_alloc if no_alloc else lib.mkb_sync_status
+    rc = fn(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)), ctypes.byref(st))
     if rc != 0:
         msg = lib.mkb_last_error().decode()
         raise MegakernelError(rc, msg, st)

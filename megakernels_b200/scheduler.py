@@ -171,18 +171,6 @@ def pool_assign_to_sms(instructions: list[Instruction], sm_count: int, memory_fr
     )
 
 
-def hint_assign_to_sms(instructions: list[Instruction], sm_count: int):
-    """Every instruction goes to the SM its builder pinned it to (``sm_hint``).
-
-    Used with the timeline-model builder (demos/latency/balanced.py), which
-    decides the block split and the SM together.  No counterpart in the reference.
-    """
-    queues: list[list[Instruction]] = [[] for _ in range(sm_count)]
-    for ins in instructions:
-        queues[ins.sm_hint % sm_count].append(ins)
-    return queues
-
-
 def assign_to_sms(
     mode: str,
     schedule: Schedule | None = None,
@@ -202,8 +190,6 @@ def assign_to_sms(
         return wave_assign_to_sms(schedule)
     if mode == "dag":
         return assign_dag_to_sms(schedule)
-    if mode == "hint":
-        return hint_assign_to_sms(instructions, sm_count)
     if mode == "pool":
         assert memory_fraction is not None
         return pool_assign_to_sms(instructions, sm_count, memory_fraction=memory_fraction)

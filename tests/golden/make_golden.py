@@ -36,7 +36,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("MK_REFERENCE_DIR", "/root/reference"))
+if "MK_REFERENCE_DIR" not in os.environ:
+    raise SystemExit("set MK_REFERENCE_DIR to a checkout of the reference (HazyResearch/Megakernels)")
+REF = Path(os.environ["MK_REFERENCE_DIR"])
 sys.path.insert(0, str(REPO))
 sys.path.insert(0, str(REF))
 

@@ -17,7 +17,7 @@ def test_header_declares_the_expected_entry_points():
     names = declared_functions()
     for must in ("mkb_launch", "mkb_sync_status", "mkb_validate_instructions", "mkb_last_error",
                  "mkb_sm_count", "mkb_smem_bytes", "mkb_block_threads", "mkb_abi_version",
-                 "mkb_launch_no_alloc", "mkb_peer_alloc", "mkb_peer_open", "mkb_peer_close", "mkb_peer_free"):
+                 "mkb_launch_no_alloc", "mkb_sync_status_no_alloc", "mkb_peer_alloc", "mkb_peer_open", "mkb_peer_close", "mkb_peer_free"):
         assert must in names
 
 

@@ -292,23 +292,3 @@ def test_fused_argmax_equals_torch_argmax_of_the_logits():
     assert gpu_sched2.globs.argmax_out is None
     got = gen2.run(torch.tensor([[toks[0]]], device="cuda:0"), 0)
     assert int(got) == int(torch.argmax(gpu_sched2.globs.logits))
-
-
-@pytest.mark.parametrize("shape", ["1b", "8b"])
-def test_balanced_schedule_matches_oracle(shape):
-    """The timeline-model builder (pinned SMs, overlapping up/gate and down-proj)."""
-    cfg = small_1b() if shape == "1b" else small_8b()
-    opts = LatencyScheduleOptions(num_attention_partitions=3, coalesce_o_proj=True, balance=True)
-    cpu_model, cpu_sched, gpu_model, gpu_sched = make_pair(cfg, 300, 280, options=opts, sched="hint")
-    embed = cpu_model.model.embed_tokens.embed_tokens.weight
-    for i, tok in enumerate(seeded_tokens(cfg.vocab_size, 2)):
-        pos = 280 + i
-        run_cpu_step(cpu_model, cpu_sched, embed[tok], pos)
-        st = run_gpu_step(gpu_sched, embed[tok], pos)
-        assert st.code == 0
-        # At the 8B widths this case (280 random N(0,1) KV positions, sharp softmax) puts the
-        # intermediates at 1.8e-2 .. 2.1e-2 of their range from run to run (bf16 atomic order), so
-        # the bisecting bound is 3e-2 here; the acceptance check on the logits stays at 2e-2.
-        compare_globals(gpu_sched.globs, cpu_sched.globs, pos, tol=3e-2)
-        assert_logits_parity(gpu_sched.globs.logits, cpu_sched.globs.logits, f"pos {pos}")
-        assert torch.equal(gpu_sched.globs.barriers.cpu(), cpu_sched.globs.barriers)

@@ -352,9 +352,14 @@ def _peer_rank_with_a_silent_peer(rank, world, port, tokens, out):
         except mk_llama.MegakernelError as err:
             verdict = f"code {err.code} opcode {err.status.opcode}"
     dist.barrier()  # rank 1 sat here on the host the whole time, nothing of it in flight
-    # the context is still usable and the exchange recovers: a normal step on both ranks
+    # Recovery rule: the aborted launch left partial sums with the current launch counter's
+    # tags in the owners' receive buffers, so both ranks move to a counter value nobody used.
+    assert gen.resync_epoch() == 1
+    # the context is still usable and the exchange recovers.  The retry decodes a DIFFERENT
+    # token than the aborted launch (same position, so the half-written K/V row is
+    # overwritten): stale sums taken for fresh ones would now show in the logits
     logits = []
-    for i, tok in enumerate(tokens):
+    for i, tok in enumerate(tokens[1:]):
         gen.run(torch.tensor([[tok]], device=dev), PREFILL + i)
         gen.check()
         logits.append(g.logits.cpu())
@@ -371,10 +376,10 @@ def test_peer_rank_that_never_launches_is_reported_not_hung(tmp_path):
     host (it simply does not launch); the waiting rank's polls are bounded."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    tokens = seeded_tokens(CFG["vocab_size"], 2)
+    tokens = seeded_tokens(CFG["vocab_size"], 3)
     out = tmp_path / "result.pt"
     mp.spawn(_peer_rank_with_a_silent_peer, args=(2, 29527, tokens, str(out)), nprocs=2, join=True)
     verdict, logits = torch.load(out)
     assert verdict.startswith("code 3"), verdict  # MKB_ERR_DEVICE_TIMEOUT
-    for a, b in zip(logits, reference_logits(tokens)):
+    for a, b in zip(logits, reference_logits(tokens[1:])):
         assert_logits_parity(a, b, "tp=2 after a timed-out launch")
