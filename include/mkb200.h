@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define MKB_ABI_VERSION 2
+#define MKB_ABI_VERSION 3
 
 /* instruction encoding (megakernels/scheduler.py:13-14) */
 #define MKB_INTS_PER_INSTRUCTION 32
@@ -46,6 +46,14 @@ enum {
      * words: [8, layer, which (0 after o-proj, 1 after down-proj), chunk, num_chunks] */
     MKB_OP_TP_ALL_REDUCE = 8,
 };
+
+/* Barrier rows: opcode k counts into row k - 1 (rows 0..6), as in the reference.  Row 8 has
+ * no counterpart there: every RMS + up/gate instruction bumps barriers[layer][8][0] once its
+ * read of the residual stream is complete, and the down-proj of that layer, which adds to the
+ * residual stream, waits for MkbGlobals.upgate_instructions_per_layer arrivals (the reference
+ * orders down-proj after the up/gate blocks of its input slice only, matvec_adds.cu:181-186,
+ * which leaves a slow SM reading a residual that already holds part of the layer's output). */
+#define MKB_BARRIER_ROW_RMS_READ 8
 
 /* MkbGlobals.flags */
 #define MKB_FLAG_RECORD_TIMINGS 1u /* write per-instruction event times (ns) into `timings` */
@@ -175,7 +183,11 @@ typedef struct MkbGlobals {
     const float *rope_sin;
 
     /* ---- activations ---- */
-    void *hidden_states;            /* bf16 [H]        in/out: residual stream */
+    void *hidden_states;            /* bf16 [H]  input: the token embedding.  The reference's kernel
+                                       adds every o-proj / down-proj output into this vector with
+                                       bf16 atomics (matvec_adds.cu:78), whose rounding depends on the
+                                       arrival order; here it is never written, the outputs are summed
+                                       in `residual_acc` */
     void *post_ln_rope_q;           /* bf16 [Hq*D] */
     void *attn_out;                 /* bf16 [Hq*D] */
     float *attn_lse_intermediates;  /* fp32 [Hq, max_partials] */
@@ -205,9 +217,22 @@ typedef struct MkbGlobals {
     /* ---- extensions without a counterpart in the reference call ---- */
     const int32_t *pos_id_device; /* if not NULL the position is read from this device word at
                                      kernel start (lets one CUDA graph replay every token) */
-    float residual_scale;         /* o-proj / down-proj outputs are multiplied by this before the
-                                     residual add; 0 means 1.  Tensor-parallel ranks set it to the
-                                     TP degree and average their residual streams afterwards */
+    float residual_scale;         /* integer factor (as a float) on every o-proj / down-proj output
+                                     added to `residual_acc`; 0 means 1.  Tensor-parallel ranks that
+                                     exchange through the host set it to the TP degree, sum their
+                                     accumulators over ranks and divide by the degree (exact) */
+    int64_t *residual_acc;        /* int64 [H], zeroed by the caller before every launch like the
+                                     barriers: sum of the token's o-proj / down-proj outputs in
+                                     Q31.32 fixed point (value * 2^32), accumulated with integer
+                                     atomics, so the result is independent of the order in which
+                                     SMs arrive and bit-identical from run to run.  The residual
+                                     stream after the launch is hidden_states + residual_acc / 2^32.
+                                     Not used (may be NULL) when tp.size > 1; with NULL,
+                                     mkb_launch_no_alloc keeps it in its static array */
+    int32_t upgate_instructions_per_layer; /* RMS + up/gate instructions per layer in `instructions`
+                                     (see MKB_BARRIER_ROW_RMS_READ); 0: down-proj does not wait for
+                                     them */
+    int32_t reserved0;
 
     MkbTensorParallel tp;         /* in-kernel tensor-parallel all-reduce; tp.size <= 1: off */
     int32_t *argmax_out;          /* if not NULL: device int32 that receives argmax(logits) (smallest
@@ -271,9 +296,11 @@ int mkb_validate_instructions(const MkbGlobals *g, const int32_t *host_instructi
  * MKB_NO_ALLOC_SCRATCH_BYTES that every GPU loading the library holds until exit.
  *
  *  - `g->attn_lse_intermediates` and `g->attn_out_intermediates` are ignored (may be
- *    NULL); `g->num_attention_heads`, `g->max_partials` and `g->head_dim` size the
- *    scratch: 256 + roundup256(Hq * max_partials * 4) + Hq * max_partials * D * 4
- *    bytes must fit MKB_NO_ALLOC_SCRATCH_BYTES (e.g. Hq 64, 24 partials, D 128),
+ *    NULL), and so may `g->residual_acc` (with NULL the accumulators live in the array
+ *    too and are cleared by every call); `g->hidden_size`, `g->num_attention_heads`,
+ *    `g->max_partials` and `g->head_dim` size the scratch:
+ *    256 + roundup256(H * 8) + roundup256(Hq * max_partials * 4) + Hq * max_partials * D * 4
+ *    bytes must fit MKB_NO_ALLOC_SCRATCH_BYTES (e.g. H 8192, Hq 64, 24 partials, D 128),
  *    otherwise MKB_ERR_UNSUPPORTED is returned and nothing is launched;
  *  - `g->status` may point at MKB_STATUS_WORDS int32 of caller memory; with NULL the
  *    record is kept inside the static array and cleared on every call.  Either way

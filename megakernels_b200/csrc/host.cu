@@ -213,7 +213,7 @@ int validate(const MkbGlobals* g) {
         return fail(MKB_ERR_INVALID_ARGUMENT, "o-proj inputs %d and intermediate %d must be multiples of %d", Hq * D, I, R);
     if (I % 16 != 0 || g->vocab_size % 16 != 0)
         return fail(MKB_ERR_INVALID_ARGUMENT, "intermediate and vocab sizes must be multiples of 16");
-    if (g->barrier_width < Hq + 2 * Hkv || g->barrier_width < I / R || g->barrier_ops < 6)
+    if (g->barrier_width < Hq + 2 * Hkv || g->barrier_width < I / R || g->barrier_ops < 7)
         return fail(MKB_ERR_INVALID_ARGUMENT, "barriers tensor too small: ops %d width %d", g->barrier_ops, g->barrier_width);
     if (g->kv_batch < 1 || g->kv_max_len < 1)
         return fail(MKB_ERR_INVALID_ARGUMENT, "KV cache needs batch >= 1 and length >= 1");
@@ -237,7 +237,15 @@ int validate(const MkbGlobals* g) {
         }
         if (!tp.partial || !aligned16(tp.partial)) return fail(MKB_ERR_INVALID_ARGUMENT, "tp: partial buffer is NULL or unaligned");
         if (!tp.epoch_device) return fail(MKB_ERR_INVALID_ARGUMENT, "tp: epoch_device is NULL");
+    } else {
+        if (!g->residual_acc || !aligned16(g->residual_acc))
+            return fail(MKB_ERR_INVALID_ARGUMENT, "residual_acc (int64 [H], zeroed per launch) is NULL or not 16-byte aligned");
+        if (g->residual_scale != 0.f && (g->residual_scale < 1.f || g->residual_scale != (float)(int)g->residual_scale))
+            return fail(MKB_ERR_INVALID_ARGUMENT, "residual_scale %g must be a positive integer", g->residual_scale);
     }
+    if (g->upgate_instructions_per_layer < 0 || g->barrier_ops <= MKB_BARRIER_ROW_RMS_READ)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "upgate_instructions_per_layer %d / barrier_ops %d (row %d is needed)",
+                    g->upgate_instructions_per_layer, g->barrier_ops, MKB_BARRIER_ROW_RMS_READ);
     return MKB_OK;
 }
 
@@ -319,7 +327,9 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     p.o_in = p.Hq * p.D;
     p.pos_id = g->pos_id;
     p.pos_id_ptr = g->pos_id_device;
-    p.residual_scale = g->residual_scale > 0.f ? g->residual_scale : 1.f;
+    p.residual_acc = (long long*)g->residual_acc;
+    p.residual_mult = g->residual_scale > 0.f ? (long long)g->residual_scale : 1;
+    p.thr_down_waits_rms = g->upgate_instructions_per_layer;
     if (g->argmax_out && ds) {  // the scratch sits behind the library's own status record
         p.argmax_out = g->argmax_out;
         p.argmax_scratch = ds->status + MKB_STATUS_WORDS;

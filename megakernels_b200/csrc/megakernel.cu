@@ -652,15 +652,20 @@ __device__ __forceinline__ void rms_prefetch(const Ctx& c, const __nv_bfloat16* 
 }
 // LL: the residual stream is read from this rank's tagged buffer (tensor parallelism), each
 // thread polling its own chunks until they carry `tag`; returns false if the wait was abandoned.
-template <bool LL>
+// Otherwise the residual stream is the token embedding in `hidden` plus, with ACC, the Q31.32
+// accumulators the row-split projections add into; `read_done` (may be null) is a counter
+// bumped once every thread's loads have completed, for producers that must not add to the
+// accumulators before this instruction has read them.
+template <bool LL, bool ACC>
 __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& pf, uint32_t tag = 0,
-                                               int layer = 0, int which = 0) {
+                                               int layer = 0, int which = 0, int* read_done = nullptr) {
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    uint4 xv[2];
+    float x[2][8];
     float ss = 0.f;
     bool ok = true;
     if constexpr (LL) {
+        uint4 xv[2];
         // 8 bf16 = four {bf16x2, tag} words = two 16-byte loads
         const uint4* ll = reinterpret_cast<const uint4*>(p.tp_hidden_ll[p.tp_rank]);
         TpPoll poll;
@@ -679,6 +684,7 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
                 }
             }
             xv[k] = make_uint4(a.x, a.z, b.x, b.z);
+            unpack8(xv[k], x[k]);
         }
         if (tid == 0) {
             c.cta_abort[4] = 0;
@@ -686,16 +692,32 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
         }
     } else {
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-            if (pf.chs[k] >= 0) xv[k] = ld_cg_v4(p.hidden + (size_t)pf.chs[k] * 8);
+        for (int k = 0; k < 2; ++k) {
+            if (pf.chs[k] < 0) continue;
+            const uint4 hv = ld_cg_v4(p.hidden + (size_t)pf.chs[k] * 8);
+            if constexpr (ACC) {
+                const long long* acc = p.residual_acc + (size_t)pf.chs[k] * 8;
+                uint4 a[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
+                unpack8(hv, x[k]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const long long lo = (long long)(((unsigned long long)a[i].y << 32) | a[i].x);
+                    const long long hi = (long long)(((unsigned long long)a[i].w << 32) | a[i].z);
+                    x[k][2 * i] += __ll2float_rn(lo) * kResidualInvScale;
+                    x[k][2 * i + 1] += __ll2float_rn(hi) * kResidualInvScale;
+                }
+            } else {
+                unpack8(hv, x[k]);
+            }
+        }
     }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         if (pf.chs[k] >= 0) {
-            float x[8];
-            unpack8(xv[k], x);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+            for (int e = 0; e < 8; ++e) ss = fmaf(x[k][e], x[k][e], ss);
         }
     }
 #pragma unroll
@@ -707,6 +729,9 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
         if (!consumer_all(ok)) return false;
     } else {
         consumer_sync();
+        // every thread's loads of the residual stream have returned (their values went into
+        // the sums above), so later writers may now be let in
+        if (tid == 0 && read_done != nullptr) red_release_gpu_add(read_done, 1);
     }
     if (tid == 0) rec(c, MKB_T_RMS_SUMMED);
     float tot = 0.f;
@@ -716,14 +741,13 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         if (pf.chs[k] >= 0) {
-            float x[8], wgt[8];
-            unpack8(xv[k], x);
+            float wgt[8];
             unpack8(pf.wv[k], wgt);
             uint32_t o[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-                o[e] = pack_bf16x2(wgt[2 * e] * bf16_round(x[2 * e] * rstd),
-                                   wgt[2 * e + 1] * bf16_round(x[2 * e + 1] * rstd));
+                o[e] = pack_bf16x2(wgt[2 * e] * bf16_round(x[k][2 * e] * rstd),
+                                   wgt[2 * e + 1] * bf16_round(x[k][2 * e + 1] * rstd));
             st_shared_v4(c.base + kSmemAttn + pf.chs[k] * 16, o[0], o[1], o[2], o[3]);
         }
     }
@@ -754,7 +778,11 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
 // Out of line: the polling loops would otherwise be inlined three times into the consumer loop.
 __device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefetch pf, int wait_layer,
                                                    int which) {
-    return rms_activation<true>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
+    return rms_activation<true, false>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
+}
+
+__device__ __noinline__ void rms_activation_plain(const Ctx& c, const RmsPrefetch pf, int* read_done) {
+    rms_activation<false, true>(c, pf, 0u, 0, 0, read_done);
 }
 
 // kTP selects the tensor-parallel build of the kernel.  It is a compile-time switch and the two
@@ -764,7 +792,7 @@ template <bool kTP>
 __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
                                                     const __nv_bfloat16* norm_w, int nblocks,
                                                     int wait_layer, int wait_row, int threshold,
-                                                    bool needed) {
+                                                    bool needed, int* read_done = nullptr) {
     RmsPrefetch pf;
     rms_prefetch(c, norm_w, pf);
     bool tagged = false;
@@ -778,18 +806,52 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
     }
     if (!tagged) {
         if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
-        rms_activation<false>(c, pf);
+        // the tensor-parallel exchange keeps the running residual stream in its tagged buffer;
+        // the only plain read there is the token embedding before the first all-reduce
+        if (kTP && c.p->tp_size > 1) rms_activation<false, false>(c, pf);
+        else rms_activation_plain(c, pf, read_done);
     }
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->H);
     return true;
 }
 
+// Warp 0 polls up to 32 counters in parallel (lane i: addr / threshold, nullptr = none); the
+// verdict reaches all 512 consumer threads through shared memory.
+__device__ __forceinline__ bool consumers_wait_lanes(const Ctx& c, ConsumerState& cs, const int* addr,
+                                                     int threshold, int layer, int row, int slot) {
+    volatile int* verdict = verdict_word(c, cs);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        bool ok = __shfl_sync(0xffffffffu, *c.cta_abort, 0) == 0;  // uniform over the warp
+        if (lane == 0) c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
+        ok = ok && warp_wait_counters(c, addr, threshold, layer, row, slot);
+        if (lane == 0) {
+            c.cta_abort[4] = 0;
+            rec(c, MKB_T_CONSUMER_WAIT_DONE);
+            *verdict = ok ? 1 : 0;
+        }
+    }
+    consumer_sync();
+    return *verdict != 0;
+}
+
+// `also` (may be null) is a second counter that must reach `also_threshold` before the vector
+// may be read or the outputs added: both are polled in the same round trips.
 __device__ __forceinline__ bool consumer_plain_matvec(const Ctx& c, ConsumerState& cs,
                                                       const __nv_bfloat16* vec, int nblocks,
                                                       int wait_layer, int wait_row, int wait_slot,
-                                                      int threshold) {
-    if (!consumers_wait_counter(c, cs, wait_layer, wait_row, wait_slot, threshold, true)) return false;
+                                                      int threshold, const int* also = nullptr,
+                                                      int also_threshold = 0) {
+    if (also != nullptr) {
+        const int lane = threadIdx.x & 31;
+        const int* addr = lane == 0 ? bar_addr(*c.p, wait_layer, wait_row, wait_slot) : lane == 1 ? also : nullptr;
+        if (!consumers_wait_lanes(c, cs, addr, lane == 1 ? also_threshold : threshold, wait_layer,
+                                  lane == 1 ? MKB_BARRIER_ROW_RMS_READ : wait_row, lane == 1 ? 0 : wait_slot))
+            return false;
+    } else if (!consumers_wait_counter(c, cs, wait_layer, wait_row, wait_slot, threshold, true)) {
+        return false;
+    }
     stage_activation(c, vec, c.p->R);
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->R);
@@ -1331,8 +1393,11 @@ __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const i
         }
         case MKB_OP_RMS_UPGATE_SILU: {
             const int layer = __ldg(w + 1), n = __ldg(w + 2);
+            // down-proj adds to the residual accumulators this instruction reads: it waits
+            // for one arrival per up/gate instruction on row MKB_BARRIER_ROW_RMS_READ
             return consumer_rms_matvec<kTP>(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
-                                       MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true);
+                                       MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true,
+                                       bar_addr(p, layer, MKB_BARRIER_ROW_RMS_READ, 0));
         }
         default: {  // MKB_OP_RMS_LM_HEAD
             const int sb = __ldg(w + 1), eb = __ldg(w + 2);
@@ -1348,8 +1413,13 @@ __device__ bool consumer_residual_op(const Ctx& c, ConsumerState& cs, int op, co
     if (op == MKB_OP_O_PROJ_RESIDUAL)
         return consumer_plain_matvec(c, cs, p.attn_out + (size_t)rb * p.R, eb - sb, layer,
                                      MKB_OP_ATTENTION_REDUCTION - 1, 0, p.thr_oproj_waits_attn);
+    // with tensor parallelism inside the kernel the outputs go to a partial-sum buffer nobody
+    // else is reading, so only the single-GPU residual needs the read-before-add ordering
+    const bool order = p.thr_down_waits_rms > 0 && p.tp_size <= 1;
     return consumer_plain_matvec(c, cs, p.silu_out + (size_t)rb * p.R, eb - sb, layer,
-                                 MKB_OP_RMS_UPGATE_SILU - 1, rb, p.thr_down_waits_upgate);
+                                 MKB_OP_RMS_UPGATE_SILU - 1, rb, p.thr_down_waits_upgate,
+                                 order ? bar_addr(p, layer, MKB_BARRIER_ROW_RMS_READ, 0) : nullptr,
+                                 p.thr_down_waits_rms);
 }
 
 template <bool kTP>
@@ -1574,12 +1644,15 @@ __device__ void storer_main(Ctx c) {
                     }
                 } else {
                     for (int b = sb; b < eb; ++b) {
-                        // residual_scale is the tensor-parallel degree when the host averages the
-                        // ranks' residual streams between launches (h + sum of the partials)
-                        const float v = storer_take_block(c, ss, lane, kr_partials) * p.residual_scale;
-                        const float hi = __shfl_down_sync(0xffffffffu, v, 1);
-                        if (lane < 16 && (lane & 1) == 0)
-                            red_add_bf16x2(p.hidden + b * kBlockRows + row, pack_bf16x2(v, hi));
+                        // Integer addition is associative: whatever order the column slices of
+                        // the SMs arrive in, the accumulator ends up with the same bits.
+                        // residual_mult is the tensor-parallel degree when the host averages the
+                        // ranks' accumulators between launches (sum of the partials after the
+                        // exact division), else 1.
+                        const float v = storer_take_block(c, ss, lane, kr_partials);
+                        if (lane < 16)
+                            red_add_u64(p.residual_acc + b * kBlockRows + row,
+                                        (unsigned long long)(__float2ll_rn(v * kResidualScale) * p.residual_mult));
                     }
                 }
                 storer_signal(ss, lane, bar_addr(p, layer, op - 1, 0), eb - sb);

@@ -73,6 +73,11 @@ struct KParams {
     const float *rope_cos, *rope_sin;
     __nv_bfloat16 *hidden, *q_rope, *attn_out, *silu_out, *logits;
     float *attn_lse, *attn_o;
+    // Residual stream of the token = hidden (the embedding, never written) + residual_acc:
+    // o-proj / down-proj add their outputs as 64-bit fixed point (Q31.32) with integer atomics,
+    // so the sum does not depend on the order in which the SMs arrive (bit-reproducible).
+    long long* residual_acc;  // [H], zeroed by the caller before every launch
+    long long residual_mult;  // integer factor on every contribution (1; the TP degree under the NCCL exchange)
     // dims
     int L, H, I, D, Hq, Hkv, V, T, B, max_partials, R;
     int qkv_rows;  // (Hq + 2 Hkv) * D
@@ -80,7 +85,6 @@ struct KParams {
     // per token
     int pos_id;
     const int* pos_id_ptr;   // when set, the position is read from device memory instead
-    float residual_scale;    // factor on o-proj / down-proj outputs before the residual add
     float attn_scale_log2e;  // attn_scale * log2(e)
     float rms_eps;
     int skip_attn_reduction;
@@ -100,6 +104,7 @@ struct KParams {
     int thr_oproj_waits_attn;   // Hq
     int thr_upgate_waits_oproj; // (H/16) * (o_in/R)
     int thr_down_waits_upgate;  // R/16
+    int thr_down_waits_rms;     // up/gate instructions of a layer (0: the schedule does not say)
     unsigned long long timeout_ns;
     int poll_sleep_ns;     // back-off between polls of a barrier counter
     int l2_window_stages;  // how many ring stages the loader may prefetch into L2 ahead of the ring
@@ -263,9 +268,12 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ void red_add_bf16x2(void* p, uint32_t packed) {
-    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(p), "r"(packed) : "memory");
+__device__ __forceinline__ void red_add_u64(void* p, unsigned long long v) {
+    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// fixed-point format of the residual accumulators: value * 2^32 in a signed 64-bit integer
+constexpr float kResidualScale = 4294967296.f;
+constexpr float kResidualInvScale = 1.f / 4294967296.f;
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -28,6 +28,7 @@ using namespace mkb;
 namespace {
 
 // [0, 256): status record (MKB_STATUS_WORDS int32, padded)
+// then ACC  [H] int64 residual accumulators (cleared on every call; only when the caller passes none)
 // then LSE  [Hq][max_partials] fp32, rounded up to 256 bytes
 // then O    [Hq][max_partials][D] fp32
 constexpr size_t kStatusBytes = 256;
@@ -87,9 +88,12 @@ extern "C" int mkb_launch_no_alloc(const MkbGlobals* g, void* cuda_stream) {
     if (g->num_attention_heads < 1 || g->max_partials < 1 || g->head_dim < 1)
         return set_error(MKB_ERR_INVALID_ARGUMENT,
                          "num_attention_heads, max_partials and head_dim must be positive");
+    if (g->hidden_size < 1)
+        return set_error(MKB_ERR_INVALID_ARGUMENT, "hidden_size must be positive");
+    const size_t acc_bytes = g->residual_acc ? 0 : round256((size_t)g->hidden_size * 8);
     const size_t lse_bytes = round256((size_t)g->num_attention_heads * g->max_partials * 4);
     const size_t o_bytes = (size_t)g->num_attention_heads * g->max_partials * g->head_dim * 4;
-    if (kStatusBytes + lse_bytes + o_bytes > (size_t)MKB_NO_ALLOC_SCRATCH_BYTES)
+    if (kStatusBytes + acc_bytes + lse_bytes + o_bytes > (size_t)MKB_NO_ALLOC_SCRATCH_BYTES)
         return set_error(MKB_ERR_UNSUPPORTED,
                          "mkb_launch_no_alloc: attention scratch for Hq x max_partials x head_dim "
                          "exceeds the built-in MKB_NO_ALLOC_SCRATCH_BYTES; lower max_partials or "
@@ -97,18 +101,24 @@ extern "C" int mkb_launch_no_alloc(const MkbGlobals* g, void* cuda_stream) {
 
     MkbGlobals local;
     memcpy(&local, g, sizeof(local));
-    local.attn_lse_intermediates = reinterpret_cast<float*>(pd->scratch + kStatusBytes);
-    local.attn_out_intermediates = reinterpret_cast<float*>(pd->scratch + kStatusBytes + lse_bytes);
+    if (!g->residual_acc) local.residual_acc = reinterpret_cast<int64_t*>(pd->scratch + kStatusBytes);
+    local.attn_lse_intermediates = reinterpret_cast<float*>(pd->scratch + kStatusBytes + acc_bytes);
+    local.attn_out_intermediates = reinterpret_cast<float*>(pd->scratch + kStatusBytes + acc_bytes + lse_bytes);
     int* status = g->status ? g->status : reinterpret_cast<int*>(pd->scratch);
 
     KParams p;
     rc = prepare_launch_uncached(&local, status, pd->sm_count, p);
     if (rc) return rc;
-    // The array keeps whatever the previous call left.  Only the built-in status
-    // record must start clean; the attention scratch is always written before it is read.
+    // The array keeps whatever the previous call left.  The built-in status record and the
+    // residual accumulators must start at zero; the attention scratch is always written
+    // before it is read.
     if (!g->status) {
         cudaError_t e = cudaMemsetAsync(pd->scratch, 0, kStatusBytes, (cudaStream_t)cuda_stream);
         if (e != cudaSuccess) return set_error(MKB_ERR_CUDA, "cudaMemsetAsync(status) failed");
+    }
+    if (acc_bytes) {
+        cudaError_t e = cudaMemsetAsync(pd->scratch + kStatusBytes, 0, acc_bytes, (cudaStream_t)cuda_stream);
+        if (e != cudaSuccess) return set_error(MKB_ERR_CUDA, "cudaMemsetAsync(residual accumulators) failed");
     }
     megakernel<<<local.num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return set_error(MKB_ERR_CUDA, "kernel launch failed");

@@ -55,6 +55,8 @@ def interpret_with_mk(globs: Globals, mk_func, stream=None, **kwargs):
         pos_id_device=globs.pos_id_device,
         tp=globs.tp,
         argmax_out=globs.argmax_out,
+        residual_acc=globs.residual_acc,
+        upgate_instructions_per_layer=globs.upgate_instructions_per_layer,
         **kwargs,
     )
 

@@ -97,11 +97,14 @@ def make_globals(model, skip_attn_reduction: bool = True, max_attn_partitions: i
     if max_attn_partitions is None:
         max_attn_partitions = get_sm_count(device)
 
-    barriers = torch.zeros(
-        [config.num_hidden_layers, 10, n_q + 2 * n_kv], dtype=torch.int32, device=device
-    )
+    # barrier counters and residual accumulators share one buffer: one fill resets both
+    bar_shape = [config.num_hidden_layers, 10, n_q + 2 * n_kv]
+    n_bar = math.prod(bar_shape)
+    acc_off = (n_bar + 3) // 4 * 4  # int64 view needs 8-byte, the kernel's loads 16-byte alignment
+    vm_state = torch.zeros(acc_off + 2 * config.hidden_size, dtype=torch.int32, device=device)
+    barriers = vm_state[:n_bar].view(bar_shape)
 
-    return Globals(
+    globs = Globals(
         qkv_proj_weights=sp.qkv_proj,
         o_proj_weights=sp.o_proj,
         attn_ln_weights=sp.attn_ln_weight,
@@ -148,6 +151,9 @@ def make_globals(model, skip_attn_reduction: bool = True, max_attn_partitions: i
         device=device,
         barriers=barriers,
     )
+    globs.vm_state = vm_state
+    globs.residual_acc = vm_state[acc_off:].view(torch.int64)
+    return globs
 
 
 def _even_ranges(num_blocks: int, parts: int):
@@ -376,6 +382,11 @@ class LatencyScheduleBuilder(ScheduleBuilder):
 
         globs = self.make_globals(model)
         nodes, end = make_dag(globs, stop_after_op, layer_limit, self.options)
+        globs.upgate_instructions_per_layer = sum(
+            1
+            for n in nodes
+            if isinstance(n.instruction, LayerNormDoubleMatVecSiLU) and n.instruction.layer_idx == 0
+        )
         return Schedule(globs, nodes, end)
 
     def make_globals(self, model):  # type: ignore[override]

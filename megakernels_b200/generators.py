@@ -84,7 +84,14 @@ class MK_Generator(Generator):
             globs.argmax_out = torch.zeros(1, dtype=torch.int32, device=globs.hidden_states.device)
 
     def fill(self):
-        self.schedule.globs.barriers.fill_(self.barrier_fill_val)
+        """Reset the per-token VM state: barrier counters and residual accumulators."""
+        globs = self.schedule.globs
+        if self.barrier_fill_val == 0 and globs.vm_state is not None:
+            globs.vm_state.zero_()  # one buffer behind both
+            return
+        globs.barriers.fill_(self.barrier_fill_val)
+        if globs.residual_acc is not None:
+            globs.residual_acc.zero_()
 
     def replace_with_noops(self):
         self.schedule.globs.instructions.zero_()
@@ -204,10 +211,11 @@ class TP_MK_Generator(MK_Generator):
     Here every rank runs the megakernel on its shard (``model`` built with
     ``ExtraModelConfig(tp_size, tp_rank)``).  The instruction stream is cut after
     every o-proj and down-proj group; between two cuts the ranks all-reduce the
-    residual stream.  Each rank adds ``tp_size`` times its partial projection to
-    its full copy of the residual (``globs.residual_scale``), so that the
-    *average* over ranks equals ``h + sum of partials`` and no separate scaling
-    or zeroing kernel is needed.
+    residual accumulators (``globs.residual_acc``, 64-bit fixed point).  Each rank
+    adds ``tp_size`` times its partial projection to its full copy
+    (``globs.residual_scale``), so that the sum over ranks divided by ``tp_size``
+    - an exact integer division - equals ``previous value + sum of partials`` on
+    every rank, bit for bit, and nothing has to be zeroed between segments.
     """
 
     def __init__(self, model, interpreter, schedule, group=None, sched: str = "rr", all_reduce=None):
@@ -229,7 +237,8 @@ class TP_MK_Generator(MK_Generator):
     def _nccl_average(self, tensor: Tensor):
         import torch.distributed as dist
 
-        dist.all_reduce(tensor, op=dist.ReduceOp.AVG, group=self.group)
+        dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)
+        tensor.floor_divide_(self.tp_size)  # every term is a multiple of tp_size: exact
 
     def begin_token(self, input_ids: Tensor, pos_id: int):
         globs = self.schedule.globs
@@ -255,7 +264,7 @@ class TP_MK_Generator(MK_Generator):
         self.fill()
         for k in range(len(self.segments)):
             if self.launch_segment(k):
-                self.all_reduce(globs.hidden_states)
+                self.all_reduce(globs.residual_acc)
         return self.finish_token()
 
     def run(self, input_ids: Tensor, pos_id: int):

@@ -98,6 +98,27 @@ class BaseGlobals:
         self.pos_id_device: Tensor | None = None  # int32[1]; overrides pos_id when set
         self.tp: TensorParallelState | None = None  # in-kernel tensor-parallel all-reduce
         self.argmax_out: Tensor | None = None  # int32[1]: the kernel's own argmax over the logits
+        # int64 [H]: the token's o-proj / down-proj outputs summed in Q31.32 fixed point by the
+        # kernel (integer atomics: the same bits whatever order the SMs arrive in).  The kernel
+        # never writes ``hidden_states``; the residual stream is ``residual_stream()``.
+        self.residual_acc: Tensor | None = None
+        # one int32 buffer behind ``barriers`` and ``residual_acc``, so that a single fill
+        # resets both before a launch
+        self.vm_state: Tensor | None = None
+        # RMS + up/gate instructions per layer of the schedule (0: unknown); the down-proj
+        # waits for that many residual-stream reads before it adds to the accumulators
+        self.upgate_instructions_per_layer: int = 0
+
+    def residual_stream(self) -> Tensor:
+        """The residual stream after a launch as fp32 ``[H]``: embedding + accumulated outputs.
+
+        The CPU checker follows the reference and adds into ``hidden_states`` itself, so its
+        accumulators stay zero and this is just ``hidden_states`` there.
+        """
+        h = self.hidden_states.float()
+        if self.residual_acc is not None:
+            h = (h.double() + self.residual_acc.double() * 2.0**-32).float()
+        return h
 
     def sm_count(self) -> int:
         return get_sm_count(self.device)

@@ -18,7 +18,7 @@ import torch
 _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libmkb200.so"
 
-MKB_ABI_VERSION = 2
+MKB_ABI_VERSION = 3
 MKB_MAX_TP = 8
 MKB_TP_MAX_CHUNKS = 32
 MKB_PEER_HANDLE_BYTES = 64
@@ -96,6 +96,9 @@ class MkbGlobals(ctypes.Structure):
         ("skip_attn_reduction", ctypes.c_int32),
         ("pos_id_device", ctypes.c_void_p),
         ("residual_scale", ctypes.c_float),
+        ("residual_acc", ctypes.c_void_p),
+        ("upgate_instructions_per_layer", ctypes.c_int32),
+        ("reserved0", ctypes.c_int32),
         ("tp", MkbTensorParallel),
         ("argmax_out", ctypes.c_void_p),
         ("flags", ctypes.c_uint32),
@@ -224,6 +227,8 @@ def pack_globals(
     residual_scale=1.0,
     tp=None,
     argmax_out=None,
+    residual_acc=None,
+    upgate_instructions_per_layer=0,
 ) -> MkbGlobals:
     """Fill the C struct from tensors; every dimension is read off the shapes."""
     bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
@@ -328,12 +333,39 @@ def pack_globals(
         g.tp.epoch_device = _check_tensor("tp.epoch_device", tp.epoch_device, i32)
     if argmax_out is not None:
         g.argmax_out = _check_tensor("argmax_out", argmax_out, i32)
+    if residual_acc is not None:
+        g.residual_acc = _check_tensor("residual_acc", residual_acc, torch.int64, 1)
+        if residual_acc.numel() < H:
+            raise ValueError(f"residual_acc needs {H} int64 elements, got {residual_acc.numel()}")
+    g.upgate_instructions_per_layer = int(upgate_instructions_per_layer)
     g.flags = MKB_FLAG_RECORD_TIMINGS if record_timings else 0
     if record_timings and timings is None:
         raise ValueError("record_timings needs the timings tensor")
     g.wait_timeout_ms = int(wait_timeout_ms)
     g.status = _check_tensor("status", status, i32) if status is not None else None
     return g
+
+
+_residual_accs: dict = {}
+
+
+def _own_residual_acc(hidden_states, stream):
+    """Accumulator for callers of the bare reference signature, zeroed on the launch stream."""
+    key = (hidden_states.device.index, hidden_states.data_ptr(), hidden_states.numel())
+    acc = _residual_accs.get(key)
+    if acc is None:
+        if len(_residual_accs) >= 16:
+            _residual_accs.clear()
+        acc = _residual_accs[key] = torch.zeros(
+            hidden_states.numel(), dtype=torch.int64, device=hidden_states.device
+        )
+    ctx = torch.cuda.stream(stream) if isinstance(stream, torch.cuda.Stream) else None
+    if ctx is None:
+        acc.zero_()
+    else:
+        with ctx:
+            acc.zero_()
+    return acc
 
 
 def _stream_handle(stream) -> int:
@@ -355,6 +387,8 @@ def mk_llama(
     residual_scale=1.0,
     tp=None,
     argmax_out=None,
+    residual_acc=None,
+    upgate_instructions_per_layer=0,
 ):
     """Enqueue one decode step; positional arguments as in the reference call.
 
@@ -364,10 +398,17 @@ def mk_llama(
     attn_out_intermediates, silu_out, logits, pos_id, attn_scale, rms_norm_eps,
     skip_attn_reduction, stream=...)``.  Asynchronous; raises
     ``MegakernelError`` when host-side validation rejects the arguments.
+
+    ``residual_acc`` (int64 ``[H]``, zero before the launch) is where the kernel sums the
+    o-proj / down-proj outputs; a caller that passes only the reference's 27 arguments gets
+    one per ``hidden_states`` buffer from this module, cleared on the launch stream before
+    every call (one small memset more than a caller who resets it with the barriers).
     """
     if len(args) != 27:
         raise TypeError(f"mk_llama expects 27 positional arguments, got {len(args)}")
     lib = load_library()
+    if residual_acc is None and tp is None:
+        residual_acc = _own_residual_acc(args[16], stream)
     g = pack_globals(
         *args,
         matvec_reduction_size=matvec_reduction_size,
@@ -378,6 +419,8 @@ def mk_llama(
         residual_scale=residual_scale,
         tp=tp,
         argmax_out=argmax_out,
+        residual_acc=residual_acc,
+        upgate_instructions_per_layer=upgate_instructions_per_layer,
     )
     rc = lib.mkb_launch(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
     if rc != 0:
@@ -439,6 +482,7 @@ def mk_llama_no_alloc(
     status=None,
     num_attention_heads=None,
     max_partials=None,
+    upgate_instructions_per_layer=0,
 ):
     """One decode step through ``mkb_launch_no_alloc``: nothing is allocated by the call.
 
@@ -447,6 +491,7 @@ def mk_llama_no_alloc(
     ``max_partials`` - the library keeps that scratch (and, unless ``status`` is
     given, its error record) in a static device array, for callers whose device
     memory is fully planned and who therefore cannot let a library call cudaMalloc.
+    The residual accumulators live in the same array and are cleared by the call.
     The array is shared by all calls: do not overlap two of them on the GPU.
     """
     if len(args) != 27:
@@ -459,6 +504,7 @@ def mk_llama_no_alloc(
         status=status,
         num_attention_heads=num_attention_heads,
         max_partials=max_partials,
+        upgate_instructions_per_layer=upgate_instructions_per_layer,
     )
     rc = lib.mkb_launch_no_alloc(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
     if rc != 0:

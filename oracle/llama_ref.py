@@ -127,11 +127,6 @@ def assert_logits_parity(test: Tensor, ref: Tensor, what: str = ""):
     m = parity_metrics(test, ref)
     assert m["max_rel"] <= MAX_REL_TOL, f"{what}: max rel err {m['max_rel']:.4g} > {MAX_REL_TOL}"
     assert m["cosine"] >= COSINE_TOL, f"{what}: cosine {m['cosine']:.6f} < {COSINE_TOL}"
-    # Logits are bf16: when the reference's two largest logits are NEIGHBOURING bf16 values (at
-    # a logit of 4..8 one step is 0.03125, above MARGIN_TOL) the winner is decided by the
-    # reference's own last rounding, and the residual stream's bf16 atomic adds, whose order
-    # varies from run to run, flip it now and then.  The argmax rule therefore applies when the
-    # margin exceeds both MARGIN_TOL and one bf16 step of the top logit.
-    if m["top2_margin"] > max(MARGIN_TOL, m["top_bf16_step"]):
+    if m["top2_margin"] > MARGIN_TOL:
         assert m["argmax_equal"], f"{what}: argmax differs with margin {m['top2_margin']:.4g}"
     return m

@@ -50,7 +50,7 @@ def interpreter():
 def run_gpu_step(gpu_sched, hidden, pos, **kw):
     g = gpu_sched.globs
     g.hidden_states[:] = hidden.to(g.hidden_states.device)
-    g.barriers.zero_()
+    g.vm_state.zero_()  # barrier counters and residual accumulators
     g.pos_id = pos
     call = interpreter().interpret(g, **kw)
     mk = sys.modules["mk_llama"]
@@ -62,17 +62,16 @@ def rel_err(test: torch.Tensor, ref: torch.Tensor) -> float:
     return float((a - b).abs().max() / b.abs().max().clamp_min(1e-12))
 
 
-def compare_globals(gpu_g, cpu_g, pos, names=ACTIVATIONS, tol=2.5e-2):
-    """max|gpu - cpu| / max|cpu| per tensor; returns the dict, asserts the tolerance.
+def tensor_of(g, name):
+    """Activation tensor by name; the residual stream is the embedding plus the accumulators."""
+    return g.residual_stream() if name == "hidden_states" else getattr(g, name)
 
-    This bisecting check of the INTERMEDIATE tensors is a quarter looser than the 2e-2 the logits
-    must meet (assert_logits_parity, always called next to it): the residual stream is summed
-    with bf16 atomics whose order changes from run to run, and a single intermediate element
-    (silu_out of the 8B shape) was seen between 1.8e-2 and 2.05e-2 across identical runs.
-    """
+
+def compare_globals(gpu_g, cpu_g, pos, names=ACTIVATIONS, tol=2e-2):
+    """max|gpu - cpu| / max|cpu| per tensor; returns the dict, asserts the tolerance."""
     out = {}
     for name in names:
-        out[name] = rel_err(getattr(gpu_g, name), getattr(cpu_g, name))
+        out[name] = rel_err(tensor_of(gpu_g, name), tensor_of(cpu_g, name))
     out["k_new"] = rel_err(gpu_g.k_cache[:, 0, pos], cpu_g.k_cache[:, 0, pos])
     out["v_new"] = rel_err(gpu_g.v_cache[:, 0, pos], cpu_g.v_cache[:, 0, pos])
     bad = {k: v for k, v in out.items() if not v <= tol}

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in mkb200.h but not exported"
     lib.mkb_abi_version.restype = ctypes.c_int
-    assert lib.mkb_abi_version() == 2
+    assert lib.mkb_abi_version() == 3
     lib.mkb_smem_bytes.restype = ctypes.c_int
     assert 0 < lib.mkb_smem_bytes() <= 227 * 1024
 

@@ -1,0 +1,158 @@
+"""GPU parity at the sizes the benchmark configurations name, against the pinned torch oracle.
+
+* the Llama-3.1-8B configuration at full depth and vocabulary (32 layers, 128,256 logits,
+  KV prefilled to 1024 positions, poison beyond), teacher-forced;
+* the Llama-3.2-1B configuration at full depth (16 layers, tied head): a prompt of 32
+  tokens prefilled through the decode kernel, then greedy decoding;
+* long contexts (4096, 16384, 65536 cached positions) with the split-KV partition counts
+  the scheduler picks, and the longest reduction list an instruction can carry;
+* run-to-run reproducibility: the same step repeated 50 times must give the same bits.
+
+Tolerance as everywhere: max|a-b|/max|b| <= 2e-2, cosine >= 0.999, argmax equal wherever the
+oracle's top-2 margin exceeds 1e-2 (oracle/llama_ref.py).  The fused argmax must equal
+torch.argmax of the logits the same launch wrote, over the full vocabulary.
+"""
+
+import pytest
+import torch
+
+from megakernels_b200.demos.latency.scheduler import (
+    LatencyScheduleOptions,
+    pick_num_attention_partitions,
+)
+from megakernels_b200.generators import MK_Generator
+from megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
+from megakernels_b200.model_types import ExtraModelConfig
+from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
+from oracle.llama_ref import TorchReferenceModel, assert_logits_parity
+from tests.gpu_utils import interpreter, make_pair, run_gpu_step
+from tests.oracle_utils import build_schedule, seeded_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def device_model(cfg, max_len, prefill, poison=True, seed_kv=2):
+    """Model drawn on the GPU (a CPU draw of 8e9 weights takes minutes) with a seeded KV prefix;
+    the oracle gets copies of exactly these tensors."""
+    extra = ExtraModelConfig(interleave_rope=True, max_len_override=max_len)
+    model = LlamaForCausalLM.from_random(cfg, extra, device=DEV, seed=0, draw_on="device")
+    gen = torch.Generator(device=DEV).manual_seed(seed_kv)
+    for c in model.stacked_kv_cache:
+        c[:, :, :prefill] = torch.randn(c[:, :, :prefill].shape, generator=gen, device=DEV).to(c.dtype)
+        if poison and prefill < max_len:
+            c[:, :, prefill:] = (torch.randn(c[:, :, prefill:].shape, generator=gen, device=DEV) * 100).to(c.dtype)
+    return model
+
+
+def engine(model, partitions, sched="rr"):
+    opts = LatencyScheduleOptions(num_attention_partitions=partitions, coalesce_o_proj=True)
+    schedule = build_schedule(model, opts)
+    tensorize_instructions(schedule.globs, assign_to_sms(sched, schedule=schedule))
+    return schedule, MK_Generator(model, interpreter(), schedule)
+
+
+def test_llama_8b_full_depth_teacher_forced():
+    """BASELINE configuration 1 as the benchmark runs it, 8 steps against the oracle."""
+    cfg = LlamaConfig.llama_3_1_8b()
+    prefill, steps = 1024, 8
+    model = device_model(cfg, prefill + steps + 8, prefill)
+    ref = TorchReferenceModel(model)
+    ref.load_kv(*model.stacked_kv_cache)
+    parts = pick_num_attention_partitions(prefill, steps, DEV, model.num_kv_heads(), min_chunk_size=128)
+    schedule, gen = engine(model, parts)
+    g = schedule.globs
+    assert g.argmax_out is not None and g.logits.numel() == 128256
+    for i, tok in enumerate(seeded_tokens(cfg.vocab_size, steps)):
+        pos = prefill + i
+        out = gen.run(torch.tensor([[tok]], device=DEV), pos)
+        gen.check()
+        want = ref.decode_token(tok, pos)
+        m = assert_logits_parity(g.logits, want, f"8B full depth, pos {pos}")
+        assert int(out) == int(torch.argmax(g.logits)), f"fused argmax at pos {pos}"
+        assert torch.equal(g.k_cache[:, 0, pos + 1 :].cpu(), ref.k_cache[:, 0, pos + 1 :]), "wrote past the token"
+        print(f"pos {pos}: max_rel {m['max_rel']:.3e} cosine {m['cosine']:.6f} margin {m['top2_margin']:.4f}")
+
+
+def test_llama_1b_full_depth_prompt_then_greedy():
+    """BASELINE configuration 0: 16 layers, tied head, prompt 32, then 16 greedy steps."""
+    cfg = LlamaConfig.llama_3_2_1b()
+    prompt_len, ntok = 32, 17
+    model = device_model(cfg, 64, 0, poison=False)
+    ref = TorchReferenceModel(model)
+    schedule, gen = engine(model, 1)
+    g = schedule.globs
+    prompt = torch.tensor(seeded_tokens(cfg.vocab_size, prompt_len, seed=1))
+    out = torch.zeros(1, ntok, dtype=torch.long, device=DEV)
+    out[:, 0] = gen.prefill(prompt.to(DEV))
+    gen.check()
+    for pos, tok in enumerate(prompt.tolist()):
+        want = ref.decode_token(tok, pos)
+    assert_logits_parity(g.logits, want, "1B after the prompt")
+    # greedy decoding, checked step by step: the oracle is teacher-forced with the kernel's tokens
+    for i in range(1, ntok):
+        tok = int(out[0, i - 1])
+        pos = prompt_len + i - 1
+        got = gen.run(out[:, i - 1 : i], pos)
+        gen.check()
+        out[:, i] = got.reshape(-1)
+        want = ref.decode_token(tok, pos)
+        assert_logits_parity(g.logits, want, f"1B greedy step {i}")
+        assert int(got) == int(torch.argmax(g.logits))
+
+
+@pytest.mark.parametrize("length", [4096, 16384, 65536])
+def test_long_context_split_kv(length):
+    """BASELINE configuration 2 at one layer of the 1B widths: the partition count the scheduler
+    picks for the length, two steps, against scaled-dot-product attention over the whole cache."""
+    cfg = LlamaConfig.llama_3_2_1b(num_hidden_layers=1, vocab_size=4096)
+    model = device_model(cfg, length + 8, length)
+    ref = TorchReferenceModel(model)
+    ref.load_kv(*model.stacked_kv_cache)
+    parts = pick_num_attention_partitions(length, 64, DEV, model.num_kv_heads(), min_chunk_size=128)
+    assert parts > 1
+    schedule, gen = engine(model, parts)
+    for i, tok in enumerate(seeded_tokens(cfg.vocab_size, 2)):
+        pos = length + i
+        gen.run(torch.tensor([[tok]], device=DEV), pos)
+        gen.check()
+        assert_logits_parity(schedule.globs.logits, ref.decode_token(tok, pos), f"length {length}, {parts} partitions")
+
+
+def test_longest_reduction_list():
+    """24 partitions per KV head: the reduction instruction's index list fills its 32 words."""
+    cfg = LlamaConfig.llama_3_2_1b(num_hidden_layers=1, vocab_size=4096)
+    length = 16384
+    model = device_model(cfg, length + 8, length)
+    ref = TorchReferenceModel(model)
+    ref.load_kv(*model.stacked_kv_cache)
+    schedule, gen = engine(model, 24)
+    tok = seeded_tokens(cfg.vocab_size, 1)[0]
+    gen.run(torch.tensor([[tok]], device=DEV), length)
+    gen.check()
+    assert_logits_parity(schedule.globs.logits, ref.decode_token(tok, length), "24 partitions")
+
+
+@pytest.mark.parametrize("shape", ["8b", "70b"])
+def test_identical_runs_give_identical_bits(shape):
+    """The residual stream is summed with integer atomics, so nothing depends on the order in
+    which SMs arrive: 50 repetitions of one step must agree bit for bit (flip rate 0)."""
+    if shape == "8b":
+        cfg = LlamaConfig.llama_3_1_8b(num_hidden_layers=2, vocab_size=4096)
+    else:
+        cfg = LlamaConfig.llama_3_1_70b(num_hidden_layers=1, vocab_size=4096)
+    opts = LatencyScheduleOptions(num_attention_partitions=3, coalesce_o_proj=True)
+    cpu_model, _, _, gpu_sched = make_pair(cfg, 300, 280, options=opts, sched="wave")
+    g = gpu_sched.globs
+    hidden = cpu_model.model.embed_tokens.embed_tokens.weight[77]
+    first = None
+    differing = 0
+    for _ in range(50):
+        st = run_gpu_step(gpu_sched, hidden, 280)
+        assert st.code == 0
+        now = (g.logits.clone(), g.residual_acc.clone(), g.silu_out.clone())
+        if first is None:
+            first = now
+        elif not all(torch.equal(a, b) for a, b in zip(first, now)):
+            differing += 1
+    assert differing == 0, f"{differing} of 49 repetitions differ from the first run"

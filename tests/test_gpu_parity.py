@@ -16,6 +16,7 @@ from megakernels_b200.llama import LlamaConfig
 from oracle.llama_ref import parity_metrics, TorchReferenceModel, assert_logits_parity
 from tests.gpu_utils import (
     compare_globals,
+    tensor_of,
     interpreter,
     make_pair,
     rel_err,
@@ -110,13 +111,14 @@ def test_golden_1b_widths_all_assignments(golden_dir, sched):
         assert_logits_parity(g.logits, step["logits"], f"vs reference VM, pos {step['pos']}")
         assert_logits_parity(g.logits, tstep["logits"], f"vs reference torch, pos {step['pos']}")
         for name in ("hidden_states", "post_ln_rope_q", "attn_out", "silu_out"):
-            assert rel_err(getattr(g, name), step[name]) <= 2e-2, name
+            assert rel_err(tensor_of(g, name), step[name]) <= 2e-2, name
         assert rel_err(g.k_cache[:, 0, step["pos"]], step["k_new"]) <= 2e-2
         assert rel_err(g.v_cache[:, 0, step["pos"]], step["v_new"]) <= 2e-2
         ours, ref = g.barriers.cpu().clone(), step["barriers"].clone()
         assert torch.equal(ours[:, 4].sum(-1), ref[:, 4].sum(-1))
         ours[:, 4] = 0
         ref[:, 4] = 0
+        ours[:, 8] = 0  # residual-read arrivals: no counterpart in the reference
         assert torch.equal(ours, ref)
 
 
@@ -142,6 +144,11 @@ def test_split_kv_attention_and_reduction(shape, prefill, partitions):
     opts = LatencyScheduleOptions(num_attention_partitions=partitions, coalesce_o_proj=True)
     cpu_model, cpu_sched, gpu_model, gpu_sched = make_pair(cfg, prefill + 8, prefill, options=opts)
     embed = cpu_model.model.embed_tokens.embed_tokens.weight
+    # the multi-partition VM solvers are this repository's generalisation; the torch path
+    # (attention over the whole cache in one call) is pinned to the reference, so it is the
+    # anchor for both the VM and the kernel here
+    ref = TorchReferenceModel(cpu_model)
+    ref.load_kv(*cpu_model.stacked_kv_cache)
     for i, tok in enumerate(seeded_tokens(cfg.vocab_size, 2)):
         pos = prefill + i
         run_cpu_step(cpu_model, cpu_sched, embed[tok], pos)
@@ -149,6 +156,9 @@ def test_split_kv_attention_and_reduction(shape, prefill, partitions):
         assert st.code == 0
         compare_globals(gpu_sched.globs, cpu_sched.globs, pos)
         assert_logits_parity(gpu_sched.globs.logits, cpu_sched.globs.logits, f"pos {pos}")
+        want = ref.decode_token(tok, pos)
+        assert_logits_parity(cpu_sched.globs.logits, want, f"VM vs torch path, pos {pos}")
+        assert_logits_parity(gpu_sched.globs.logits, want, f"kernel vs torch path, pos {pos}")
         assert torch.equal(gpu_sched.globs.barriers.cpu(), cpu_sched.globs.barriers)
 
 
@@ -251,7 +261,7 @@ def test_greedy_generation_matches_oracle():
     for i in range(ntok):
         want = int(logits.argmax())
         m = parity_metrics(logits, logits)  # margin and bf16 spacing of the oracle's own logits
-        if m["top2_margin"] > max(1e-2, m["top_bf16_step"]):
+        if m["top2_margin"] > 1e-2:
             assert got[i] == want, f"token {i}: {got[i]} vs {want}"
         if i + 1 < ntok:
             logits = ref.decode_token(got[i], prompt.numel() + i)

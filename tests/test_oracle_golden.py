@@ -67,11 +67,14 @@ def test_python_vm_reproduces_reference_vm_bit_for_bit(fx_1b):
         assert torch.equal(g.k_cache[:, 0, step["pos"]], step["k_new"])
         assert torch.equal(g.v_cache[:, 0, step["pos"]], step["v_new"])
         # barriers: identical except the up/gate row, which the reference VM keeps in
-        # slot 0 only while the CUDA kernels (and this oracle) use one slot per slice
+        # slot 0 only while the CUDA kernels (and this oracle) use one slot per slice,
+        # and row 8, where this oracle counts the up/gate reads of the residual stream
         ours, ref = g.barriers.clone(), step["barriers"].clone()
         assert torch.equal(ours[:, 4].sum(-1), ref[:, 4].sum(-1))
+        assert bool((ours[:, 8, 0] == g.upgate_instructions_per_layer).all()) and int(ref[:, 8].abs().sum()) == 0
         ours[:, 4] = 0
         ref[:, 4] = 0
+        ours[:, 8] = 0
         assert torch.equal(ours, ref)
 
 

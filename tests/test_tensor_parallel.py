@@ -120,10 +120,11 @@ def test_emulated_ranks_on_one_gpu(tp):
             g.begin_token(ids, PREFILL + i)
         for k in range(len(gens[0].segments)):
             flags = [g.launch_segment(k) for g in gens]
-            if flags[0]:
-                mean = torch.stack([g.schedule.globs.hidden_states.float() for g in gens]).mean(0)
+            if flags[0]:  # what TP_MK_Generator._nccl_average does across processes
+                total = torch.stack([g.schedule.globs.residual_acc for g in gens]).sum(0)
+                assert int((total % tp).abs().sum()) == 0, "every term is a multiple of the degree"
                 for g in gens:
-                    g.schedule.globs.hidden_states.copy_(mean.to(torch.bfloat16))
+                    g.schedule.globs.residual_acc.copy_(total // tp)
         for g in gens:
             g.check()
             assert_logits_parity(g.schedule.globs.logits, want[i], f"tp={tp} step {i}")

@@ -1,39 +1,47 @@
-"""``mkb_launch_no_alloc`` against ``mkb_launch`` (collected last on purpose).
+"""``mkb_launch_no_alloc`` against ``mkb_launch`` and the CPU oracle (collected last on purpose).
 
 Some hosts of the decode kernel cannot allocate device memory while they run:
 their memory plan is fixed before the first token, or every byte already
 belongs to their own pool.  For them the library offers one entry point that
-calls no allocator at all and keeps the split-KV attention scratch and the
-error record in a static device array.  This test drives that entry point
-through the C ABI with the attention intermediates set to NULL, on a schedule
-that really uses the scratch (several attention partitions plus reductions),
-twice in a row, and compares every output with the ordinary entry point on
-the same inputs.  The array keeps the previous call's contents, so the second
-call also shows that nothing stale leaks into the result.
+calls no allocator at all and keeps the split-KV attention scratch, the
+residual accumulators and the error record in a static device array.  These
+tests drive that entry point through the C ABI with the attention
+intermediates set to NULL, on a schedule that really uses the scratch (several
+attention partitions plus reductions), twice in a row, and compare every
+output with the ordinary entry point and with the oracle on the same inputs.
+The array keeps the previous call's contents, so the second call also shows
+that nothing stale leaks into the result.  One test repeats this in a fresh
+process where the no-alloc call is the very first thing the library does on
+the device, with the error record left inside the static array as well.
 """
 
+import subprocess
 import sys
+from pathlib import Path
 
 import pytest
 import torch
 
 from megakernels_b200.demos.latency.scheduler import LatencyScheduleOptions
 from megakernels_b200.llama import LlamaConfig
-from tests.gpu_utils import interpreter, make_pair, rel_err, run_gpu_step
+from oracle.llama_ref import assert_logits_parity
+from tests.gpu_utils import interpreter, make_pair, rel_err, run_cpu_step, run_gpu_step
 from tests.oracle_utils import seeded_tokens
 
 pytestmark = pytest.mark.gpu
 
 TOL = 2e-2  # the tolerance of the parity tests: max|a-b| / max|b|
+PARTS, PREFILL = 5, 150
+OUTPUTS = ("logits", "post_ln_rope_q", "attn_out", "silu_out")
 
 
-def launch_no_alloc(g, hidden, pos, max_partials):
+def launch_no_alloc(g, hidden, pos, max_partials, own_status=True):
     mk = sys.modules["mk_llama"]
     g.hidden_states[:] = hidden.to(g.hidden_states.device)
     g.barriers.zero_()
     g.pos_id = pos
     L, B, T, Hkv, D = g.k_cache.shape
-    status = torch.zeros(16, dtype=torch.int32, device=g.hidden_states.device)
+    status = torch.zeros(16, dtype=torch.int32, device=g.hidden_states.device) if own_status else None
     call = mk.mk_llama_no_alloc(
         g.barriers, g.instructions, g.timings,
         g.qkv_proj_weights, g.attn_ln_weights, g.o_proj_weights, g.mlp_ln_weights,
@@ -49,32 +57,75 @@ def launch_no_alloc(g, hidden, pos, max_partials):
         status=status,
         num_attention_heads=g.num_attention_heads,
         max_partials=max_partials,
+        upgate_instructions_per_layer=g.upgate_instructions_per_layer,
     )
-    return mk.sync_status(call)
+    return mk.sync_status(call, no_alloc=True)
+
+
+def small_case():
+    cfg = LlamaConfig.llama_3_2_1b(num_hidden_layers=2, vocab_size=4096)
+    opts = LatencyScheduleOptions(num_attention_partitions=PARTS, coalesce_o_proj=True)
+    return cfg, opts
 
 
 def test_no_alloc_entry_point_matches_the_allocating_one():
     interpreter()
-    cfg = LlamaConfig.llama_3_2_1b(num_hidden_layers=2, vocab_size=4096)
-    parts = 5
-    opts = LatencyScheduleOptions(num_attention_partitions=parts, coalesce_o_proj=True)
-    prefill = 150
-    _, _, model_a, sched_a = make_pair(cfg, prefill + 8, prefill, options=opts)
-    _, _, model_b, sched_b = make_pair(cfg, prefill + 8, prefill, options=opts)
-    embed = model_a.model.embed_tokens.embed_tokens.weight.cpu()
+    cfg, opts = small_case()
+    cpu_model, cpu_sched, model_a, sched_a = make_pair(cfg, PREFILL + 8, PREFILL, options=opts)
+    _, _, model_b, sched_b = make_pair(cfg, PREFILL + 8, PREFILL, options=opts)
+    embed = cpu_model.model.embed_tokens.embed_tokens.weight
     ga, gb = sched_a.globs, sched_b.globs
     for i, tok in enumerate(seeded_tokens(cfg.vocab_size, 2)):  # two calls in a row
-        pos = prefill + i
+        pos = PREFILL + i
+        run_cpu_step(cpu_model, cpu_sched, embed[tok], pos)
         st = run_gpu_step(sched_a, embed[tok], pos)
         assert st.code == 0
-        st = launch_no_alloc(gb, embed[tok], pos, max_partials=parts)
+        st = launch_no_alloc(gb, embed[tok], pos, max_partials=PARTS)
         assert st.code == 0
-        for name in ("logits", "hidden_states", "post_ln_rope_q", "attn_out", "silu_out"):
+        # integer accumulation makes the two entry points agree exactly, not just within TOL
+        for name in OUTPUTS:
             assert rel_err(getattr(gb, name), getattr(ga, name)) <= TOL, f"{name} at pos {pos}"
-        assert rel_err(gb.k_cache[:, 0, pos], ga.k_cache[:, 0, pos]) <= TOL
-        assert rel_err(gb.v_cache[:, 0, pos], ga.v_cache[:, 0, pos]) <= TOL
+            assert torch.equal(getattr(gb, name), getattr(ga, name)), f"{name} at pos {pos}"
+        assert torch.equal(gb.k_cache[:, 0, pos], ga.k_cache[:, 0, pos])
+        assert torch.equal(gb.v_cache[:, 0, pos], ga.v_cache[:, 0, pos])
         assert torch.equal(gb.barriers, ga.barriers)
-        assert int(gb.logits.argmax()) == int(ga.logits.argmax())
+        assert_logits_parity(gb.logits, cpu_sched.globs.logits, f"no-alloc vs oracle, pos {pos}")
+
+
+def fresh_process_body():
+    """Runs in a child process: the no-alloc call is the library's first act on the device."""
+    interpreter()  # loads the library; launches nothing
+    cfg, opts = small_case()
+    cpu_model, cpu_sched, model_a, sched_a = make_pair(cfg, PREFILL + 8, PREFILL, options=opts)
+    _, _, model_b, sched_b = make_pair(cfg, PREFILL + 8, PREFILL, options=opts)
+    embed = cpu_model.model.embed_tokens.embed_tokens.weight
+    ga, gb = sched_a.globs, sched_b.globs
+    for i, tok in enumerate(seeded_tokens(cfg.vocab_size, 2)):
+        pos = PREFILL + i
+        # error record inside the static array too (status=None), read back without allocating
+        st = launch_no_alloc(gb, embed[tok], pos, max_partials=PARTS, own_status=False)
+        assert st.code == 0
+        run_cpu_step(cpu_model, cpu_sched, embed[tok], pos)
+        assert_logits_parity(gb.logits, cpu_sched.globs.logits, f"fresh process vs oracle, pos {pos}")
+        st = run_gpu_step(sched_a, embed[tok], pos)  # only now the allocating entry point
+        assert st.code == 0
+        for name in OUTPUTS:
+            assert torch.equal(getattr(gb, name), getattr(ga, name)), f"{name} at pos {pos}"
+    print("FRESH-PROCESS-OK")
+
+
+def test_no_alloc_entry_point_as_first_call_in_a_fresh_process():
+    root = Path(__file__).resolve().parent.parent
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "import torch\n"
+        "from megakernels_b200.utils import set_sm_count_override\n"
+        "set_sm_count_override(torch.cuda.get_device_properties(0).multi_processor_count)\n"
+        "from tests.test_zz_no_alloc import fresh_process_body\n"
+        "fresh_process_body()\n"
+    ) % str(root)
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "FRESH-PROCESS-OK" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
 
 
 def test_no_alloc_entry_point_rejects_oversized_scratch():
