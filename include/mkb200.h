@@ -145,7 +145,7 @@ typedef struct MkbTensorParallel {
  * llama.cuh:15-26); under tensor parallelism they are the per-rank values.
  * This build instantiates its pipelines for hidden_size 2048, 4096 or 8192,
  * head_dim 64 or 128, a GQA ratio of 4 (or 8 with head_dim 128) and
- * matvec_reduction_size 512, 1024 or 2048; anything else is refused with
+ * matvec_reduction_size 256, 512, 1024 or 2048; anything else is refused with
  * MKB_ERR_UNSUPPORTED before a launch.
  */
 typedef struct MkbGlobals {

@@ -207,8 +207,8 @@ int validate(const MkbGlobals* g) {
     if (!(gqa == 4 || (gqa == 8 && D == 128)))
         return fail(MKB_ERR_UNSUPPORTED, "GQA ratio %d with head_dim %d is not supported", gqa, D);
     if (Hq % 4 != 0) return fail(MKB_ERR_UNSUPPORTED, "Hq %d must be a multiple of 4", Hq);
-    if (R != 512 && R != 1024 && R != 2048)
-        return fail(MKB_ERR_UNSUPPORTED, "matvec_reduction_size %d: supported are 512, 1024, 2048", R);
+    if (R != 256 && R != 512 && R != 1024 && R != 2048)
+        return fail(MKB_ERR_UNSUPPORTED, "matvec_reduction_size %d: supported are 256, 512, 1024, 2048", R);
     if ((Hq * D) % R != 0 || I % R != 0)
         return fail(MKB_ERR_INVALID_ARGUMENT, "o-proj inputs %d and intermediate %d must be multiples of %d", Hq * D, I, R);
     if (I % 16 != 0 || g->vocab_size % 16 != 0)

@@ -72,12 +72,12 @@ def pick_num_attention_partitions(
 
 def pick_matvec_reduction_size(o_in_features: int, intermediate_size: int) -> int:
     """Largest input-column slice (<= 2048) dividing both row-split projections."""
-    for r in (2048, 1024, 512):
+    for r in (2048, 1024, 512, 256):
         if o_in_features % r == 0 and intermediate_size % r == 0:
             return r
     raise ValueError(
         f"o-proj inputs {o_in_features} and intermediate {intermediate_size} "
-        "must both be multiples of 512"
+        "must both be multiples of 256"
     )
 
 
@@ -98,7 +98,10 @@ def make_globals(model, skip_attn_reduction: bool = True, max_attn_partitions: i
         max_attn_partitions = get_sm_count(device)
 
     # barrier counters and residual accumulators share one buffer: one fill resets both
-    bar_shape = [config.num_hidden_layers, 10, n_q + 2 * n_kv]
+    # one slot per head as in the reference (latency/scheduler.py:59); small tensor-parallel
+    # shards can have more down-proj input slices than heads, and every slice needs a slot
+    reduction = pick_matvec_reduction_size(n_q * config.head_dim, inter)
+    bar_shape = [config.num_hidden_layers, 10, max(n_q + 2 * n_kv, inter // reduction)]
     n_bar = math.prod(bar_shape)
     acc_off = (n_bar + 3) // 4 * 4  # int64 view needs 8-byte, the kernel's loads 16-byte alignment
     vm_state = torch.zeros(acc_off + 2 * config.hidden_size, dtype=torch.int32, device=device)
@@ -144,7 +147,7 @@ def make_globals(model, skip_attn_reduction: bool = True, max_attn_partitions: i
         qkv_block_size=16,
         o_proj_block_size=16,
         lm_head_block_size=16,
-        matvec_reduction_size=pick_matvec_reduction_size(n_q * config.head_dim, inter),
+        matvec_reduction_size=reduction,
         attn_kv_block_size=16,
         attn_reduction_size=4,
         vocab_size=config.vocab_size,

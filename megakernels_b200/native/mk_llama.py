@@ -309,7 +309,7 @@ def pack_globals(
     elif rope_cos.shape[0] <= int(pos_id):
         raise ValueError(f"rope tables have {rope_cos.shape[0]} rows, pos_id is {pos_id}")
     if matvec_reduction_size is None:
-        for r in (2048, 1024, 512):
+        for r in (2048, 1024, 512, 256):
             if (Hq * D) % r == 0 and g.intermediate_size % r == 0:
                 matvec_reduction_size = r
                 break

@@ -175,13 +175,14 @@ def test_70b_widths_one_layer():
     assert_logits_parity(gpu_sched.globs.logits, cpu_sched.globs.logits, "70b widths")
 
 
-@pytest.mark.parametrize("tp", [2, 8])
-def test_tensor_parallel_shard_shapes(tp):
-    """One rank's shard of the 70B widths: R = 2048 (tp 2) and 512 (tp 8) slices."""
+@pytest.mark.parametrize("width,tp", [("70b", 2), ("70b", 8), ("8b", 2), ("8b", 4), ("8b", 8)])
+def test_tensor_parallel_shard_shapes(width, tp):
+    """One rank's shard, run on its own: input-column slices of 2048 (70B widths, tp 2), 512
+    (70B tp 8, 8B tp 4), 1024 (8B tp 2) and 256 (8B tp 8: fewer heads than down-proj slices)."""
     from tests.oracle_utils import build_model, build_schedule, fill_kv
     from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
 
-    cfg = small_70b()
+    cfg = small_70b() if width == "70b" else small_8b(num_hidden_layers=1)
     opts = LatencyScheduleOptions(num_attention_partitions=1, coalesce_o_proj=True)
     cpu_model = build_model(cfg, 64, device="cpu", tp_size=tp, tp_rank=tp - 1)
     fill_kv(cpu_model, 40, poison=True)
