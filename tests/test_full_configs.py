@@ -9,8 +9,13 @@
 * run-to-run reproducibility: the same step repeated 50 times must give the same bits.
 
 Tolerance as everywhere: max|a-b|/max|b| <= 2e-2, cosine >= 0.999, argmax equal wherever the
-oracle's top-2 margin exceeds 1e-2 (oracle/llama_ref.py).  The fused argmax must equal
-torch.argmax of the logits the same launch wrote, over the full vocabulary.
+oracle's top-2 margin exceeds 1e-2 (oracle/llama_ref.py).  The two full-depth cases use the
+depth-aware bound instead: with random-init weights every rounding is amplified from layer to
+layer, and the bf16 reference path itself is already 2e-2 away from exact float32 arithmetic
+after 8 layers of the 8B widths (measured on the CPU restatement); the bound is twice the
+oracle's own distance from exact arithmetic, computed in the test for the very step compared,
+and the measured figures are printed.  The fused argmax must equal torch.argmax of the logits
+the same launch wrote, over the full vocabulary.
 """
 
 import pytest
@@ -24,7 +29,7 @@ from megakernels_b200.generators import MK_Generator
 from megakernels_b200.llama import LlamaConfig, LlamaForCausalLM
 from megakernels_b200.model_types import ExtraModelConfig
 from megakernels_b200.scheduler import assign_to_sms, tensorize_instructions
-from oracle.llama_ref import TorchReferenceModel, assert_logits_parity
+from oracle.llama_ref import TorchReferenceModel, assert_logits_parity, parity_metrics
 from tests.gpu_utils import interpreter, make_pair, run_gpu_step
 from tests.oracle_utils import build_schedule, seeded_tokens
 
@@ -67,11 +72,15 @@ def test_llama_8b_full_depth_teacher_forced():
         pos = prefill + i
         out = gen.run(torch.tensor([[tok]], device=DEV), pos)
         gen.check()
+        exact = ref.decode_token_exact(tok, pos)  # reads the cache below pos only: call it first
         want = ref.decode_token(tok, pos)
-        m = assert_logits_parity(g.logits, want, f"8B full depth, pos {pos}")
+        m = assert_logits_parity(g.logits, want, f"8B full depth, pos {pos}", exact=exact)
         assert int(out) == int(torch.argmax(g.logits)), f"fused argmax at pos {pos}"
         assert torch.equal(g.k_cache[:, 0, pos + 1 :].cpu(), ref.k_cache[:, 0, pos + 1 :]), "wrote past the token"
-        print(f"pos {pos}: max_rel {m['max_rel']:.3e} cosine {m['cosine']:.6f} margin {m['top2_margin']:.4f}")
+        floor, ours = parity_metrics(want, exact), parity_metrics(g.logits, exact)
+        print(f"pos {pos}: kernel vs oracle max_rel {m['max_rel']:.3e} cosine {m['cosine']:.6f} "
+              f"(bound {m['max_rel_tol']:.3e}); oracle vs exact {floor['max_rel']:.3e}; "
+              f"kernel vs exact {ours['max_rel']:.3e}; margin {m['top2_margin']:.4f}")
 
 
 def test_llama_1b_full_depth_prompt_then_greedy():
@@ -87,8 +96,10 @@ def test_llama_1b_full_depth_prompt_then_greedy():
     out[:, 0] = gen.prefill(prompt.to(DEV))
     gen.check()
     for pos, tok in enumerate(prompt.tolist()):
+        if pos == prompt_len - 1:
+            exact = ref.decode_token_exact(tok, pos)
         want = ref.decode_token(tok, pos)
-    assert_logits_parity(g.logits, want, "1B after the prompt")
+    assert_logits_parity(g.logits, want, "1B after the prompt", exact=exact)
     # greedy decoding, checked step by step: the oracle is teacher-forced with the kernel's tokens
     for i in range(1, ntok):
         tok = int(out[0, i - 1])
@@ -96,9 +107,11 @@ def test_llama_1b_full_depth_prompt_then_greedy():
         got = gen.run(out[:, i - 1 : i], pos)
         gen.check()
         out[:, i] = got.reshape(-1)
+        exact = ref.decode_token_exact(tok, pos)
         want = ref.decode_token(tok, pos)
-        assert_logits_parity(g.logits, want, f"1B greedy step {i}")
+        m = assert_logits_parity(g.logits, want, f"1B greedy step {i}", exact=exact)
         assert int(got) == int(torch.argmax(g.logits))
+        print(f"step {i}: max_rel {m['max_rel']:.3e} (bound {m['max_rel_tol']:.3e}) cosine {m['cosine']:.6f}")
 
 
 @pytest.mark.parametrize("length", [4096, 16384, 65536])
