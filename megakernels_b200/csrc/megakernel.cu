@@ -730,8 +730,10 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
     } else {
         consumer_sync();
         // every thread's loads of the residual stream have returned (their values went into
-        // the sums above), so later writers may now be let in
-        if (tid == 0 && read_done != nullptr) red_release_gpu_add(read_done, 1);
+        // the sums above), so later writers may now be let in.  A relaxed add is enough: a
+        // load that has delivered its value cannot observe a store issued afterwards, and a
+        // releasing add would stall this thread (and with it warp 0 and the whole ring) on a fence.
+        if (tid == 0 && read_done != nullptr) atomicAdd(read_done, 1);
     }
     if (tid == 0) rec(c, MKB_T_RMS_SUMMED);
     float tot = 0.f;
