@@ -398,7 +398,7 @@ def check_parity(args, gen, schedule, model, cfg, prefill, token, pos, world, tp
         exact = ref.decode_token_exact(token, pos)  # float32 throughout: the oracle's own noise floor
         want = ref.decode_token(token, pos)
         m, floor, ours = parity_metrics(logits, want), parity_metrics(want, exact), parity_metrics(logits, exact)
-        rel_tol, cos_tol = depth_aware_tolerance(want, exact)
+        rel_tol, cos_tol, _ = depth_aware_tolerance(want, exact)
         argmax_ok = m["argmax_equal"] or m["top2_margin"] <= MARGIN_TOL
         result.update(
             ok=bool(m["max_rel"] <= rel_tol and m["cosine"] >= cos_tol and argmax_ok
