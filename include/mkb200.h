@@ -223,19 +223,12 @@ typedef struct MkbGlobals {
                                      accumulators over ranks and divide by the degree (exact) */
     int64_t *residual_acc;        /* int64 [H], zeroed by the caller before every launch like the
                                      barriers: sum of the token's o-proj / down-proj outputs in
-                                     fixed point, accumulated with integer atomics, so the result
-                                     is independent of the order in which SMs arrive and
-                                     bit-identical from run to run.  Word layout: bits 0..53 the
-                                     sum of (value * 2^22 + 2^42) over the contributions (each
-                                     clamped to |value| < 2^19), bits 54..63 their number - a reader
-                                     sees from the word itself whether every column slice of a
-                                     stage has arrived, and the RMSNorm instructions poll their
-                                     words instead of a counter followed by a dependent load.
-                                     When residual_scale > 1, or num_layers * (Hq*D + I) /
-                                     matvec_reduction_size > 1023, the words are plain value * 2^22.
-                                     Residual stream after the launch: hidden_states + decoded
-                                     residual_acc.  Not used (may be NULL) when tp.size > 1; with
-                                     NULL, mkb_launch_no_alloc keeps it in its static array */
+                                     Q31.32 fixed point (value * 2^32), accumulated with integer
+                                     atomics, so the result is independent of the order in which
+                                     SMs arrive and bit-identical from run to run.  The residual
+                                     stream after the launch is hidden_states + residual_acc / 2^32.
+                                     Not used (may be NULL) when tp.size > 1; with NULL,
+                                     mkb_launch_no_alloc keeps it in its static array */
     int32_t upgate_instructions_per_layer; /* RMS + up/gate instructions per layer in `instructions`
                                      (see MKB_BARRIER_ROW_RMS_READ); 0: down-proj does not wait for
                                      them */

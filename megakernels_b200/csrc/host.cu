@@ -329,9 +329,6 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     p.pos_id_ptr = g->pos_id_device;
     p.residual_acc = (long long*)g->residual_acc;
     p.residual_mult = g->residual_scale > 0.f ? (long long)g->residual_scale : 1;
-    // contribution counts inside the accumulator words: only while the whole token's count fits
-    // the field, and not when the host sums the accumulators of several ranks
-    p.acc_counting = (p.residual_mult == 1 && (long long)p.L * ((p.o_in + p.I) / p.R) <= kAccMaxCount) ? 1 : 0;
     p.thr_down_waits_rms = g->upgate_instructions_per_layer;
     if (g->argmax_out && ds) {  // the scratch sits behind the library's own status record
         p.argmax_out = g->argmax_out;

@@ -656,13 +656,9 @@ __device__ __forceinline__ void rms_prefetch(const Ctx& c, const __nv_bfloat16* 
 // accumulators the row-split projections add into; `read_done` (may be null) is a counter
 // bumped once every thread's loads have completed, for producers that must not add to the
 // accumulators before this instruction has read them.
-// With expected >= 0 (and accumulator words that carry counts) every thread polls its own
-// words until they show `expected` contributions: data and completion arrive in ONE round
-// trip, instead of a counter poll followed by a dependent load.
 template <bool LL, bool ACC>
 __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& pf, uint32_t tag = 0,
-                                               int layer = 0, int which = 0, int* read_done = nullptr,
-                                               int expected = -1) {
+                                               int layer = 0, int which = 0, int* read_done = nullptr) {
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float x[2][8];
@@ -695,39 +691,26 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
             rec(c, MKB_T_CONSUMER_WAIT_DONE);
         }
     } else {
-        TpPoll poll;
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             if (pf.chs[k] < 0) continue;
             const uint4 hv = ld_cg_v4(p.hidden + (size_t)pf.chs[k] * 8);
             if constexpr (ACC) {
                 const long long* acc = p.residual_acc + (size_t)pf.chs[k] * 8;
-                const int counting = p.acc_counting;
                 uint4 a[4];
-                while (true) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) a[i] = ld_volatile_v4(acc + 2 * i);
-                    if (expected < 0 || !ok) break;
-                    uint32_t seen = 0;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        seen |= (acc_count(a[i].y) ^ (uint32_t)expected) | (acc_count(a[i].w) ^ (uint32_t)expected);
-                    if (seen == 0) break;
-                    if (!poll.tick(c, layer, 400 + which, pf.chs[k], (int)acc_count(a[0].y))) ok = false;
-                }
+                for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
                 unpack8(hv, x[k]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    x[k][2 * i] += acc_value(a[i].x, a[i].y, counting);
-                    x[k][2 * i + 1] += acc_value(a[i].z, a[i].w, counting);
+                    const long long lo = (long long)(((unsigned long long)a[i].y << 32) | a[i].x);
+                    const long long hi = (long long)(((unsigned long long)a[i].w << 32) | a[i].z);
+                    x[k][2 * i] += __ll2float_rn(lo) * kResidualInvScale;
+                    x[k][2 * i + 1] += __ll2float_rn(hi) * kResidualInvScale;
                 }
             } else {
                 unpack8(hv, x[k]);
             }
-        }
-        if (ACC && expected >= 0 && tid == 0) {
-            c.cta_abort[4] = 0;  // the ring drains again
-            rec(c, MKB_T_CONSUMER_WAIT_DONE);
         }
     }
 #pragma unroll
@@ -745,11 +728,7 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
     if constexpr (LL) {
         if (!consumer_all(ok)) return false;
     } else {
-        if (ACC && expected >= 0) {
-            if (!consumer_all(ok)) return false;
-        } else {
-            consumer_sync();
-        }
+        consumer_sync();
         // every thread's loads of the residual stream have returned (their values went into
         // the sums above), so later writers may now be let in.  A relaxed add is enough: a
         // load that has delivered its value cannot observe a store issued afterwards, and a
@@ -780,19 +759,18 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
 
 // Consumer thread 0 waits for a counter; the verdict reaches all 512 consumer
 // threads through shared memory so that they leave the instruction together.
-// `more_to_come`: a second wait phase follows (the caller clears the stall flag and stamps the time).
 __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerState& cs, int layer,
                                                        int row, int slot, int threshold,
-                                                       bool needed, bool more_to_come = false) {
+                                                       bool needed) {
     volatile int* verdict = verdict_word(c, cs);
     if (threadIdx.x == 0) {
         bool ok = !*c.cta_abort;
         if (ok && needed) {
             c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
             ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
-            if (!more_to_come) c.cta_abort[4] = 0;
+            c.cta_abort[4] = 0;
         }
-        if (!more_to_come) rec(c, MKB_T_CONSUMER_WAIT_DONE);
+        rec(c, MKB_T_CONSUMER_WAIT_DONE);
         *verdict = ok ? 1 : 0;
     }
     consumer_sync();
@@ -805,9 +783,8 @@ __device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefet
     return rms_activation<true, false>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
 }
 
-__device__ __noinline__ bool rms_activation_plain(const Ctx& c, const RmsPrefetch pf, int* read_done,
-                                                  int expected, int layer, int which) {
-    return rms_activation<false, true>(c, pf, 0u, layer, which, read_done, expected);
+__device__ __noinline__ void rms_activation_plain(const Ctx& c, const RmsPrefetch pf, int* read_done) {
+    rms_activation<false, true>(c, pf, 0u, 0, 0, read_done);
 }
 
 // kTP selects the tensor-parallel build of the kernel.  It is a compile-time switch and the two
@@ -817,7 +794,7 @@ template <bool kTP>
 __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
                                                     const __nv_bfloat16* norm_w, int nblocks,
                                                     int wait_layer, int wait_row, int threshold,
-                                                    bool needed, int expected, int* read_done = nullptr) {
+                                                    bool needed, int* read_done = nullptr) {
     RmsPrefetch pf;
     rms_prefetch(c, norm_w, pf);
     bool tagged = false;
@@ -830,22 +807,11 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
         }
     }
     if (!tagged) {
-        if (kTP && c.p->tp_size > 1) {
-            // the tensor-parallel exchange keeps the running residual stream in its tagged buffer;
-            // the only plain read there is the token embedding before the first all-reduce
-            if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
-            rms_activation<false, false>(c, pf);
-        } else {
-            // Two phases: thread 0 watches the (cheap) counter until the producers are nearly
-            // done, then every thread polls the accumulator words it needs, which carry their
-            // own contribution counts.  The last additions are thus seen one round trip after
-            // they land; a counter alone costs the producer's fence, the poll and a dependent load.
-            const bool poll_data = needed && c.p->acc_counting != 0;
-            const int early = poll_data ? threshold - (threshold >> 3) : threshold;
-            if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, early, needed, poll_data)) return false;
-            const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
-            if (!rms_activation_plain(c, pf, read_done, poll_data ? expected : -1, wait_layer, which)) return false;
-        }
+        if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
+        // the tensor-parallel exchange keeps the running residual stream in its tagged buffer;
+        // the only plain read there is the token embedding before the first all-reduce
+        if (kTP && c.p->tp_size > 1) rms_activation<false, false>(c, pf);
+        else rms_activation_plain(c, pf, read_done);
     }
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->H);
@@ -1421,15 +1387,11 @@ __device__ __forceinline__ bool consumer_tp_all_reduce(const Ctx& c, ConsumerSta
 template <bool kTP>
 __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
     const KParams& p = *c.p;
-    // contributions every element of the residual stream receives per layer: one per input
-    // column slice of the o-proj and of the down-proj
-    const int per_layer = (p.o_in + p.I) / p.R;
     switch (op) {
         case MKB_OP_RMS_QKV_ROPE_APPEND: {
             const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
             return consumer_rms_matvec<kTP>(c, cs, p.attn_ln_w + (size_t)layer * p.H, eb - sb, layer - 1,
-                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, layer > 0,
-                                       layer * per_layer);
+                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, layer > 0);
         }
         case MKB_OP_RMS_UPGATE_SILU: {
             const int layer = __ldg(w + 1), n = __ldg(w + 2);
@@ -1437,14 +1399,12 @@ __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const i
             // for one arrival per up/gate instruction on row MKB_BARRIER_ROW_RMS_READ
             return consumer_rms_matvec<kTP>(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
                                        MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true,
-                                       layer * per_layer + p.o_in / p.R,
                                        bar_addr(p, layer, MKB_BARRIER_ROW_RMS_READ, 0));
         }
         default: {  // MKB_OP_RMS_LM_HEAD
             const int sb = __ldg(w + 1), eb = __ldg(w + 2);
             return consumer_rms_matvec<kTP>(c, cs, p.lm_norm_w, eb - sb, p.L - 1,
-                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true,
-                                       p.L * per_layer);
+                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true);
         }
     }
 }
@@ -1694,7 +1654,7 @@ __device__ void storer_main(Ctx c) {
                         const float v = storer_take_block(c, ss, lane, kr_partials);
                         if (lane < 16)
                             red_add_u64(p.residual_acc + b * kBlockRows + row,
-                                        acc_contribution(v, p.residual_mult, p.acc_counting));
+                                        (unsigned long long)(__float2ll_rn(v * kResidualScale) * p.residual_mult));
                     }
                 }
                 storer_signal(ss, lane, bar_addr(p, layer, op - 1, 0), eb - sb);

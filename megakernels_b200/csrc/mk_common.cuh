@@ -74,14 +74,10 @@ struct KParams {
     __nv_bfloat16 *hidden, *q_rope, *attn_out, *silu_out, *logits;
     float *attn_lse, *attn_o;
     // Residual stream of the token = hidden (the embedding, never written) + residual_acc:
-    // o-proj / down-proj add their outputs as 64-bit fixed point with integer atomics, so the
-    // sum does not depend on the order in which the SMs arrive (bit-reproducible).  Word
-    // layout with `acc_counting`: bits 0..53 sum of (value * 2^22 + 2^42), bits 54..63 the number
-    // of contributions, so that a reader can tell from the word itself whether all column
-    // slices of a stage have arrived (mk_common.cuh: acc_*).  Without: plain value * 2^22.
+    // o-proj / down-proj add their outputs as 64-bit fixed point (Q31.32) with integer atomics,
+    // so the sum does not depend on the order in which the SMs arrive (bit-reproducible).
     long long* residual_acc;  // [H], zeroed by the caller before every launch
     long long residual_mult;  // integer factor on every contribution (1; the TP degree under the NCCL exchange)
-    int acc_counting;
     // dims
     int L, H, I, D, Hq, Hkv, V, T, B, max_partials, R;
     int qkv_rows;  // (Hq + 2 Hkv) * D
@@ -275,34 +271,9 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
 __device__ __forceinline__ void red_add_u64(void* p, unsigned long long v) {
     asm volatile("red.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-// Fixed-point format of the residual accumulators (see KParams::residual_acc).  A contribution
-// is clamped to |v| < 2^19, so value * 2^22 + 2^42 lies in (0, 2^43) and up to 1023 of them
-// fit below bit 54 without a carry into the count.
-constexpr float kAccScale = 4194304.f;  // 2^22
-constexpr float kAccInvScale = 1.f / 4194304.f;
-constexpr float kAccMaxValue = 524287.f;
-constexpr long long kAccBias = 1ll << 42;
-constexpr int kAccCountShift = 54;
-constexpr int kAccMaxCount = 1023;
-__device__ __forceinline__ unsigned long long acc_contribution(float v, long long mult, int counting) {
-    v = fminf(fmaxf(v, -kAccMaxValue), kAccMaxValue);
-    long long q = __float2ll_rn(v * kAccScale);
-    if (counting) q += kAccBias + (1ll << kAccCountShift);
-    return (unsigned long long)(q * mult);
-}
-// count field of an accumulator word given as {lo, hi}
-__device__ __forceinline__ uint32_t acc_count(uint32_t hi) { return hi >> (kAccCountShift - 32); }
-__device__ __forceinline__ float acc_value(uint32_t lo, uint32_t hi, int counting) {
-    long long q;
-    if (counting) {
-        const uint32_t n = acc_count(hi);
-        const unsigned long long low = ((unsigned long long)(hi & ((1u << (kAccCountShift - 32)) - 1u)) << 32) | lo;
-        q = (long long)low - (long long)n * kAccBias;
-    } else {
-        q = (long long)(((unsigned long long)hi << 32) | lo);
-    }
-    return __ll2float_rn(q) * kAccInvScale;
-}
+// fixed-point format of the residual accumulators: value * 2^32 in a signed 64-bit integer
+constexpr float kResidualScale = 4294967296.f;
+constexpr float kResidualInvScale = 1.f / 4294967296.f;
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -98,10 +98,9 @@ class BaseGlobals:
         self.pos_id_device: Tensor | None = None  # int32[1]; overrides pos_id when set
         self.tp: TensorParallelState | None = None  # in-kernel tensor-parallel all-reduce
         self.argmax_out: Tensor | None = None  # int32[1]: the kernel's own argmax over the logits
-        # int64 [H]: the token's o-proj / down-proj outputs summed in fixed point by the kernel
-        # (integer atomics: the same bits whatever order the SMs arrive in; word layout in
-        # include/mkb200.h, MkbGlobals.residual_acc).  The kernel never writes
-        # ``hidden_states``; the residual stream is ``residual_stream()``.
+        # int64 [H]: the token's o-proj / down-proj outputs summed in Q31.32 fixed point by the
+        # kernel (integer atomics: the same bits whatever order the SMs arrive in).  The kernel
+        # never writes ``hidden_states``; the residual stream is ``residual_stream()``.
         self.residual_acc: Tensor | None = None
         # one int32 buffer behind ``barriers`` and ``residual_acc``, so that a single fill
         # resets both before a launch
@@ -118,17 +117,8 @@ class BaseGlobals:
         """
         h = self.hidden_states.float()
         if self.residual_acc is not None:
-            h = (h.double() + decode_residual_acc(self.residual_acc, self.residual_acc_counts())).float()
+            h = (h.double() + self.residual_acc.double() * 2.0**-32).float()
         return h
-
-    def residual_acc_counts(self) -> bool:
-        """Whether the accumulator words carry contribution counts (the library's rule: no host
-        exchange of the accumulators, and the token's total count fits the 10-bit field)."""
-        splits = getattr(self, "num_o_proj_col_splits", None)
-        if splits is None:
-            return False
-        per_layer = self.num_o_proj_col_splits() + self.num_down_proj_col_splits()
-        return self.residual_scale == 1.0 and self.num_hidden_layers * per_layer <= 1023
 
     def sm_count(self) -> int:
         return get_sm_count(self.device)
@@ -155,16 +145,6 @@ class BaseGlobals:
             _, adiff, rdiff = diff_tensors(a, b, f.name, verbose=verbose)
             out[f.name] = (float(adiff.max()), float(rdiff.mean()))
         return out
-
-
-def decode_residual_acc(acc: Tensor, counting: bool) -> Tensor:
-    """Accumulator words -> float64 values.  With counts: bits 0..53 hold the sum of
-    (value * 2^22 + 2^42) over the contributions, bits 54..63 their number; else value * 2^22."""
-    if not counting:
-        return acc.double() * 2.0**-22
-    n = (acc >> 54) & 1023
-    low = acc & ((1 << 54) - 1)
-    return (low - n * (1 << 42)).double() * 2.0**-22
 
 
 def diff_tensors(a: Tensor, b: Tensor, name: str, verbose: bool = True):
