@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define MKB_ABI_VERSION 3
+#define MKB_ABI_VERSION 4
 
 /* instruction encoding (megakernels/scheduler.py:13-14) */
 #define MKB_INTS_PER_INSTRUCTION 32
@@ -45,6 +45,14 @@ enum {
      * tensor-parallel all-reduce of the residual stream, see MkbTensorParallel.
      * words: [8, layer, which (0 after o-proj, 1 after down-proj), chunk, num_chunks] */
     MKB_OP_TP_ALL_REDUCE = 8,
+    /* No counterpart in the reference's latency instruction set (its kernel decodes one
+     * sequence and fuses the norm into the consuming matvec).  Batched launches only
+     * (MkbGlobals.batch > 1): RMSNorm of ONE sequence's residual stream into `normed_states`,
+     * so that the 148 SMs do not each normalise all sequences.
+     * words: [9, layer, which (0 attention norm, 1 MLP norm, 2 final norm), sequence];
+     * counts into barriers[layer][MKB_BARRIER_ROW_RMS_NORM][which]; the RMS + matvec
+     * opcodes 1, 5 and 7 then wait for `batch` arrivals there instead of normalising. */
+    MKB_OP_RMS_NORM = 9,
 };
 
 /* Barrier rows: opcode k counts into row k - 1 (rows 0..6), as in the reference.  Row 8 has
@@ -54,6 +62,9 @@ enum {
  * orders down-proj after the up/gate blocks of its input slice only, matvec_adds.cu:181-186,
  * which leaves a slow SM reading a residual that already holds part of the layer's output). */
 #define MKB_BARRIER_ROW_RMS_READ 8
+#define MKB_BARRIER_ROW_RMS_NORM 9 /* batched launches: see MKB_OP_RMS_NORM */
+
+#define MKB_MAX_BATCH 8
 
 /* MkbGlobals.flags */
 #define MKB_FLAG_RECORD_TIMINGS 1u /* write per-instruction event times (ns) into `timings` */
@@ -232,7 +243,26 @@ typedef struct MkbGlobals {
     int32_t upgate_instructions_per_layer; /* RMS + up/gate instructions per layer in `instructions`
                                      (see MKB_BARRIER_ROW_RMS_READ); 0: down-proj does not wait for
                                      them */
-    int32_t reserved0;
+
+    /* Batched decode (no counterpart in the reference's latency kernel): `batch` independent
+     * sequences, 2..MKB_MAX_BATCH, advance by one token in ONE launch that streams the weights
+     * once (the sequences' activation vectors are the columns of the MMA's B operand).  Then
+     *   - every activation tensor has a leading batch dimension: hidden_states [batch, H],
+     *     residual_acc [batch, H], post_ln_rope_q / attn_out [batch, Hq*D], silu_out [batch, I],
+     *     logits [batch, V], attn_lse_intermediates [batch, Hq, max_partials],
+     *     attn_out_intermediates [batch, Hq, max_partials, D], argmax_out [batch];
+     *   - sequence s lives in slot s of the KV cache (kv_batch >= batch) at its own position
+     *     pos_ids[s] (or pos_id_device[s]); lengths may differ;
+     *   - PartialAttention carries the sequence as a sixth word, AttentionReduction after its
+     *     output index, and barriers[layer][1] has one slot per (sequence, Q head):
+     *     barrier_width >= batch * Hq;
+     *   - the schedule holds one MKB_OP_RMS_NORM per sequence and norm; `normed_states`
+     *     (bf16 [batch, H]) receives their output;
+     *   - hidden_size <= 4096, tp.size <= 1, not available through mkb_launch_no_alloc.
+     * batch 0 or 1: the single-sequence kernel and the layout of the reference. */
+    int32_t batch;
+    int32_t pos_ids[8];
+    void *normed_states;
 
     MkbTensorParallel tp;         /* in-kernel tensor-parallel all-reduce; tp.size <= 1: off */
     int32_t *argmax_out;          /* if not NULL: device int32 that receives argmax(logits) (smallest

@@ -15,6 +15,10 @@ namespace mkb {
 __global__ void megakernel(const __grid_constant__ KParams p);
 __global__ void megakernel_tp(const __grid_constant__ KParams p);
 }
+namespace mkb_batched {  // megakernel_batched.cu
+int max_batch();
+cudaError_t launch(const void* params, size_t params_bytes, int grid, cudaStream_t stream);
+}
 
 using namespace mkb;
 
@@ -217,7 +221,7 @@ int validate(const MkbGlobals* g) {
         return fail(MKB_ERR_INVALID_ARGUMENT, "barriers tensor too small: ops %d width %d", g->barrier_ops, g->barrier_width);
     if (g->kv_batch < 1 || g->kv_max_len < 1)
         return fail(MKB_ERR_INVALID_ARGUMENT, "KV cache needs batch >= 1 and length >= 1");
-    if (!g->pos_id_device && (g->pos_id < 0 || g->pos_id >= g->kv_max_len))
+    if (g->batch <= 1 && !g->pos_id_device && (g->pos_id < 0 || g->pos_id >= g->kv_max_len))
         return fail(MKB_ERR_INVALID_ARGUMENT, "pos_id %d outside the KV cache length %d", g->pos_id, g->kv_max_len);
     if (g->max_partials < 1) return fail(MKB_ERR_INVALID_ARGUMENT, "max_partials must be >= 1");
     const MkbTensorParallel& tp = g->tp;
@@ -243,6 +247,26 @@ int validate(const MkbGlobals* g) {
         if (g->residual_scale != 0.f && (g->residual_scale < 1.f || g->residual_scale != (float)(int)g->residual_scale))
             return fail(MKB_ERR_INVALID_ARGUMENT, "residual_scale %g must be a positive integer", g->residual_scale);
     }
+    if (g->batch > 1) {
+        if (g->batch > MKB_MAX_BATCH || g->batch > mkb_batched::max_batch())
+            return fail(MKB_ERR_UNSUPPORTED, "batch %d: at most %d sequences per launch", g->batch, MKB_MAX_BATCH);
+        if (H > 4096) return fail(MKB_ERR_UNSUPPORTED, "batched decode supports hidden_size <= 4096, got %d", H);
+        if (tp.size > 1) return fail(MKB_ERR_UNSUPPORTED, "batched decode has no tensor-parallel variant");
+        if (!g->normed_states || !aligned16(g->normed_states))
+            return fail(MKB_ERR_INVALID_ARGUMENT, "batch > 1 needs normed_states (bf16 [batch, H], 16-byte aligned)");
+        if (g->kv_batch < g->batch)
+            return fail(MKB_ERR_INVALID_ARGUMENT, "KV cache holds %d sequences, batch is %d", g->kv_batch, g->batch);
+        if (g->barrier_width < g->batch * Hq || g->barrier_ops <= MKB_BARRIER_ROW_RMS_NORM)
+            return fail(MKB_ERR_INVALID_ARGUMENT, "batch %d needs barrier_width >= %d and barrier_ops > %d",
+                        g->batch, g->batch * Hq, MKB_BARRIER_ROW_RMS_NORM);
+        if (!g->pos_id_device)
+            for (int s = 0; s < g->batch; ++s)
+                if (g->pos_ids[s] < 0 || g->pos_ids[s] >= g->kv_max_len)
+                    return fail(MKB_ERR_INVALID_ARGUMENT, "pos_ids[%d] = %d outside the KV cache length %d", s,
+                                g->pos_ids[s], g->kv_max_len);
+    } else if (g->batch < 0) {
+        return fail(MKB_ERR_INVALID_ARGUMENT, "batch %d", g->batch);
+    }
     if (g->upgate_instructions_per_layer < 0 || g->barrier_ops <= MKB_BARRIER_ROW_RMS_READ)
         return fail(MKB_ERR_INVALID_ARGUMENT, "upgate_instructions_per_layer %d / barrier_ops %d (row %d is needed)",
                     g->upgate_instructions_per_layer, g->barrier_ops, MKB_BARRIER_ROW_RMS_READ);
@@ -263,7 +287,7 @@ int device_state(DeviceState** out) {
         MKB_CUDA(cudaFuncSetAttribute(megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc));
         MKB_CUDA(cudaFuncSetAttribute(megakernel_tp, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc));
         // status record, then the fused-argmax scratch: arrival counter + {value, index} per CTA
-        const size_t words = MKB_STATUS_WORDS + 2 + 2 * (size_t)ds.sm_count;
+        const size_t words = MKB_STATUS_WORDS + 2 + 2 * (size_t)ds.sm_count * MKB_MAX_BATCH;
         MKB_CUDA(cudaMalloc(&ds.status, words * sizeof(int)));
         MKB_CUDA(cudaMemset(ds.status, 0, words * sizeof(int)));
         ds.attr_set = true;
@@ -329,7 +353,11 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     p.pos_id_ptr = g->pos_id_device;
     p.residual_acc = (long long*)g->residual_acc;
     p.residual_mult = g->residual_scale > 0.f ? (long long)g->residual_scale : 1;
-    p.thr_down_waits_rms = g->upgate_instructions_per_layer;
+    p.batch = g->batch > 1 ? g->batch : 1;
+    for (int s = 0; s < 8; ++s) p.pos_ids[s] = g->pos_ids[s];
+    p.normed = (__nv_bfloat16*)g->normed_states;
+    // batched launches order the down-proj behind the RMS_NORM instructions through the up/gate
+    p.thr_down_waits_rms = g->batch > 1 ? 0 : g->upgate_instructions_per_layer;
     if (g->argmax_out && ds) {  // the scratch sits behind the library's own status record
         p.argmax_out = g->argmax_out;
         p.argmax_scratch = ds->status + MKB_STATUS_WORDS;
@@ -424,6 +452,10 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     KParams p;
     rc = prepare_launch(g, ds, (g && g->status) ? g->status : ds->status, ds->sm_count, p);
     if (rc) return rc;
+    if (p.batch > 1) {
+        MKB_CUDA(mkb_batched::launch(&p, sizeof(p), g->num_sms, (cudaStream_t)cuda_stream));
+        return MKB_OK;
+    }
     if (p.tp_size > 1)
         megakernel_tp<<<g->num_sms, kBlockThreads, kSmemAlloc, (cudaStream_t)cuda_stream>>>(p);
     else
@@ -485,12 +517,14 @@ int mkb_validate_instructions(const MkbGlobals* g, const int32_t* host_instructi
                     if (w[3] < 1 || w[4] < 0 || w[4] >= w[3]) return bad("partial index outside num_partials");
                     if (!g->skip_attn_reduction && w[4] >= g->max_partials) return bad("partial index beyond max_partials");
                     if (g->skip_attn_reduction && w[3] != 1) return bad("skip_attn_reduction needs num_partials == 1");
+                    if (w[5] < 0 || w[5] >= (g->batch > 1 ? g->batch : 1)) return bad("sequence outside the batch");
                     break;
                 case MKB_OP_ATTENTION_REDUCTION: {
                     if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
                     if (w[2] < 0 || w[2] + 4 > Hq) return bad("head range outside the Q heads");
                     const int n = w[5];
-                    if (n < 1 || n > 25) return bad("reduction list length must be 1..25");
+                    if (n < 1 || n > 24) return bad("reduction list length must be 1..24");
+                    if (w[7 + n] < 0 || w[7 + n] >= (g->batch > 1 ? g->batch : 1)) return bad("sequence outside the batch");
                     for (int j = 0; j < n; ++j)
                         if (w[6 + j] < 0 || w[6 + j] >= g->max_partials) return bad("reduction index beyond max_partials");
                     if (!w[4] && (w[6 + n] < 0 || w[6 + n] >= g->max_partials)) return bad("output partial index beyond max_partials");
@@ -513,6 +547,12 @@ int mkb_validate_instructions(const MkbGlobals* g, const int32_t* host_instructi
                     break;
                 case MKB_OP_RMS_LM_HEAD:
                     if (!range_ok(w[1], w[2], g->vocab_size / 16)) return bad("block range outside the vocabulary");
+                    break;
+                case MKB_OP_RMS_NORM:
+                    if (g->batch <= 1) return bad("RMS_NORM instruction in a single-sequence launch");
+                    if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
+                    if (w[2] < 0 || w[2] > 2) return bad("which must be 0, 1 or 2");
+                    if (w[3] < 0 || w[3] >= g->batch) return bad("sequence outside the batch");
                     break;
                 case MKB_OP_TP_ALL_REDUCE:
                     if (g->tp.size <= 1) return bad("all-reduce instruction without tensor parallelism");

@@ -17,7 +17,7 @@
 //                   logits) and signals the next op's barrier counter.
 #include "mk_common.cuh"
 
-namespace mkb {
+namespace MKB_NAMESPACE {
 
 // --------------------------------------------------------------------------- //
 // control / error reporting
@@ -26,10 +26,16 @@ struct Ctx {
     const KParams* p;
     uint32_t base;            // shared-window address of the aligned smem base
     volatile int* cta_abort;  // generic pointer to the CTA-wide abort word
-    int pos;                  // position of the token being decoded
+    int pos;                  // position of the token being decoded (sequence 0)
     int instr;                // instruction index being executed (for reports)
     int opcode;
     int role;
+
+    // position of sequence b's token (batched build: kept behind the control words)
+    __device__ __forceinline__ int pos_of(int b) const {
+        if constexpr (kBatch == 1) return pos;
+        else return cta_abort[8 + b];
+    }
 
     __device__ __forceinline__ uint32_t full_bar(int slot) const { return base + kSmemBars + slot * 8; }
     __device__ __forceinline__ uint32_t empty_bar(int slot) const {
@@ -308,7 +314,7 @@ struct StreamCursor {
     int spb = 1;                        // stages per block
     uint32_t bytes = 0;
     int kvh = 0, t0 = 0, lb = 0, ts = 0;
-    int pos = 0;  // position of the token being decoded
+    const Ctx* ctx = nullptr;  // positions of the tokens being decoded
 
     __device__ __forceinline__ void set_matrix(const CUtensorMap* m, int kc, int chunk0_, int layer_) {
         map = m;
@@ -351,9 +357,10 @@ struct StreamCursor {
                 set_matrix(&p.lm_map, p.H, 0, 0);
                 break;
             case MKB_OP_PARTIAL_ATTENTION: {
-                const AttnRange r = attn_range(p, pos, __ldg(w + 3), __ldg(w + 4));
+                const int seq = kBatch == 1 ? 0 : __ldg(w + 5);
+                const AttnRange r = attn_range(p, ctx->pos_of(seq), __ldg(w + 3), __ldg(w + 4));
                 kvh = __ldg(w + 2);
-                lb = __ldg(w + 1) * p.B;
+                lb = __ldg(w + 1) * p.B + seq;
                 t0 = r.t0;
                 ts = (kStageBytes / 4) / p.D;
                 eb = r.n_stages;
@@ -427,7 +434,7 @@ __device__ void loader_main(Ctx c) {
         }
     }
     StreamCursor issue, ahead;  // `ahead` is never behind `issue`
-    issue.pos = ahead.pos = c.pos;
+    issue.ctx = ahead.ctx = &c;
     StageDesc d, da;
     uint32_t stage = 0;       // stages copied into the ring so far
     uint32_t ahead_stage = 0; // stages the look-ahead cursor has passed
@@ -562,7 +569,8 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
     const uint32_t line = (uint32_t)(warp * 16 + row0) * 128u;
     const uint32_t off_a = line + (uint32_t)((t ^ row0) << 4);
     const uint32_t off_b = line + (uint32_t)(((t + 4) ^ row0) << 4);
-    const uint32_t act0 = c.base + kSmemAttn + (uint32_t)(warp * 64 + t * 8) * 2u;
+    // batched build: column g of the B operand is sequence g's activation vector
+    const uint32_t act0 = c.base + kSmemAttn + (uint32_t)(warp * 64 + t * 8) * 2u + (uint32_t)(g * kActStride);
 
     for (int b = 0; b < nblocks; ++b) {
         float d[4] = {0.f, 0.f, 0.f, 0.f};
@@ -575,7 +583,7 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
                 const uint4 w2 = lds_v4(sbase + off_b);
                 const uint4 w3 = lds_v4(sbase + off_b + 8 * 128);
                 uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-                if (g == 0) {
+                if (kBatch > 1 || g == 0) {
                     x0 = lds_v4(act0 + (uint32_t)st * (kStageCols * 2));
                     x1 = lds_v4(act0 + (uint32_t)st * (kStageCols * 2) + 64);
                 }
@@ -590,11 +598,21 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
         if (!cs.dead && !mbar_try_wait(obar, cs.ophase ^ 1u)) {
             if (!mbar_wait_slow(c, obar, cs.ophase ^ 1u, true)) cs.dead = true;
         }
-        if (t == 0) {  // column 0 of D: rows row0 (d[0]) and row0 + 8 (d[2])
+        if constexpr (kBatch == 1) {
+            if (t == 0) {  // column 0 of D: rows row0 (d[0]) and row0 + 8 (d[2])
+                float* out = reinterpret_cast<float*>(__cvta_shared_to_generic(
+                    c.base + kSmemOut + (cs.oslot * kOutSlotFloats + row0 * 16 + warp) * 4));
+                out[0] = d[0];
+                out[8 * 16] = d[2];
+            }
+        } else {
+            // columns 2t, 2t + 1 of D are sequences 2t, 2t + 1: slot layout [row][sequence][warp]
             float* out = reinterpret_cast<float*>(__cvta_shared_to_generic(
-                c.base + kSmemOut + (cs.oslot * kOutSlotFloats + row0 * 16 + warp) * 4));
+                c.base + kSmemOut + (cs.oslot * kOutSlotFloats + (row0 * kBatch + 2 * t) * 16 + warp) * 4));
             out[0] = d[0];
-            out[8 * 16] = d[2];
+            out[16] = d[1];
+            out[8 * kBatch * 16] = d[2];
+            out[8 * kBatch * 16 + 16] = d[3];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(c.out_full_bar(cs.oslot));
@@ -620,15 +638,33 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c2), "r"(d) : "memory");
 }
 
-// Park a bf16 activation vector of `kc` elements in shared memory.
-__device__ __forceinline__ void stage_activation(const Ctx& c, const __nv_bfloat16* vec, int kc) {
+// Park a bf16 activation vector of `kc` elements in shared memory (batched build: the vectors
+// of all sequences, `seq_stride` elements apart in global memory; unused columns are zeroed so
+// that no stale NaN pattern ever enters an MMA).
+__device__ __forceinline__ void stage_activation(const Ctx& c, const __nv_bfloat16* vec, int kc,
+                                                 size_t seq_stride = 0) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if constexpr (kBatch == 1) {
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const int ch = own_chunk(warp, lane, k, kc);
+        for (int k = 0; k < 2; ++k) {
+            const int ch = own_chunk(warp, lane, k, kc);
+            if (ch >= 0) {
+                const uint4 v = ld_cg_v4(vec + (size_t)ch * 8);
+                st_shared_v4(c.base + kSmemAttn + ch * 16, v.x, v.y, v.z, v.w);
+            }
+        }
+    } else {
+        const int ch = own_chunk(warp, lane, 0, kc);  // kc <= 4096: one chunk per thread
         if (ch >= 0) {
-            const uint4 v = ld_cg_v4(vec + (size_t)ch * 8);
-            st_shared_v4(c.base + kSmemAttn + ch * 16, v.x, v.y, v.z, v.w);
+            uint4 v[kBatch];
+#pragma unroll
+            for (int s = 0; s < kBatch; ++s) {
+                v[s] = make_uint4(0, 0, 0, 0);
+                if (s < c.p->batch) v[s] = ld_cg_v4(vec + s * seq_stride + (size_t)ch * 8);
+            }
+#pragma unroll
+            for (int s = 0; s < kBatch; ++s)
+                st_shared_v4(c.base + kSmemAttn + s * kActStride + ch * 16, v[s].x, v[s].y, v[s].z, v[s].w);
         }
     }
     __syncwarp();
@@ -656,11 +692,15 @@ __device__ __forceinline__ void rms_prefetch(const Ctx& c, const __nv_bfloat16* 
 // accumulators the row-split projections add into; `read_done` (may be null) is a counter
 // bumped once every thread's loads have completed, for producers that must not add to the
 // accumulators before this instruction has read them.
+// Batched build: `seq` selects the sequence whose residual stream is normalised, and the result
+// goes to the global `normed` buffer (one RMS_NORM instruction per sequence) instead of shared memory.
 template <bool LL, bool ACC>
 __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& pf, uint32_t tag = 0,
-                                               int layer = 0, int which = 0, int* read_done = nullptr) {
+                                               int layer = 0, int which = 0, int* read_done = nullptr,
+                                               int seq = 0) {
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t seq_off = kBatch == 1 ? 0 : (size_t)seq * p.H;
     float x[2][8];
     float ss = 0.f;
     bool ok = true;
@@ -694,9 +734,9 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             if (pf.chs[k] < 0) continue;
-            const uint4 hv = ld_cg_v4(p.hidden + (size_t)pf.chs[k] * 8);
+            const uint4 hv = ld_cg_v4(p.hidden + seq_off + (size_t)pf.chs[k] * 8);
             if constexpr (ACC) {
-                const long long* acc = p.residual_acc + (size_t)pf.chs[k] * 8;
+                const long long* acc = p.residual_acc + seq_off + (size_t)pf.chs[k] * 8;
                 uint4 a[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
@@ -750,7 +790,10 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
             for (int e = 0; e < 4; ++e)
                 o[e] = pack_bf16x2(wgt[2 * e] * bf16_round(x[k][2 * e] * rstd),
                                    wgt[2 * e + 1] * bf16_round(x[k][2 * e + 1] * rstd));
-            st_shared_v4(c.base + kSmemAttn + pf.chs[k] * 16, o[0], o[1], o[2], o[3]);
+            if constexpr (kBatch == 1)
+                st_shared_v4(c.base + kSmemAttn + pf.chs[k] * 16, o[0], o[1], o[2], o[3]);
+            else
+                *reinterpret_cast<uint4*>(p.normed + seq_off + (size_t)pf.chs[k] * 8) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
     __syncwarp();
@@ -783,8 +826,8 @@ __device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefet
     return rms_activation<true, false>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
 }
 
-__device__ __noinline__ void rms_activation_plain(const Ctx& c, const RmsPrefetch pf, int* read_done) {
-    rms_activation<false, true>(c, pf, 0u, 0, 0, read_done);
+__device__ __noinline__ void rms_activation_plain(const Ctx& c, const RmsPrefetch pf, int* read_done, int seq = 0) {
+    rms_activation<false, true>(c, pf, 0u, 0, 0, read_done, seq);
 }
 
 // kTP selects the tensor-parallel build of the kernel.  It is a compile-time switch and the two
@@ -794,7 +837,18 @@ template <bool kTP>
 __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState& cs,
                                                     const __nv_bfloat16* norm_w, int nblocks,
                                                     int wait_layer, int wait_row, int threshold,
-                                                    bool needed, int* read_done = nullptr) {
+                                                    bool needed, int* read_done = nullptr,
+                                                    int norm_layer = 0, int norm_slot = 0) {
+    if constexpr (kBatch > 1) {
+        // batched build: RMS_NORM instructions (one per sequence) have published the normalised
+        // activations of all sequences; wait for them and park the vectors
+        if (!consumers_wait_counter(c, cs, norm_layer, MKB_BARRIER_ROW_RMS_NORM, norm_slot, c.p->batch, true))
+            return false;
+        stage_activation(c, c.p->normed, c.p->H, (size_t)c.p->H);
+        if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
+        consume_blocks(c, cs, nblocks, c.p->H);
+        return true;
+    }
     RmsPrefetch pf;
     rms_prefetch(c, norm_w, pf);
     bool tagged = false;
@@ -844,7 +898,7 @@ __device__ __forceinline__ bool consumer_plain_matvec(const Ctx& c, ConsumerStat
                                                       const __nv_bfloat16* vec, int nblocks,
                                                       int wait_layer, int wait_row, int wait_slot,
                                                       int threshold, const int* also = nullptr,
-                                                      int also_threshold = 0) {
+                                                      int also_threshold = 0, size_t seq_stride = 0) {
     if (also != nullptr) {
         const int lane = threadIdx.x & 31;
         const int* addr = lane == 0 ? bar_addr(*c.p, wait_layer, wait_row, wait_slot) : lane == 1 ? also : nullptr;
@@ -854,7 +908,7 @@ __device__ __forceinline__ bool consumer_plain_matvec(const Ctx& c, ConsumerStat
     } else if (!consumers_wait_counter(c, cs, wait_layer, wait_row, wait_slot, threshold, true)) {
         return false;
     }
-    stage_activation(c, vec, c.p->R);
+    stage_activation(c, vec, c.p->R, seq_stride);
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->R);
     return true;
@@ -934,7 +988,15 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
     const KParams& p = *c.p;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int layer = __ldg(w + 1), kvh = __ldg(w + 2), np = __ldg(w + 3), pi = __ldg(w + 4);
-    const AttnRange r = attn_range(p, c.pos, np, pi);
+    // batched build: the sequence this instruction serves, its position and its activation rows
+    const int seq = kBatch == 1 ? 0 : __ldg(w + 5);
+    const int pos_tok = c.pos_of(seq);
+    const AttnRange r = attn_range(p, pos_tok, np, pi);
+    const __nv_bfloat16* q_rope = p.q_rope + (size_t)seq * p.o_in;
+    __nv_bfloat16* attn_out = p.attn_out + (size_t)seq * p.o_in;
+    float* attn_o = p.attn_o + (size_t)seq * p.Hq * p.max_partials * D;
+    float* attn_lse = p.attn_lse + (size_t)seq * p.Hq * p.max_partials;
+    const int part_slot0 = seq * p.Hq;  // this sequence's slots in the partial-attention barrier row
 
     // barrier: the GQA query heads, then this KV head's K and V blocks
     {
@@ -978,7 +1040,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
 #pragma unroll
     for (int j = 0; j < KP; ++j) {
         qa[j] = make_uint4(0, 0, 0, 0);
-        if (head_ok) qa[j] = ld_cg_v4(p.q_rope + (size_t)(kvh * GQA + g) * D + (t + 4 * j) * 8);
+        if (head_ok) qa[j] = ld_cg_v4(q_rope + (size_t)(kvh * GQA + g) * D + (t + 4 * j) * 8);
     }
     if (tid == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     // the token being decoded: its K/V were appended by another SM in this launch,
@@ -992,13 +1054,13 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
 #pragma unroll
     for (int h = 0; h < GQA; ++h) s_cur[h] = -INFINITY;
     if (warp == 0 && r.has_cur) {
-        const size_t off = (((size_t)layer * p.B) * p.T + c.pos) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
+        const size_t off = (((size_t)layer * p.B + seq) * p.T + pos_tok) * p.Hkv * D + (size_t)kvh * D + lane * DPL;
         load_row_gmem<DPL>(p.k_cache + off, k_cur);
         load_row_gmem<DPL>(p.v_cache + off, v_cur);
 #pragma unroll
         for (int h = 0; h < GQA; ++h) {
             float q_cur[DPL];
-            load_row_gmem<DPL>(p.q_rope + (size_t)(kvh * GQA + h) * D + lane * DPL, q_cur);
+            load_row_gmem<DPL>(q_rope + (size_t)(kvh * GQA + h) * D + lane * DPL, q_cur);
             float d = 0.f;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) d = fmaf(q_cur[i], k_cur[i], d);
@@ -1096,7 +1158,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
                 const int head = kvh * GQA + h;
                 const float wgt = r.has_cur ? 1.f : 0.f;
                 if (p.skip_attn_reduction) {
-                    __nv_bfloat16* dst = p.attn_out + (size_t)head * D + lane * DPL;
+                    __nv_bfloat16* dst = attn_out + (size_t)head * D + lane * DPL;
                     if constexpr (DPL == 4) {
                         uint2 v;
                         v.x = pack_bf16x2(v_cur[0] * wgt, v_cur[1] * wgt);
@@ -1106,11 +1168,11 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
                         *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(v_cur[0] * wgt, v_cur[1] * wgt);
                     }
                 } else {
-                    float* dst = p.attn_o + ((size_t)head * p.max_partials + pi) * D + lane * DPL;
+                    float* dst = attn_o + ((size_t)head * p.max_partials + pi) * D + lane * DPL;
 #pragma unroll
                     for (int i = 0; i < DPL; ++i) dst[i] = v_cur[i] * wgt;
                     if (lane == 0)
-                        p.attn_lse[(size_t)head * p.max_partials + pi] = r.has_cur ? s_cur[h] : -INFINITY;
+                        attn_lse[(size_t)head * p.max_partials + pi] = r.has_cur ? s_cur[h] : -INFINITY;
                 }
             }
             __syncwarp();
@@ -1119,7 +1181,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
                     red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);
             } else {
                 if (lane < GQA)
-                    red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, kvh * GQA + lane), 1);
+                    red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, part_slot0 + kvh * GQA + lane), 1);
             }
         }
         return true;
@@ -1172,11 +1234,11 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         if (p.skip_attn_reduction) {
             const float hi = __shfl_down_sync(0xffffffffu, val, 1);
             if ((d & 1) == 0 && !cs.dead)
-                *reinterpret_cast<uint32_t*>(p.attn_out + (size_t)head * D + d) = pack_bf16x2(val, hi);
+                *reinterpret_cast<uint32_t*>(attn_out + (size_t)head * D + d) = pack_bf16x2(val, hi);
         } else if (!cs.dead) {
-            p.attn_o[((size_t)head * p.max_partials + pi) * D + d] = val;
+            attn_o[((size_t)head * p.max_partials + pi) * D + d] = val;
             if (d == 0)
-                p.attn_lse[(size_t)head * p.max_partials + pi] = den > 0.f ? mx + log2f(den) : -INFINITY;
+                attn_lse[(size_t)head * p.max_partials + pi] = den > 0.f ? mx + log2f(den) : -INFINITY;
         }
     }
     consumer_sync();  // scratch reads and global stores of all threads are done
@@ -1187,7 +1249,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
                 red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);
         } else {
             if (lane < GQA)
-                red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, kvh * GQA + lane), 1);
+                red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, part_slot0 + kvh * GQA + lane), 1);
         }
     }
     return true;
@@ -1203,11 +1265,17 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
     const int layer = __ldg(w + 1), h0 = __ldg(w + 2), num_partials = __ldg(w + 3);
     const int is_terminal = __ldg(w + 4), n = __ldg(w + 5);
     const int out_idx = __ldg(w + 6 + n);
+    // batched build: the sequence's own intermediates, output rows and barrier slots
+    const int seq = kBatch == 1 ? 0 : __ldg(w + 7 + n);
+    float* attn_o = p.attn_o + (size_t)seq * p.Hq * p.max_partials * D;
+    float* attn_lse = p.attn_lse + (size_t)seq * p.Hq * p.max_partials;
+    __nv_bfloat16* attn_out = p.attn_out + (size_t)seq * p.o_in;
+    const int part_slot0 = seq * p.Hq;
     volatile int* verdict = verdict_word(c, cs);
     if (warp == 0) {
         const int row = MKB_OP_PARTIAL_ATTENTION - 1;
         bool ok = __shfl_sync(0xffffffffu, *c.cta_abort, 0) == 0;  // uniform over the warp
-        ok = ok && warp_wait_counters(c, lane < 4 ? bar_addr(p, layer, row, h0 + lane) : nullptr,
+        ok = ok && warp_wait_counters(c, lane < 4 ? bar_addr(p, layer, row, part_slot0 + h0 + lane) : nullptr,
                                       num_partials, layer, row, h0 + lane);
         if (lane == 0) {
             rec(c, MKB_T_CONSUMER_WAIT_DONE);
@@ -1224,10 +1292,10 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
         float lse = -INFINITY;
         if (lane < n) {
             idx = __ldg(w + 6 + lane);
-            lse = ld_cg_f32(p.attn_lse + (size_t)head * p.max_partials + idx);
+            lse = ld_cg_f32(attn_lse + (size_t)head * p.max_partials + idx);
         }
         constexpr int NB = 12;
-        const float* base = p.attn_o + (size_t)head * p.max_partials * D + dim;
+        const float* base = attn_o + (size_t)head * p.max_partials * D + dim;
         float acc = 0.f, mx = 0.f, wgt = 0.f, denom = 0.f;
         for (int j0 = 0; j0 < n; j0 += NB) {
             float part[NB];
@@ -1258,11 +1326,11 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
         if (is_terminal) {
             const float hi = __shfl_down_sync(0xffffffffu, val, 1);
             if ((dim & 1) == 0)
-                *reinterpret_cast<uint32_t*>(p.attn_out + (size_t)head * D + dim) = pack_bf16x2(val, hi);
+                *reinterpret_cast<uint32_t*>(attn_out + (size_t)head * D + dim) = pack_bf16x2(val, hi);
         } else {
-            p.attn_o[((size_t)head * p.max_partials + out_idx) * D + dim] = val;
+            attn_o[((size_t)head * p.max_partials + out_idx) * D + dim] = val;
             if (dim == 0)
-                p.attn_lse[(size_t)head * p.max_partials + out_idx] =
+                attn_lse[(size_t)head * p.max_partials + out_idx] =
                     denom > 0.f ? mx + log2f(denom) : -INFINITY;
         }
     }
@@ -1271,7 +1339,7 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
         if (is_terminal) {
             if (lane == 0) red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), 4);
         } else if (lane < 4) {
-            red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, h0 + lane), 1);
+            red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, part_slot0 + h0 + lane), 1);
         }
     }
     return true;
@@ -1391,7 +1459,8 @@ __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const i
         case MKB_OP_RMS_QKV_ROPE_APPEND: {
             const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
             return consumer_rms_matvec<kTP>(c, cs, p.attn_ln_w + (size_t)layer * p.H, eb - sb, layer - 1,
-                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, layer > 0);
+                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, layer > 0,
+                                       nullptr, layer, 0);
         }
         case MKB_OP_RMS_UPGATE_SILU: {
             const int layer = __ldg(w + 1), n = __ldg(w + 2);
@@ -1399,29 +1468,52 @@ __device__ bool consumer_rms_op(const Ctx& c, ConsumerState& cs, int op, const i
             // for one arrival per up/gate instruction on row MKB_BARRIER_ROW_RMS_READ
             return consumer_rms_matvec<kTP>(c, cs, p.mlp_ln_w + (size_t)layer * p.H, 2 * n, layer,
                                        MKB_OP_O_PROJ_RESIDUAL - 1, p.thr_upgate_waits_oproj, true,
-                                       bar_addr(p, layer, MKB_BARRIER_ROW_RMS_READ, 0));
+                                       bar_addr(p, layer, MKB_BARRIER_ROW_RMS_READ, 0), layer, 1);
         }
         default: {  // MKB_OP_RMS_LM_HEAD
             const int sb = __ldg(w + 1), eb = __ldg(w + 2);
             return consumer_rms_matvec<kTP>(c, cs, p.lm_norm_w, eb - sb, p.L - 1,
-                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true);
+                                       MKB_OP_DOWN_PROJ_RESIDUAL - 1, p.thr_qkv_waits_down, true,
+                                       nullptr, p.L - 1, 2);
         }
     }
+}
+
+// RMS_NORM (batched build): normalise one sequence's residual stream once, for all SMs.
+// words: [9, layer, which (0 attention norm, 1 MLP norm, 2 final norm), sequence]
+__device__ bool consumer_rms_norm(const Ctx& c, ConsumerState& cs, const int* w) {
+    const KParams& p = *c.p;
+    const int layer = __ldg(w + 1), which = __ldg(w + 2), seq = __ldg(w + 3);
+    const __nv_bfloat16* norm_w = which == 0 ? p.attn_ln_w + (size_t)layer * p.H
+                                  : which == 1 ? p.mlp_ln_w + (size_t)layer * p.H
+                                               : p.lm_norm_w;
+    RmsPrefetch pf;
+    rms_prefetch(c, norm_w, pf);
+    const bool needed = !(which == 0 && layer == 0);
+    const int wait_layer = which == 0 ? layer - 1 : layer;
+    const int wait_row = (which == 1 ? MKB_OP_O_PROJ_RESIDUAL : MKB_OP_DOWN_PROJ_RESIDUAL) - 1;
+    const int thr = which == 1 ? p.thr_upgate_waits_oproj : p.thr_qkv_waits_down;
+    if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, thr, needed)) return false;
+    rms_activation_plain(c, pf, nullptr, seq);
+    consumer_sync();  // every thread's part of the vector is written
+    if (threadIdx.x == 0) red_release_gpu_add(bar_addr(p, layer, MKB_BARRIER_ROW_RMS_NORM, which), 1);
+    return true;
 }
 
 __device__ bool consumer_residual_op(const Ctx& c, ConsumerState& cs, int op, const int* w) {
     const KParams& p = *c.p;
     const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3), rb = __ldg(w + 4);
-    if (op == MKB_OP_O_PROJ_RESIDUAL)
+    if (op == MKB_OP_O_PROJ_RESIDUAL)  // every sequence's attention must be complete
         return consumer_plain_matvec(c, cs, p.attn_out + (size_t)rb * p.R, eb - sb, layer,
-                                     MKB_OP_ATTENTION_REDUCTION - 1, 0, p.thr_oproj_waits_attn);
+                                     MKB_OP_ATTENTION_REDUCTION - 1, 0, p.thr_oproj_waits_attn * p.batch,
+                                     nullptr, 0, (size_t)p.o_in);
     // with tensor parallelism inside the kernel the outputs go to a partial-sum buffer nobody
     // else is reading, so only the single-GPU residual needs the read-before-add ordering
     const bool order = p.thr_down_waits_rms > 0 && p.tp_size <= 1;
     return consumer_plain_matvec(c, cs, p.silu_out + (size_t)rb * p.R, eb - sb, layer,
                                  MKB_OP_RMS_UPGATE_SILU - 1, rb, p.thr_down_waits_upgate,
                                  order ? bar_addr(p, layer, MKB_BARRIER_ROW_RMS_READ, 0) : nullptr,
-                                 p.thr_down_waits_rms);
+                                 p.thr_down_waits_rms, (size_t)p.I);
 }
 
 template <bool kTP>
@@ -1459,6 +1551,15 @@ __device__ void consumer_main(Ctx c) {
                 if (p.D == 64) ok = consumer_attn_reduction<64>(c, cs, w);
                 else ok = consumer_attn_reduction<128>(c, cs, w);
                 break;
+            case MKB_OP_RMS_NORM:
+                if constexpr (kBatch > 1) {
+                    ok = consumer_rms_norm(c, cs, w);
+                    break;
+                } else {
+                    if (threadIdx.x == 0) report_error(c, MKB_ERR_BAD_OPCODE, op, 0, 0, 0);
+                    ok = false;
+                    break;
+                }
             case MKB_OP_TP_ALL_REDUCE:
                 if (kTP && p.tp_size > 1) {
                     ok = consumer_tp_all_reduce(c, cs, w);
@@ -1578,6 +1679,207 @@ __device__ __forceinline__ void storer_signal(StorerState& ss, int lane, int* ad
     ss.n_entries++;
 }
 
+#if MKB_BATCH > 1
+// ---- batched build: every block carries 16 rows x up to 8 sequences -------------------- //
+// Lane = row + 16 * half; the lane owns sequences 4 * half .. 4 * half + 3 of its row.
+constexpr int kSeqPerLane = kBatch / 2;
+__device__ __forceinline__ void storer_take_block_batched(const Ctx& c, StorerState& ss, int lane,
+                                                          float (&v)[kSeqPerLane]) {
+    const int oslot = ss.oslot;
+    const uint32_t obar = c.out_full_bar(oslot);
+    if (!ss.dead && !mbar_try_wait(obar, ss.ophase)) {
+        if (!mbar_wait_slow(c, obar, ss.ophase, true)) ss.dead = true;
+    }
+    const int row = lane & 15, half = lane >> 4;
+#pragma unroll
+    for (int j = 0; j < kSeqPerLane; ++j) {
+        const uint32_t src = c.base + kSmemOut + (oslot * kOutSlotFloats + (row * kBatch + half * kSeqPerLane + j) * 16) * 4;
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // the 16 per-warp partials of this (row, sequence)
+            const uint4 q = lds_v4(src + k * 16);
+            acc += (__uint_as_float(q.x) + __uint_as_float(q.y)) + (__uint_as_float(q.z) + __uint_as_float(q.w));
+        }
+        v[j] = acc;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(c.out_empty_bar(oslot));
+    if (++ss.oslot == kOutSlots) {
+        ss.oslot = 0;
+        ss.ophase ^= 1u;
+    }
+}
+
+struct BatchedArgmax {
+    float val[kSeqPerLane];
+    int idx[kSeqPerLane];
+};
+
+// Per-sequence version of storer_finish_argmax: scratch = [arrivals, pad, {value, index} x CTA x sequence]
+__device__ __noinline__ void storer_finish_argmax_batched(const Ctx& c, BatchedArgmax& best, int lane) {
+    const KParams& p = *c.p;
+    const int half = lane >> 4;
+    int* slots = p.argmax_scratch + 2;
+#pragma unroll
+    for (int j = 0; j < kSeqPerLane; ++j) {
+        float v = best.val[j];
+        int i = best.idx[j];
+#pragma unroll
+        for (int o = 8; o >= 1; o >>= 1)  // within the 16 lanes that own this sequence
+            argmax_merge(v, i, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, i, o));
+        if ((lane & 15) == 0) {
+            const int s = half * kSeqPerLane + j;
+            slots[2 * (s * gridDim.x + blockIdx.x)] = __float_as_int(v);
+            slots[2 * (s * gridDim.x + blockIdx.x) + 1] = i;
+        }
+    }
+    __syncwarp();
+    int old = 0;
+    if (lane == 0) {
+        __threadfence();
+        old = atomicAdd(p.argmax_scratch, 1);
+    }
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old != (int)gridDim.x - 1) return;
+    __threadfence();
+    for (int s = 0; s < p.batch; ++s) {
+        float v = -INFINITY;
+        int i = 0x7fffffff;
+        for (int k = lane; k < (int)gridDim.x; k += 32)
+            argmax_merge(v, i, __int_as_float((int)ld_cg_u32(slots + 2 * (s * gridDim.x + k))),
+                         (int)ld_cg_u32(slots + 2 * (s * gridDim.x + k) + 1));
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1)
+            argmax_merge(v, i, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, i, o));
+        if (lane == 0) p.argmax_out[s] = i;
+    }
+    if (lane == 0) *p.argmax_scratch = 0;
+}
+
+template <bool kTP>
+__device__ void storer_main(Ctx c) {
+    const KParams& p = *c.p;
+    StorerState ss;
+    BatchedArgmax best;
+    const int lane = threadIdx.x & 31;
+    const int row = lane & 15, half = lane >> 4;
+    const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
+    c.role = kRoleStorer;
+#pragma unroll
+    for (int j = 0; j < kSeqPerLane; ++j) {
+        best.val[j] = -INFINITY;
+        best.idx[j] = 0x7fffffff;
+    }
+    // RoPE rows at every sequence's position: [sequence][cos 128 | sin 128]
+    float* rope = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemRope));
+    for (int s = 0; s < p.batch; ++s)
+        for (int d = lane; d < p.D; d += 32) {
+            rope[s * 256 + d] = __ldg(p.rope_cos + (size_t)c.pos_of(s) * p.D + d);
+            rope[s * 256 + 128 + d] = __ldg(p.rope_sin + (size_t)c.pos_of(s) * p.D + d);
+        }
+    __syncwarp();
+    const int k_start = p.Hq * p.D, v_start = (p.Hq + p.Hkv) * p.D;
+    const bool even = (row & 1) == 0;
+
+    for (int i = 0; i < p.queue_len; ++i) {
+        const int* w = queue + i * MKB_INTS_PER_INSTRUCTION;
+        const int op = __ldg(w);
+        c.instr = i;
+        c.opcode = op;
+        const int stop = (*c.cta_abort != 0) || ss.dead;
+        if (__any_sync(0xffffffffu, stop)) break;
+        if (lane == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_STORER_START);
+        float v[kSeqPerLane];
+        switch (op) {
+            case MKB_OP_RMS_QKV_ROPE_APPEND: {
+                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
+                for (int b = sb; b < eb; ++b) {
+                    storer_take_block_batched(c, ss, lane, v);
+                    const int start = b * kBlockRows;
+                    const int seg = start % p.D;
+#pragma unroll
+                    for (int j = 0; j < kSeqPerLane; ++j) {
+                        const int s = half * kSeqPerLane + j;
+                        float x = bf16_round(v[j]);
+                        if (start < v_start) {
+                            const float cs_ = rope[s * 256 + seg + row];
+                            const float sn = rope[s * 256 + 128 + seg + row];
+                            const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+                            x = x * cs_ + ((row & 1) ? other : -other) * sn;
+                        }
+                        const float hi = __shfl_down_sync(0xffffffffu, x, 1);
+                        __nv_bfloat16* dst;
+                        if (start < k_start) {
+                            dst = p.q_rope + (size_t)s * p.o_in + start;
+                        } else {
+                            const size_t tok = (((size_t)layer * p.B + s) * p.T + c.pos_of(s)) * p.Hkv * p.D;
+                            dst = (start < v_start) ? p.k_cache + tok + (start - k_start)
+                                                    : p.v_cache + tok + (start - v_start);
+                        }
+                        if (even && s < p.batch) *reinterpret_cast<uint32_t*>(dst + row) = pack_bf16x2(x, hi);
+                    }
+                    storer_signal(ss, lane, bar_addr(p, layer, op - 1, start / p.D), 1);
+                }
+                storer_flush(ss, lane);
+            } break;
+            case MKB_OP_O_PROJ_RESIDUAL:
+            case MKB_OP_DOWN_PROJ_RESIDUAL: {
+                const int layer = __ldg(w + 1), sb = __ldg(w + 2), eb = __ldg(w + 3);
+                for (int b = sb; b < eb; ++b) {
+                    storer_take_block_batched(c, ss, lane, v);
+#pragma unroll
+                    for (int j = 0; j < kSeqPerLane; ++j) {
+                        const int s = half * kSeqPerLane + j;
+                        if (s < p.batch)
+                            red_add_u64(p.residual_acc + (size_t)s * p.H + b * kBlockRows + row,
+                                        (unsigned long long)(__float2ll_rn(v[j] * kResidualScale) * p.residual_mult));
+                    }
+                }
+                storer_signal(ss, lane, bar_addr(p, layer, op - 1, 0), eb - sb);
+                storer_flush(ss, lane);
+            } break;
+            case MKB_OP_RMS_UPGATE_SILU: {
+                const int layer = __ldg(w + 1), n = __ldg(w + 2);
+                for (int jb = 0; jb < n; ++jb) {
+                    const int b = __ldg(w + 3 + jb);
+                    float g[kSeqPerLane];
+                    storer_take_block_batched(c, ss, lane, v);
+                    storer_take_block_batched(c, ss, lane, g);
+#pragma unroll
+                    for (int j = 0; j < kSeqPerLane; ++j) {
+                        const int s = half * kSeqPerLane + j;
+                        const float up = bf16_round(v[j]), gate = bf16_round(g[j]);
+                        const float x = bf16_round(gate / (1.f + __expf(-gate))) * up;
+                        const float hi = __shfl_down_sync(0xffffffffu, x, 1);
+                        if (even && s < p.batch)
+                            *reinterpret_cast<uint32_t*>(p.silu_out + (size_t)s * p.I + b * kBlockRows + row) = pack_bf16x2(x, hi);
+                    }
+                    storer_signal(ss, lane, bar_addr(p, layer, op - 1, b * kBlockRows / p.R), 1);
+                }
+                storer_flush(ss, lane);
+            } break;
+            case MKB_OP_RMS_LM_HEAD: {
+                const int sb = __ldg(w + 1), eb = __ldg(w + 2);
+                for (int b = sb; b < eb; ++b) {
+                    storer_take_block_batched(c, ss, lane, v);
+#pragma unroll
+                    for (int j = 0; j < kSeqPerLane; ++j) {
+                        const int s = half * kSeqPerLane + j;
+                        const float hi = __shfl_down_sync(0xffffffffu, v[j], 1);
+                        if (even && s < p.batch)
+                            *reinterpret_cast<uint32_t*>(p.logits + (size_t)s * p.V + b * kBlockRows + row) = pack_bf16x2(v[j], hi);
+                        argmax_merge(best.val[j], best.idx[j], bf16_round(v[j]), b * kBlockRows + row);
+                    }
+                }
+            } break;
+            default:
+                break;
+        }
+        if (lane == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_STORER_DONE);
+    }
+    if (p.argmax_out != nullptr) storer_finish_argmax_batched(c, best, lane);
+}
+#else
 template <bool kTP>
 __device__ void storer_main(Ctx c) {
     const KParams& p = *c.p;
@@ -1692,6 +1994,7 @@ __device__ void storer_main(Ctx c) {
     }
     if (p.argmax_out != nullptr) storer_finish_argmax(c, ss, lane);
 }
+#endif  // MKB_BATCH
 
 // --------------------------------------------------------------------------- //
 // kernel
@@ -1710,7 +2013,8 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
     c.instr = -1;
     c.opcode = -1;
     c.role = -1;
-    c.pos = p.pos_id_ptr ? __ldg(p.pos_id_ptr) : p.pos_id;
+    if constexpr (kBatch == 1) c.pos = p.pos_id_ptr ? __ldg(p.pos_id_ptr) : p.pos_id;
+    else c.pos = p.pos_id_ptr ? __ldg(p.pos_id_ptr) : p.pos_ids[0];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kNumStages; ++s) {
@@ -1722,13 +2026,26 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
             mbar_init(c.out_empty_bar(s), 1);
         }
         for (int k = 0; k < 8; ++k) c.cta_abort[k] = 0;
+        if constexpr (kBatch > 1)
+            for (int s = 0; s < kBatch; ++s)
+                c.cta_abort[8 + s] = s < p.batch ? (p.pos_id_ptr ? __ldg(p.pos_id_ptr + s) : p.pos_ids[s]) : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    if (c.pos < 0 || c.pos >= p.T) {  // uniform over the grid: every thread read the same word
-        if (threadIdx.x == 0) report_error(c, MKB_ERR_INVALID_ARGUMENT, c.pos, p.T, 0, 0);
-        return;
+    if constexpr (kBatch == 1) {
+        if (c.pos < 0 || c.pos >= p.T) {  // uniform over the grid: every thread read the same word
+            if (threadIdx.x == 0) report_error(c, MKB_ERR_INVALID_ARGUMENT, c.pos, p.T, 0, 0);
+            return;
+        }
+    } else {
+        for (int s = 0; s < p.batch; ++s) {
+            const int ps = c.pos_of(s);
+            if (ps < 0 || ps >= p.T) {  // uniform over the grid as well
+                if (threadIdx.x == 0) report_error(c, MKB_ERR_INVALID_ARGUMENT, ps, p.T, s, 0);
+                return;
+            }
+        }
     }
 
     const int warp = threadIdx.x >> 5;
@@ -1755,6 +2072,7 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
     }
 }
 
+#if MKB_BATCH == 1
 // Two kernels from one body: the single-GPU one, and the one that can exchange partial sums
 // with peer GPUs (MkbTensorParallel), launched when tp.size > 1.
 __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_constant__ KParams p) {
@@ -1763,5 +2081,11 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
 __global__ void __launch_bounds__(kBlockThreads, 1) megakernel_tp(const __grid_constant__ KParams p) {
     megakernel_body<true>(p);
 }
+#else
+// The batched build: up to kBatch sequences per launch (MkbGlobals.batch > 1).
+__global__ void __launch_bounds__(kBlockThreads, 1) megakernel_batched(const __grid_constant__ KParams p) {
+    megakernel_body<false>(p);
+}
+#endif
 
-}  // namespace mkb
+}  // namespace MKB_NAMESPACE

@@ -21,9 +21,23 @@
 
 #include "../../include/mkb200.h"
 
-namespace mkb {
+// The kernel source is compiled twice.  MKB_BATCH == 1 (default): one sequence per launch, the
+// latency-optimised build.  MKB_BATCH == 8: up to 8 independent sequences per launch (the
+// activation vectors of all sequences are the 8 columns of the MMA's B operand, so the weights
+// are still streamed once); it trades two ring stages for room to park 8 activation vectors.
+#ifndef MKB_BATCH
+#define MKB_BATCH 1
+#endif
+#if MKB_BATCH == 1
+#define MKB_NAMESPACE mkb
+#else
+#define MKB_NAMESPACE mkb_batched
+#endif
+
+namespace MKB_NAMESPACE {
 
 // ---- geometry ------------------------------------------------------------ //
+constexpr int kBatch = MKB_BATCH;
 constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;  // 512
 constexpr int kLoaderWarp = kConsumerWarps;            // warp 16
@@ -31,26 +45,35 @@ constexpr int kStorerWarp = kConsumerWarps + 1;        // warp 17
 constexpr int kBlockThreads = (kConsumerWarps + 2) * 32;  // 576
 
 constexpr int kStageBytes = 32768;  // one ring stage
-constexpr int kNumStages = 6;       // 192 KiB of weights / KV in flight per SM
-constexpr int kOutSlots = 4;        // ring of per-block partial sums, consumer -> storer
-constexpr int kOutSlotFloats = 16 * 16;  // [row][partial]
+constexpr int kNumStages = kBatch == 1 ? 6 : 4;  // 192 (128) KiB of weights / KV in flight per SM
+constexpr int kOutSlots = kBatch == 1 ? 4 : 2;   // ring of per-block partial sums, consumer -> storer
+constexpr int kOutSlotFloats = 16 * 16 * kBatch; // [row][sequence][partial]
 constexpr int kBlockRows = 16;      // output rows per matvec block
+// Parked activation vectors: one per sequence, kActStride bytes apart.  The stride is 64 mod
+// 128 so that the 8 lanes of a quarter warp (two sequences x four chunks) hit 8 different
+// 16-byte bank groups when they load their B-operand fragments.
+constexpr int kActBytes = kBatch == 1 ? 16384 : 8192;  // longest vector: H (or R) bf16 elements
+constexpr int kActStride = kBatch == 1 ? 0 : kActBytes + 64;
 
 // attention: cross-warp merge scratch, 8 slots x 4 heads x (D + m + l)
 constexpr int kAttnHeadsPerPass = 4;
 constexpr int kAttnSlotFloats = kAttnHeadsPerPass * (128 + 4);
 constexpr int kAttnScratchFloats = 8 * kAttnSlotFloats;
+constexpr int kActAreaBytes = kBatch == 1 ? kAttnScratchFloats * 4 : kBatch * kActStride;
+static_assert(kActAreaBytes >= kAttnScratchFloats * 4 && kActAreaBytes >= kActBytes, "");
 
 // shared-memory map (byte offsets from the 1024-aligned base)
 constexpr int kSmemRing = 0;
 constexpr int kSmemOut = kSmemRing + kNumStages * kStageBytes;
-constexpr int kSmemAttn = kSmemOut + kOutSlots * kOutSlotFloats * 4;
-constexpr int kSmemRed = kSmemAttn + kAttnScratchFloats * 4;  // 32 floats
-constexpr int kSmemRope = kSmemRed + 32 * 4;                   // cos[D], sin[D] of this token's position
-constexpr int kSmemBars = kSmemRope + 2 * 128 * 4;             // mbarriers, 8 B each
+constexpr int kSmemAttn = kSmemOut + kOutSlots * kOutSlotFloats * 4;  // activations / attention scratch
+constexpr int kSmemRed = kSmemAttn + kActAreaBytes;            // 32 floats
+constexpr int kSmemRope = kSmemRed + 32 * 4;                   // cos[D], sin[D] at every sequence's position
+constexpr int kSmemBars = kSmemRope + kBatch * 2 * 128 * 4;    // mbarriers, 8 B each
 constexpr int kNumMbars = 2 * kNumStages + 2 * kOutSlots;
-constexpr int kSmemCtl = kSmemBars + kNumMbars * 8;            // 8 ints of control words
-constexpr int kSmemTotal = kSmemCtl + 8 * 4;
+constexpr int kSmemCtl = kSmemBars + kNumMbars * 8;            // control words, then the positions
+constexpr int kCtlWords = 8 + 8;
+constexpr int kSmemTotal = kSmemCtl + kCtlWords * 4;
+static_assert(kSmemTotal + 1024 <= 227 * 1024, "shared memory budget of one CTA");
 constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack to align the base
 
 enum Role { kRoleLoader = 0, kRoleConsumer = 1, kRoleStorer = 2 };
@@ -84,7 +107,12 @@ struct KParams {
     int o_in;      // Hq * D
     // per token
     int pos_id;
-    const int* pos_id_ptr;   // when set, the position is read from device memory instead
+    const int* pos_id_ptr;   // when set, the position(s) are read from device memory instead
+    // batched build: sequences decoded by this launch, their positions when pos_id_ptr is not
+    // set, and the RMS-normalised activations [batch][H] that RMS_NORM instructions publish
+    int batch;
+    int pos_ids[8];
+    __nv_bfloat16* normed;
     float attn_scale_log2e;  // attn_scale * log2(e)
     float rms_eps;
     int skip_attn_reduction;
@@ -293,4 +321,4 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-}  // namespace mkb
+}  // namespace MKB_NAMESPACE

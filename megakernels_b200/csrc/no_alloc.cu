@@ -85,6 +85,8 @@ extern "C" int mkb_launch_no_alloc(const MkbGlobals* g, void* cuda_stream) {
 
     if (g->tp.size > 1)
         return set_error(MKB_ERR_UNSUPPORTED, "mkb_launch_no_alloc has no tensor-parallel variant");
+    if (g->batch > 1)
+        return set_error(MKB_ERR_UNSUPPORTED, "mkb_launch_no_alloc decodes one sequence per launch");
     if (g->num_attention_heads < 1 || g->max_partials < 1 || g->head_dim < 1)
         return set_error(MKB_ERR_INVALID_ARGUMENT,
                          "num_attention_heads, max_partials and head_dim must be positive");

@@ -15,7 +15,15 @@ Reference: megakernels/demos/latency/instructions.py.  Word layouts (after
  6    DownProjResidual                [6, layer, start_blk, end_blk, red_blk]
  7    RMS_LM_Head                     [7, start_blk, end_blk]
  8    TP_AllReduce                    [8, layer, which, chunk, num_chunks]
+ 9    RMS_Norm                        [9, layer, which, sequence]
 ====  ==============================  ==========================================
+
+Batched decode (``Globals.batch_size`` > 1, no counterpart in the reference's latency
+kernel): opcode 2 carries the sequence as a sixth word, opcode 3 as the word after
+``out_idx`` (both 0 for a single sequence, where the padded words equal the reference's),
+and opcode 9 normalises one sequence's residual stream for all SMs (``which`` 0: attention
+norm, 1: MLP norm, 2: final norm); opcodes 1, 5 and 7 then wait for one arrival per sequence
+in barrier row 9 instead of normalising themselves.
 
 Opcode 8 has no counterpart in the reference: it is one chunk of the in-kernel
 tensor-parallel all-reduce of the residual stream (``which`` 0: after the
@@ -118,6 +126,7 @@ class PartialAttention(Instruction):
     kv_head_idx: int
     num_partials: int
     partial_idx: int
+    batch_idx: int = 0
 
     @classmethod
     def opcode(cls) -> int:
@@ -142,6 +151,7 @@ class AttentionReduction(Instruction):
     is_terminal: bool
     reduction_list: list[int]
     output_partial_idx: Optional[int] = None
+    batch_idx: int = 0
 
     @classmethod
     def opcode(cls) -> int:
@@ -242,6 +252,22 @@ class TP_AllReduce(Instruction):
 
     def cost(self, globs: Globals):
         return globs.hidden_size // self.num_chunks * 64
+
+
+@dataclass
+class RMS_Norm(Instruction):
+    """Batched decode only: RMSNorm of one sequence's residual stream into ``normed_states``."""
+
+    layer_idx: int
+    which: int  # 0: attention norm of the layer, 1: its MLP norm, 2: the final norm
+    batch_idx: int
+
+    @classmethod
+    def opcode(cls) -> int:
+        return 9
+
+    def cost(self, globs: Globals):
+        return globs.hidden_size * 8
 
 
 @dataclass

@@ -57,6 +57,9 @@ def interpret_with_mk(globs: Globals, mk_func, stream=None, **kwargs):
         argmax_out=globs.argmax_out,
         residual_acc=globs.residual_acc,
         upgate_instructions_per_layer=globs.upgate_instructions_per_layer,
+        batch=globs.batch_size,
+        pos_ids=globs.pos_ids,
+        normed_states=globs.normed_states,
         **kwargs,
     )
 

@@ -33,6 +33,7 @@ from megakernels_b200.demos.latency.instructions import (
     O_ProjResidual,
     PartialAttention,
     RMS_LM_Head,
+    RMS_Norm,
     TP_AllReduce,
 )
 from megakernels_b200.instructions import NoOp, TensorParallelState
@@ -48,6 +49,9 @@ class LatencyScheduleOptions:
 
     num_attention_partitions: int = 1
     coalesce_o_proj: bool = False
+    # > 1: batched decode, that many independent sequences per launch (at most 8); the model's
+    # KV cache must hold them (ExtraModelConfig.max_batch_size)
+    batch_size: int = 1
     # > 0 on a tensor-parallel shard: all-reduce the residual stream inside the kernel,
     # split into this many chunks (a multiple of the TP degree); 0 leaves the exchange
     # to the host (generators.TP_MK_Generator cuts the stream and calls NCCL)
@@ -81,13 +85,22 @@ def pick_matvec_reduction_size(o_in_features: int, intermediate_size: int) -> in
     )
 
 
-def make_globals(model, skip_attn_reduction: bool = True, max_attn_partitions: int | None = None):
-    """Allocate activation buffers and barriers; gather weights (scheduler.py:38-115)."""
+def make_globals(
+    model, skip_attn_reduction: bool = True, max_attn_partitions: int | None = None, batch_size: int = 1
+):
+    """Allocate activation buffers and barriers; gather weights (scheduler.py:38-115).
+
+    ``batch_size`` > 1 gives every activation buffer a leading batch dimension.
+    """
     config = model.config
     device = model.device
     dtype = model.dtype
+    assert 1 <= batch_size <= 8 and batch_size <= model.extra_config.max_batch_size
 
     def make_buffer(shape, buffer_dtype=dtype):
+        shape = [shape] if isinstance(shape, int) else list(shape)
+        if batch_size > 1:
+            shape = [batch_size] + shape
         return torch.zeros(shape, device=device, dtype=buffer_dtype)
 
     sp = model.stacked_params
@@ -95,16 +108,18 @@ def make_globals(model, skip_attn_reduction: bool = True, max_attn_partitions: i
     n_kv = model.num_kv_heads()
     inter = model.local_intermediate_size()
     if max_attn_partitions is None:
-        max_attn_partitions = get_sm_count(device)
+        max_attn_partitions = get_sm_count(device) if batch_size == 1 else 24
 
     # barrier counters and residual accumulators share one buffer: one fill resets both
     # one slot per head as in the reference (latency/scheduler.py:59); small tensor-parallel
     # shards can have more down-proj input slices than heads, and every slice needs a slot
     reduction = pick_matvec_reduction_size(n_q * config.head_dim, inter)
-    bar_shape = [config.num_hidden_layers, 10, max(n_q + 2 * n_kv, inter // reduction)]
+    # (and a batched launch one slot per sequence and Q head in the partial-attention row)
+    width = max(n_q + 2 * n_kv, inter // reduction, batch_size * n_q if batch_size > 1 else 0)
+    bar_shape = [config.num_hidden_layers, 10, width]
     n_bar = math.prod(bar_shape)
     acc_off = (n_bar + 3) // 4 * 4  # int64 view needs 8-byte, the kernel's loads 16-byte alignment
-    vm_state = torch.zeros(acc_off + 2 * config.hidden_size, dtype=torch.int32, device=device)
+    vm_state = torch.zeros(acc_off + 2 * batch_size * config.hidden_size, dtype=torch.int32, device=device)
     barriers = vm_state[:n_bar].view(bar_shape)
 
     globs = Globals(
@@ -156,6 +171,11 @@ def make_globals(model, skip_attn_reduction: bool = True, max_attn_partitions: i
     )
     globs.vm_state = vm_state
     globs.residual_acc = vm_state[acc_off:].view(torch.int64)
+    if batch_size > 1:
+        globs.batch_size = batch_size
+        globs.residual_acc = globs.residual_acc.view(batch_size, config.hidden_size)
+        globs.normed_states = make_buffer(config.hidden_size)
+        globs.pos_ids = [0] * batch_size
     return globs
 
 
@@ -347,6 +367,50 @@ def make_dag_layer(
     return new_nodes, down_nodes
 
 
+def make_batched_dag(globs: Globals, options: LatencyScheduleOptions, layer_limit: int | None = None):
+    """One decode step of ``globs.batch_size`` independent sequences (no counterpart in the
+    reference).  The projections are the same instructions as for one sequence - a block is
+    multiplied with every sequence's activation vector while it is in shared memory - and
+    wait for ``RMS_Norm`` instructions instead of normalising; attention and its reduction are
+    emitted per sequence, each over that sequence's own length."""
+    B, n_part = globs.batch_size, options.num_attention_partitions
+    assert globs.tp is None, "batched decode has no tensor-parallel variant"
+    assert 1 <= n_part <= MAX_REDUCTION_LIST and n_part <= globs.attn_lse_intermediates.shape[-1]
+    assert globs.skip_attn_reduction == (n_part == 1)
+    nodes: list[DAG_Node] = []
+    nlayers = globs.num_hidden_layers if layer_limit is None else layer_limit
+    gqa = assert_div(globs.num_attention_heads, globs.num_kv_heads)
+    last: list[DAG_Node] = []
+
+    def emit(instructions, deps):
+        new = [DAG_Node(ins, deps) for ins in instructions]
+        nodes.extend(new)
+        return new
+
+    for layer in range(nlayers):
+        norm = emit([RMS_Norm(layer, 0, b) for b in range(B)], last)
+        qkv = emit(schedule_qkv(globs, layer), norm)
+        attn_out: list[DAG_Node] = []
+        for b in range(B):
+            for kv in range(globs.num_kv_heads):
+                parts = emit([PartialAttention(layer, kv, n_part, p, b) for p in range(n_part)], qkv)
+                if globs.skip_attn_reduction:
+                    attn_out.extend(parts)
+                    continue
+                for h0 in range(kv * gqa, (kv + 1) * gqa, globs.attn_reduction_size):
+                    attn_out.extend(
+                        emit([AttentionReduction(layer, h0, n_part, True, list(range(n_part)), None, b)], parts)
+                    )
+        o = emit(schedule_oproj(globs, layer, options.coalesce_o_proj), attn_out)
+        norm = emit([RMS_Norm(layer, 1, b) for b in range(B)], o)
+        up = emit(schedule_upgate(globs, layer), norm)
+        last = emit(schedule_downproj(globs, layer), up)
+    if nlayers == globs.num_hidden_layers:
+        norm = emit([RMS_Norm(nlayers - 1, 2, b) for b in range(B)], last)
+        last = emit(schedule_lm_head(globs), norm)
+    return nodes, DAG_Node(NoOp(), last)
+
+
 def make_dag(
     globs: Globals,
     stop_after_op: str | None = None,
@@ -354,6 +418,9 @@ def make_dag(
     options: LatencyScheduleOptions | None = None,
 ):
     """Reference: megakernels/demos/latency/scheduler.py:235-267."""
+    if globs.batch_size > 1:
+        assert stop_after_op is None, "the batched builder emits whole layers"
+        return make_batched_dag(globs, options or LatencyScheduleOptions(), layer_limit)
     nodes: list[DAG_Node] = []
     nlayers = globs.num_hidden_layers if layer_limit is None else layer_limit
     last_outputs: list[DAG_Node] = []
@@ -385,7 +452,8 @@ class LatencyScheduleBuilder(ScheduleBuilder):
 
         globs = self.make_globals(model)
         nodes, end = make_dag(globs, stop_after_op, layer_limit, self.options)
-        globs.upgate_instructions_per_layer = sum(
+        # (a batched launch orders the down-proj behind the norm through the up/gate itself)
+        globs.upgate_instructions_per_layer = 0 if globs.batch_size > 1 else sum(
             1
             for n in nodes
             if isinstance(n.instruction, LayerNormDoubleMatVecSiLU) and n.instruction.layer_idx == 0
@@ -394,7 +462,7 @@ class LatencyScheduleBuilder(ScheduleBuilder):
 
     def make_globals(self, model):  # type: ignore[override]
         skip = self.options.num_attention_partitions == 1
-        globs = make_globals(model, skip_attn_reduction=skip)
+        globs = make_globals(model, skip_attn_reduction=skip, batch_size=self.options.batch_size)
         extra = model.extra_config
         if self.options.tp_all_reduce_chunks and extra.tp_size > 1:
             globs.tp = TensorParallelState(extra.tp_size, extra.tp_rank, self.options.tp_all_reduce_chunks)

@@ -55,7 +55,13 @@ class Generator:
 
 
 class MK_Generator(Generator):
-    """Batch-1 greedy decoding, one megakernel launch per token."""
+    """Greedy decoding, one megakernel launch per token.
+
+    As in the reference one sequence (``generate``, ``prefill``).  With a schedule built
+    for ``LatencyScheduleOptions(batch_size=B)`` the same ``run`` advances B independent
+    sequences by one token per launch: ``input_ids`` is ``[B, 1]``, ``pos_id`` a list of B
+    positions (sequence b lives in slot b of the KV cache), the result ``[B]`` token ids.
+    """
 
     def __init__(
         self,
@@ -81,7 +87,9 @@ class MK_Generator(Generator):
         globs = schedule.globs
         has_head = globs.instructions is not None and bool((globs.instructions[:, :, 0] == 7).any())
         if fused_argmax and has_head and not skip_mk and globs.hidden_states.is_cuda:
-            globs.argmax_out = torch.zeros(1, dtype=torch.int32, device=globs.hidden_states.device)
+            globs.argmax_out = torch.zeros(
+                globs.batch_size, dtype=torch.int32, device=globs.hidden_states.device
+            )
 
     def fill(self):
         """Reset the per-token VM state: barrier counters and residual accumulators."""
@@ -108,9 +116,10 @@ class MK_Generator(Generator):
         """
         globs = self.schedule.globs
         device = globs.hidden_states.device
-        self._graph_tok = torch.zeros(1, 1, dtype=torch.long, device=device)
-        self._graph_out = torch.zeros(1, dtype=torch.long, device=device)
-        globs.pos_id_device = torch.full((1,), warmup_pos, dtype=torch.int32, device=device)
+        B = globs.batch_size
+        self._graph_tok = torch.zeros(B, 1, dtype=torch.long, device=device)
+        self._graph_out = torch.zeros(B, dtype=torch.long, device=device)
+        globs.pos_id_device = torch.full((B,), warmup_pos, dtype=torch.int32, device=device)
         globs.pos_id = warmup_pos
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
@@ -128,7 +137,7 @@ class MK_Generator(Generator):
         """The device work of one token; the position is already in the globals."""
         globs = self.schedule.globs
         post = self.model.model.embed_tokens(BatchState(input_ids=input_ids))
-        globs.hidden_states[:] = post.hidden_states.reshape(-1)
+        globs.hidden_states[:] = post.hidden_states.reshape(globs.hidden_states.shape)
         self.fill()
         self.last_call = self.interpreter.interpret(globs)
         return self._next_token()
@@ -139,22 +148,29 @@ class MK_Generator(Generator):
             return globs.argmax_out.to(torch.long)
         return torch.argmax(globs.logits, dim=-1)
 
-    def _replay(self, input_ids: Tensor, pos_id: int) -> Tensor:
-        self._graph_tok.copy_(input_ids.reshape(1, 1))
-        self.schedule.globs.pos_id_device.fill_(pos_id)
+    def _replay(self, input_ids: Tensor, pos_id) -> Tensor:
+        self._graph_tok.copy_(input_ids.reshape(self._graph_tok.shape))
+        if isinstance(pos_id, int):
+            self.schedule.globs.pos_id_device.fill_(pos_id)
+        else:  # one position per sequence
+            self.schedule.globs.pos_id_device.copy_(torch.as_tensor(pos_id, dtype=torch.int32), non_blocking=True)
         self._graph.replay()
         return self._graph_out
 
-    def run(self, input_ids: Tensor, pos_id: int):
+    def run(self, input_ids: Tensor, pos_id):
         if getattr(self, "_graph", None) is not None:
             return self._replay(input_ids, pos_id)
         globs = self.schedule.globs
         if not self.skip_rest:
             post = self.model.model.embed_tokens(BatchState(input_ids=input_ids))
             assert post.hidden_states is not None
-            globs.hidden_states[:] = post.hidden_states.reshape(-1)
+            globs.hidden_states[:] = post.hidden_states.reshape(globs.hidden_states.shape)
         self.fill()
-        globs.pos_id = pos_id
+        if globs.batch_size > 1:
+            globs.pos_ids = [int(p) for p in pos_id]
+            assert len(globs.pos_ids) == globs.batch_size
+        else:
+            globs.pos_id = pos_id
         if not self.skip_mk:
             self.last_call = self.interpreter.interpret(globs)
         if self.skip_rest:

@@ -108,6 +108,11 @@ class BaseGlobals:
         # RMS + up/gate instructions per layer of the schedule (0: unknown); the down-proj
         # waits for that many residual-stream reads before it adds to the accumulators
         self.upgate_instructions_per_layer: int = 0
+        # batched decode: sequences per launch, their positions (host list, or a device int32
+        # tensor in ``pos_id_device``), and the buffer RMS_Norm instructions write
+        self.batch_size: int = 1
+        self.pos_ids: list[int] | None = None
+        self.normed_states: Tensor | None = None
 
     def residual_stream(self) -> Tensor:
         """The residual stream after a launch as fp32 ``[H]``: embedding + accumulated outputs.
@@ -181,13 +186,18 @@ class Instruction:
 
         Ints (and bools) take one word, ``None`` becomes 0, tuples and lists
         are length-prefixed, and a field named ``global_idx`` is skipped
-        (reference: megakernels/instructions.py:97-119).
+        (reference: megakernels/instructions.py:97-119).  ``batch_idx`` (always the
+        last field, no counterpart in the reference) is only written when non-zero.
         """
         words = [self.opcode()]
         for f in fields(self):
             if f.name == "global_idx":
                 continue
             v = getattr(self, f.name)
+            if f.name == "batch_idx" and v == 0:
+                # trailing sequence index of a batched launch: absent for sequence 0, so that a
+                # single-sequence stream is word for word the reference's (the padding is zero)
+                continue
             if isinstance(v, int):
                 words.append(int(v))
             elif isinstance(v, (tuple, list)):

@@ -18,7 +18,7 @@ import torch
 _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libmkb200.so"
 
-MKB_ABI_VERSION = 3
+MKB_ABI_VERSION = 4
 MKB_MAX_TP = 8
 MKB_TP_MAX_CHUNKS = 32
 MKB_PEER_HANDLE_BYTES = 64
@@ -98,7 +98,9 @@ class MkbGlobals(ctypes.Structure):
         ("residual_scale", ctypes.c_float),
         ("residual_acc", ctypes.c_void_p),
         ("upgate_instructions_per_layer", ctypes.c_int32),
-        ("reserved0", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("pos_ids", ctypes.c_int32 * 8),
+        ("normed_states", ctypes.c_void_p),
         ("tp", MkbTensorParallel),
         ("argmax_out", ctypes.c_void_p),
         ("flags", ctypes.c_uint32),
@@ -229,6 +231,9 @@ def pack_globals(
     argmax_out=None,
     residual_acc=None,
     upgate_instructions_per_layer=0,
+    batch=1,
+    pos_ids=None,
+    normed_states=None,
 ) -> MkbGlobals:
     """Fill the C struct from tensors; every dimension is read off the shapes."""
     bf16, i32, f32 = torch.bfloat16, torch.int32, torch.float32
@@ -268,14 +273,12 @@ def pack_globals(
         g.attn_lse_intermediates = None
         g.attn_out_intermediates = None
     else:
-        g.attn_lse_intermediates = _check_tensor(
-            "attn_lse_intermediates", attn_lse_intermediates, f32, 2
-        )
-        g.attn_out_intermediates = _check_tensor(
-            "attn_out_intermediates", attn_out_intermediates, f32, 3
-        )
-        num_attention_heads = attn_lse_intermediates.shape[0]
-        max_partials = attn_lse_intermediates.shape[1]
+        g.attn_lse_intermediates = _check_tensor("attn_lse_intermediates", attn_lse_intermediates, f32)
+        g.attn_out_intermediates = _check_tensor("attn_out_intermediates", attn_out_intermediates, f32)
+        if attn_lse_intermediates.ndim not in (2, 3) or attn_out_intermediates.ndim != attn_lse_intermediates.ndim + 1:
+            raise ValueError("attention intermediates must be [(batch,) Hq, P] and [(batch,) Hq, P, D]")
+        num_attention_heads = attn_lse_intermediates.shape[-2]
+        max_partials = attn_lse_intermediates.shape[-1]
     g.silu_out = _check_tensor("silu_out", silu_out, bf16)
     g.logits = _check_tensor("logits", logits, bf16)
 
@@ -333,10 +336,33 @@ def pack_globals(
         g.tp.epoch_device = _check_tensor("tp.epoch_device", tp.epoch_device, i32)
     if argmax_out is not None:
         g.argmax_out = _check_tensor("argmax_out", argmax_out, i32)
+    batch = int(batch or 1)
     if residual_acc is not None:
-        g.residual_acc = _check_tensor("residual_acc", residual_acc, torch.int64, 1)
-        if residual_acc.numel() < H:
-            raise ValueError(f"residual_acc needs {H} int64 elements, got {residual_acc.numel()}")
+        g.residual_acc = _check_tensor("residual_acc", residual_acc, torch.int64)
+        if residual_acc.numel() < batch * H:
+            raise ValueError(f"residual_acc needs {batch * H} int64 elements, got {residual_acc.numel()}")
+    if batch > 1:
+        # batched decode: leading batch dimension on the activation tensors
+        for name, t, n in (
+            ("hidden_states", hidden_states, H), ("post_ln_rope_q", post_ln_rope_q, Hq * D),
+            ("attn_out", attn_out, Hq * D), ("silu_out", silu_out, g.intermediate_size),
+            ("logits", logits, g.vocab_size),
+        ):
+            if tuple(t.shape) != (batch, n):
+                raise ValueError(f"{name} must be [{batch}, {n}] for a batch of {batch}, got {tuple(t.shape)}")
+        g.batch = batch
+        g.normed_states = _check_tensor("normed_states", normed_states, bf16, 2)
+        if pos_id_device is None:
+            if pos_ids is None or len(pos_ids) != batch:
+                raise ValueError("a batched launch needs pos_ids (one position per sequence) or pos_id_device")
+            for s, pos in enumerate(pos_ids):
+                if not 0 <= int(pos) < min(T, rope_cos.shape[0]):
+                    raise ValueError(f"pos_ids[{s}] = {pos} outside the KV cache / rope tables")
+                g.pos_ids[s] = int(pos)
+        elif pos_id_device.numel() < batch:
+            raise ValueError("pos_id_device must hold one position per sequence")
+        if argmax_out is not None and argmax_out.numel() < batch:
+            raise ValueError("argmax_out must hold one token per sequence")
     g.upgate_instructions_per_layer = int(upgate_instructions_per_layer)
     g.flags = MKB_FLAG_RECORD_TIMINGS if record_timings else 0
     if record_timings and timings is None:
@@ -389,6 +415,9 @@ def mk_llama(
     argmax_out=None,
     residual_acc=None,
     upgate_instructions_per_layer=0,
+    batch=1,
+    pos_ids=None,
+    normed_states=None,
 ):
     """Enqueue one decode step; positional arguments as in the reference call.
 
@@ -421,6 +450,9 @@ def mk_llama(
         argmax_out=argmax_out,
         residual_acc=residual_acc,
         upgate_instructions_per_layer=upgate_instructions_per_layer,
+        batch=batch,
+        pos_ids=pos_ids,
+        normed_states=normed_states,
     )
     rc = lib.mkb_launch(ctypes.byref(g), ctypes.c_void_p(_stream_handle(stream)))
     if rc != 0:

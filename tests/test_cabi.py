@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in mkb200.h but not exported"
     lib.mkb_abi_version.restype = ctypes.c_int
-    assert lib.mkb_abi_version() == 3
+    assert lib.mkb_abi_version() == 4
     lib.mkb_smem_bytes.restype = ctypes.c_int
     assert 0 < lib.mkb_smem_bytes() <= 227 * 1024
 
@@ -44,7 +44,7 @@ def test_struct_layout_matches_between_header_and_shim():
     text = (ROOT / "include" / "mkb200.h").read_text()
     body = text[text.index("typedef struct MkbGlobals {") : text.index("} MkbGlobals;")]
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
-    names = re.findall(r"[\w\*]\s+\**(\w+);", body)
+    names = re.findall(r"[\w\*]\s+\**(\w+)(?:\[\w+\])?;", body)
     assert names == [f[0] for f in mk_llama.MkbGlobals._fields_]
     body = text[text.index("typedef struct MkbTensorParallel {") : text.index("} MkbTensorParallel;")]
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
