@@ -80,6 +80,9 @@ def parse_args():
                     help="tensor parallel: all-reduce inside the kernel over peer memory "
                          "(one launch per token) or NCCL between 2L+1 launches")
     ap.add_argument("--tp-chunks", type=int, default=0, help="chunks per in-kernel all-reduce (0 = H / 1024)")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="independent sequences decoded per launch (2..8: the batched kernel; each sequence "
+                         "gets a seeded random KV length in [256, 4096] unless --prefill is given)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -101,8 +104,21 @@ def is_tensor_parallel(args, world: int) -> bool:
     return world > 1 and WORKLOADS[args.workload]["tp"] and not args.replicas
 
 
+def sequence_lengths(args, prefill: int) -> list[int]:
+    """KV length of every sequence: the workload's prefill, or (batched, no --prefill) seeded
+    uniform lengths in [256, 4096]."""
+    if args.batch > 1 and not args.prefill:
+        return torch.randint(256, 4097, (args.batch,), generator=torch.Generator().manual_seed(4)).tolist()
+    return [prefill] * args.batch
+
+
 def workload_name(args, cfg, prefill: int, world: int) -> str:
     """The same string in both arms, so that their lines can be matched."""
+    if args.batch > 1:
+        lens = sequence_lengths(args, prefill)
+        return (f"{args.workload} batched decode, {args.batch} independent sequences per launch, "
+                f"{cfg.num_hidden_layers} layers, KV lengths {min(lens)}..{max(lens)} (mean {sum(lens) // len(lens)}), "
+                "teacher-forced")
     name = f"{args.workload} batch-1 decode, {cfg.num_hidden_layers} layers, KV prefill {prefill}, teacher-forced"
     if is_tensor_parallel(args, world):
         how = "in-kernel all-reduce over peer memory" if args.tp_exchange == "peer" else "NCCL all-reduce"
@@ -305,20 +321,25 @@ def build_engine(args, device, tp_size=1, tp_rank=0, group=None, layers=0, steps
 
     cfg, prefill = model_config(args, layers)
     steps = args.steps + args.warmup if steps is None else steps
-    total = prefill + steps + 8
+    lens = sequence_lengths(args, prefill)
+    total = max(lens) + steps + 8
     extra = ExtraModelConfig(
-        interleave_rope=True, max_len_override=total, tp_size=tp_size, tp_rank=tp_rank, tp_group=group
+        interleave_rope=True, max_len_override=total, tp_size=tp_size, tp_rank=tp_rank, tp_group=group,
+        max_batch_size=args.batch,
     )
     model = LlamaForCausalLM.from_random(cfg, extra, device=device, seed=0, draw_on="device")
-    fill_kv_prefix(model, prefill, cfg.num_key_value_heads, tp_size, tp_rank, device)
+    fill_kv_prefix(model, lens, cfg.num_key_value_heads, tp_size, tp_rank, device)
     n_part = args.attn_partitions or pick_num_attention_partitions(
-        prefill, steps, device, model.num_kv_heads(), min_chunk_size=128
+        max(lens), steps, device, model.num_kv_heads(), min_chunk_size=128
     )
+    if args.batch > 1:  # all sequences' partials of a layer should fit one wave of SMs
+        n_part = args.attn_partitions or max(1, min(n_part, 148 // (args.batch * model.num_kv_heads())))
     peer = tp_size > 1 and args.tp_exchange == "peer"
     options = LatencyScheduleOptions(
         num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj,
         # chunks of 1024 elements: one pair per consumer thread, a multiple of the TP degree
         tp_all_reduce_chunks=(args.tp_chunks or max(tp_size, cfg.hidden_size // 1024)) if peer else 0,
+        batch_size=args.batch,
     )
     schedule = make_schedule_builder("latency", options).build(model)
     schedule.globs.pos_id = prefill
@@ -339,16 +360,18 @@ def build_engine(args, device, tp_size=1, tp_rank=0, group=None, layers=0, steps
     return cfg, prefill, model, schedule, generator, info
 
 
-def fill_kv_prefix(model, prefill, total_kv_heads, tp_size, tp_rank, device):
-    """Seeded N(0,1) prefix.  Every rank draws the full cache (same seed, same values) and
-    keeps its own KV heads, so that the ranks together hold one sequence's cache."""
+def fill_kv_prefix(model, lens, total_kv_heads, tp_size, tp_rank, device):
+    """Seeded N(0,1) prefix of ``lens[b]`` positions for sequence b.  Every rank draws the full
+    cache (same seed, same values) and keeps its own KV heads, so that the ranks together hold
+    one sequence's cache."""
     gen = torch.Generator(device=device).manual_seed(2)
     per = total_kv_heads // tp_size
     for c in model.stacked_kv_cache:
         L, B, _, _, D = c.shape
         for layer in range(L):  # layer by layer: the full-width temporary stays small
-            full = torch.randn((B, prefill, total_kv_heads, D), generator=gen, device=device)
-            c[layer, :, :prefill] = full[:, :, tp_rank * per : (tp_rank + 1) * per].to(c.dtype)
+            for b, n in enumerate(lens):
+                full = torch.randn((n, total_kv_heads, D), generator=gen, device=device)
+                c[layer, b, :n] = full[:, tp_rank * per : (tp_rank + 1) * per].to(c.dtype)
 
 
 def check_parity(args, gen, schedule, model, cfg, prefill, token, pos, world, tp, rank, device):
@@ -416,6 +439,47 @@ def check_parity(args, gen, schedule, model, cfg, prefill, token, pos, world, tp
     return result, ref
 
 
+def check_parity_batched(gen, schedule, model, cfg, lens, tokens, step, device):
+    """Batched launch: every sequence's logits against its own single-sequence oracle run."""
+    from oracle.llama_ref import (
+        COSINE_TOL, MARGIN_TOL, MAX_REL_TOL, TorchReferenceModel, depth_aware_tolerance, parity_metrics,
+    )
+
+    globs = schedule.globs
+    torch.cuda.synchronize()
+    pos = [n + step for n in lens]
+    caches = [tuple(c[:, b : b + 1, : pos[b] + 2].cpu().clone() for c in model.stacked_kv_cache) for b in range(len(lens))]
+    out = gen.run(tokens.view(-1, 1).to(device), pos_id=pos)
+    gen.check()
+    logits = globs.logits.cpu()
+    ref = TorchReferenceModel(model, kv_len=8)
+    worst = {"max_rel": 0.0, "cosine": 1.0}
+    floor_worst = {"max_rel": 0.0, "cosine": 1.0}
+    ok = literal = True
+    for b in range(len(lens)):
+        ref.k_cache, ref.v_cache = caches[b]
+        exact = ref.decode_token_exact(int(tokens[b]), pos[b])
+        want = ref.decode_token(int(tokens[b]), pos[b])
+        m, floor = parity_metrics(logits[b], want), parity_metrics(want, exact)
+        rel_tol, cos_tol, _ = depth_aware_tolerance(want, exact)
+        argmax_ok = m["argmax_equal"] or m["top2_margin"] <= MARGIN_TOL
+        ok = ok and m["max_rel"] <= rel_tol and m["cosine"] >= cos_tol and argmax_ok
+        literal = literal and m["max_rel"] <= MAX_REL_TOL and m["cosine"] >= COSINE_TOL and argmax_ok
+        ok = ok and int(out[b]) == int(logits[b].float().argmax())
+        worst = {"max_rel": max(worst["max_rel"], m["max_rel"]), "cosine": min(worst["cosine"], m["cosine"])}
+        floor_worst = {"max_rel": max(floor_worst["max_rel"], floor["max_rel"]),
+                       "cosine": min(floor_worst["cosine"], floor["cosine"])}
+    return {
+        "checked": f"logits of all {len(lens)} sequences at the first timed step, each against its own "
+                   "single-sequence run of the CPU oracle",
+        "ok": bool(ok), "meets_stated_tolerance": bool(literal),
+        "max_rel": worst["max_rel"], "cosine": worst["cosine"], "oracle_vs_float32": floor_worst,
+        "tolerance": f"stated: max_rel <= {MAX_REL_TOL}, cosine >= {COSINE_TOL}; ok uses twice the bf16 oracle's own "
+                     "distance from the same step in float32 (never below the stated values); worst sequence shown",
+        "layers": cfg.num_hidden_layers,
+    }, ref
+
+
 def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -437,8 +501,10 @@ def run_ours(args):
     tp = is_tensor_parallel(args, world)
     if WORKLOADS[args.workload]["preset"] == "llama_3_1_70b" and world == 1 and not args.layers:
         raise SystemExit(f"{args.workload} does not fit one GPU at full depth: launch it on 2, 4 or 8 GPUs")
-    K, W = args.steps, args.warmup
-    ids = torch.randint(0, 128256, (W + K,), generator=torch.Generator().manual_seed(3))
+    K, W, B = args.steps, args.warmup, args.batch
+    if B > 1 and (world > 1 or WORKLOADS[args.workload]["preset"] == "llama_3_1_70b"):
+        raise SystemExit("--batch runs on one GPU (8B or 1B shape)")
+    ids = torch.randint(0, 128256, (W + K, B), generator=torch.Generator().manual_seed(3))
 
     # ---- parity at reduced depth first, for workloads whose oracle does not fit the host ---- #
     parity = None
@@ -448,7 +514,7 @@ def run_ours(args):
         cfg_s, prefill_s, model_s, sched_s, gen_s, _ = build_engine(
             args, device, tp_size=world if tp else 1, tp_rank=rank if tp else 0, layers=parity_layers, steps=8
         )
-        parity, _ = check_parity(args, gen_s, sched_s, model_s, cfg_s, prefill_s, int(ids[0]) % cfg_s.vocab_size,
+        parity, _ = check_parity(args, gen_s, sched_s, model_s, cfg_s, prefill_s, int(ids[0, 0]) % cfg_s.vocab_size,
                                  prefill_s, world, tp, rank, device)
         if hasattr(gen_s, "close"):
             gen_s.close()
@@ -462,27 +528,35 @@ def run_ours(args):
     gen_holder = [gen]
     log(f"engine ready: {info}")
     ids = ids % cfg.vocab_size
-    ids_dev = ids.to(device).view(-1, 1, 1)
+    ids_dev = ids.to(device).view(W + K, B, 1)
+    lens = sequence_lengths(args, prefill)
+
+    def pos_at(step):  # position(s) of the token(s) decoded at `step`
+        return prefill + step if B == 1 else [n + step for n in lens]
+
     # 2L+1 launches per token (NCCL exchange) are launch-bound without a graph
     use_graph = args.cuda_graph or (tp and args.tp_exchange == "nccl")
 
     # ---- warm-up ----------------------------------------------------------- #
     for i in range(min(W, 3)):
-        gen.run(ids_dev[i], pos_id=prefill + i)
+        gen.run(ids_dev[i], pos_id=pos_at(i))
     gen.check()
     log("eager warm-up done")
     if use_graph:
         gen.enable_cuda_graph(warmup_pos=prefill)
         log("graph captured")
     for i in range(W):
-        gen.run(ids_dev[i], pos_id=prefill + i)
+        gen.run(ids_dev[i], pos_id=pos_at(i))
     gen.check()
 
     # ---- parity of the first timed step, outside the timed region ---------- #
     ref = None
     if parity is None and not args.no_parity:
-        parity, ref = check_parity(args, gen, schedule, model, cfg, prefill, int(ids[W]), prefill + W,
-                                   world, tp, rank, device)
+        if B > 1:
+            parity, ref = check_parity_batched(gen, schedule, model, cfg, lens, ids[W], W, device)
+        else:
+            parity, ref = check_parity(args, gen, schedule, model, cfg, prefill, int(ids[W, 0]), prefill + W,
+                                       world, tp, rank, device)
         log(f"parity: {parity}")
 
     # ---- device-resident timing: exactly K steps between barriers -------- #
@@ -500,13 +574,16 @@ def run_ours(args):
     start.record()
     if use_graph:
         for i in range(K):
-            gen.run(ids_dev[W + i], pos_id=prefill + W + i)
+            gen.run(ids_dev[W + i], pos_id=pos_at(W + i))
     else:
         for i in range(K):
             # the body of MK_Generator.run, with events around the kernel launch
-            globs.hidden_states[:] = embed[ids_dev[W + i]].reshape(-1)
+            globs.hidden_states[:] = embed[ids_dev[W + i]].reshape(globs.hidden_states.shape)
             gen.fill()
-            globs.pos_id = prefill + W + i
+            if B > 1:
+                globs.pos_ids = pos_at(W + i)
+            else:
+                globs.pos_id = prefill + W + i
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             gen.last_call = interp.interpret(globs)
@@ -534,26 +611,26 @@ def run_ours(args):
     # ---- end to end: token id from pinned host memory, produced token back to host ---- #
     e2e = None
     if not args.no_e2e:
-        host_in = torch.empty(1, dtype=torch.long).pin_memory()
-        host_out = torch.empty(1, dtype=torch.long).pin_memory()
-        dev_in = torch.empty(1, 1, dtype=torch.long, device=device)
-        pos0 = prefill + W  # re-decode the same positions: same work per step
+        host_in = torch.empty(B, dtype=torch.long).pin_memory()
+        host_out = torch.empty(B, dtype=torch.long).pin_memory()
+        dev_in = torch.empty(B, 1, dtype=torch.long, device=device)
+        # re-decode the same positions: same work per step
         if not use_graph:
             # the public generator replays the whole step (embedding row, state reset, megakernel,
             # argmax) as one CUDA graph; the device-timed loop above stays eager so that each
             # megakernel launch can be bracketed by events
             gen.enable_cuda_graph(warmup_pos=prefill)
         for i in range(3):
-            host_in[0] = ids[W + i]
-            dev_in.copy_(host_in.view(1, 1), non_blocking=True)
-            host_out.copy_(gen.run(dev_in, pos_id=pos0 + i).view(-1), non_blocking=True)
+            host_in.copy_(ids[W + i])
+            dev_in.copy_(host_in.view(B, 1), non_blocking=True)
+            host_out.copy_(gen.run(dev_in, pos_id=pos_at(W + i)).view(-1), non_blocking=True)
             torch.cuda.synchronize()
         barrier()
         t0 = time.perf_counter()
         for i in range(K):
-            host_in[0] = ids[W + i]
-            dev_in.copy_(host_in.view(1, 1), non_blocking=True)
-            out = gen.run(dev_in, pos_id=pos0 + i)
+            host_in.copy_(ids[W + i])
+            dev_in.copy_(host_in.view(B, 1), non_blocking=True)
+            out = gen.run(dev_in, pos_id=pos_at(W + i))
             host_out.copy_(out.view(-1), non_blocking=True)
             torch.cuda.current_stream().synchronize()
             _ = int(host_out[0])
@@ -571,13 +648,15 @@ def run_ours(args):
 
     if rank == 0:
         peak, peak_kind = hbm_peak()
-        mid_len = prefill + W + K // 2
-        nbytes = algorithmic_bytes_per_token(cfg, mid_len, tp=world if tp else 1)
+        mid = W + K // 2
+        nbytes = algorithmic_bytes_per_token(cfg, lens[0] + mid, tp=world if tp else 1)
+        # a batched launch streams the weights once and every sequence's own KV prefix
+        nbytes["kv"] = sum(algorithmic_bytes_per_token(cfg, n + mid)["kv"] for n in lens) if B > 1 else nbytes["kv"]
         algo = sum(nbytes.values())
         achieved = algo / (kernel_ms * 1e-3) / 1e9
-        replicas = 1 if tp else world  # a tensor-parallel job decodes one sequence
+        replicas = B if B > 1 else (1 if tp else world)  # a tensor-parallel job decodes one sequence
         line = {
-            "metric": METRIC,
+            "metric": METRIC if B == 1 else "batched_decode_tokens_per_s",
             "value": replicas * K / (elapsed_ms * 1e-3),
             "unit": UNIT,
             "n_gpus": world,
@@ -621,8 +700,8 @@ def run_ours(args):
             line["e2e"] = {
                 "value": replicas * K / e2e,
                 "unit": UNIT,
-                "h2d_bytes_per_step": 8,
-                "d2h_bytes_per_step": 8,
+                "h2d_bytes_per_step": 8 * B,
+                "d2h_bytes_per_step": 8 * B,
                 "ms_per_step": e2e / K * 1e3,
             }
         if world == 1 and not args.no_cpu_baseline:
@@ -631,9 +710,9 @@ def run_ours(args):
             del model, schedule, gen
             gen_holder.clear()
             torch.cuda.empty_cache()
-            if ref.k_cache.shape[2] < prefill + 12:
+            if ref.k_cache.shape[2] < prefill + 12 or ref.k_cache.shape[1] != 1:
                 ref.k_cache = torch.zeros(
-                    (*ref.k_cache.shape[:2], prefill + 12, *ref.k_cache.shape[3:]), dtype=ref.k_cache.dtype)
+                    (ref.k_cache.shape[0], 1, prefill + 12, *ref.k_cache.shape[3:]), dtype=ref.k_cache.dtype)
                 ref.v_cache = torch.zeros_like(ref.k_cache)
                 seeded_kv_prefix(ref, prefill)
             base, _ = time_cpu_path(ref, cfg, prefill, tokens=8, budget_s=25.0)
