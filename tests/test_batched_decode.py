@@ -99,8 +99,12 @@ def test_batched_decode_matches_independent_sequences(shape, batch, parts):
         assert out.shape == (batch,)
         for b in range(batch):
             ref.k_cache, ref.v_cache = caches[b]
+            # 2e-2 / 0.999 as everywhere (the bounds never go below the stated values); with so
+            # many (sequence, step) samples some top-2 pairs are one bf16 step apart, and for
+            # those the float32 restatement says whether the oracle itself can tell them apart
+            exact = ref.decode_token_exact(int(ids[step, b]), pos[b])
             want = ref.decode_token(int(ids[step, b]), pos[b])
-            assert_logits_parity(g.logits[b], want, f"step {step}, sequence {b} at position {pos[b]}")
+            assert_logits_parity(g.logits[b], want, f"step {step}, sequence {b} at position {pos[b]}", exact=exact)
             assert int(out[b]) == int(torch.argmax(g.logits[b])), f"fused argmax, sequence {b}"
             # the appended K/V row, and nothing beyond it
             assert torch.equal(g.k_cache[:, b, pos[b] + 1 :].cpu(), ref.k_cache[:, 0, pos[b] + 1 :])
