@@ -469,6 +469,8 @@ __device__ void loader_main(Ctx c) {
                 ahead_more = ahead.next(p, queue, da);
                 if (ahead_more) {
                     ++ahead_stage;
+                    // weights only: K/V tiles in the look-ahead measured no gain (batched and
+                    // 64k-context runs alike), their stages are bound by the strided tile copy
                     if (da.map) prefetch_l2_tile4(da.map, 0, da.c1, da.c2, da.c3);
                 }
                 continue;
@@ -606,9 +608,13 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
                 out[8 * 16] = d[2];
             }
         } else {
-            // columns 2t, 2t + 1 of D are sequences 2t, 2t + 1: slot layout [row][sequence][warp]
+            // columns 2t, 2t + 1 of D are sequences 2t, 2t + 1: slot layout [row][sequence][16 partials].
+            // Every (row, sequence) group starts on a 64-byte boundary, so without a rotation all 32
+            // lanes of a store would hit one bank; the storer only sums a group's 16 floats, so the
+            // position inside the group is free: rotate it per lane (2-way instead of 32-way conflicts).
+            const int w_rot = (warp + ((g & 3) << 2) + t) & 15;
             float* out = reinterpret_cast<float*>(__cvta_shared_to_generic(
-                c.base + kSmemOut + (cs.oslot * kOutSlotFloats + (row0 * kBatch + 2 * t) * 16 + warp) * 4));
+                c.base + kSmemOut + (cs.oslot * kOutSlotFloats + (row0 * kBatch + 2 * t) * 16 + w_rot) * 4));
             out[0] = d[0];
             out[16] = d[1];
             out[8 * kBatch * 16] = d[2];

@@ -26,6 +26,7 @@ OP_NAMES = {
     6: "down_proj_residual",
     7: "lm_head",
     8: "tp_all_reduce",
+    9: "rms_norm",
 }
 
 
