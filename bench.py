@@ -399,8 +399,11 @@ def check_parity(args, gen, schedule, model, cfg, prefill, token, pos, world, tp
     result = {"checked": f"logits of the first timed step (token {token}, position {pos}) against the CPU oracle"}
     ref = None
     if tp:
+        # the residual stream every rank ends up with: the tagged buffer of the in-kernel
+        # exchange, or the accumulators the NCCL flavour sums between launches
+        mine = globs.tp.hidden_tagged[:, 0].cpu() if globs.tp is not None else globs.residual_acc.cpu()
         streams = [None] * world
-        dist.all_gather_object(streams, globs.tp.hidden_tagged[:, 0].cpu())
+        dist.all_gather_object(streams, mine)
         caches = [None] * world
         dist.all_gather_object(caches, (k_shard, v_shard))
         result["ranks_bit_identical_residual"] = all(torch.equal(streams[0], s) for s in streams[1:])
@@ -630,6 +633,7 @@ def run_ours(args):
             torch.cuda.synchronize()
         barrier()
         t0 = time.perf_counter()
+        step_s = []
         for i in range(K):
             host_in.copy_(ids[W + i])
             dev_in.copy_(host_in.view(B, 1), non_blocking=True)
@@ -637,8 +641,10 @@ def run_ours(args):
             host_out.copy_(out.view(-1), non_blocking=True)
             torch.cuda.current_stream().synchronize()
             _ = int(host_out[0])
+            step_s.append(time.perf_counter())
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
+        log("e2e per-step ms: " + " ".join(f"{(b - a) * 1e3:.2f}" for a, b in zip([t0] + step_s, step_s)))
         gen.check()
         e2e = e2e_s
 

@@ -54,7 +54,7 @@ def summarize(globs) -> dict:
             d["wait"].append(us(T_WAIT_DONE) - us(T_CONSUMER_START))
             if op in (1, 4, 5, 6, 7):
                 d["activation"].append(us(T_ACT_READY) - us(T_WAIT_DONE))
-                if op in (1, 5, 7):
+                if op in (1, 5, 7) and getattr(globs, "batch_size", 1) == 1:
                     d["act:load"].append(us(6) - us(T_WAIT_DONE))
                     d["act:sync"].append(us(7) - us(6))
                     d["act:norm"].append(us(T_ACT_READY) - us(7))
@@ -70,6 +70,10 @@ def summarize(globs) -> dict:
                 if int(t[6]) != 0:  # only the chunk's owner waits for arrivals and broadcasts
                     d["arrivals"].append(us(6) - us(5))
                     d["reduce_bcast"].append(us(T_CONSUMER_DONE) - us(6))
+            elif op == 9:  # batched launches: one sequence's RMSNorm for all SMs
+                d["load"].append(us(6) - us(T_WAIT_DONE))
+                d["sync"].append(us(7) - us(6))
+                d["norm_store_signal"].append(us(T_CONSUMER_DONE) - us(7))
             else:
                 d["work"].append(us(T_CONSUMER_DONE) - us(T_WAIT_DONE))
             key = (_layer_of(ins[sm, i]), op)
