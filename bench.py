@@ -81,8 +81,8 @@ def parse_args():
                          "(one launch per token) or NCCL between 2L+1 launches")
     ap.add_argument("--tp-chunks", type=int, default=0, help="chunks per in-kernel all-reduce (0 = H / 1024)")
     ap.add_argument("--batch", type=int, default=1,
-                    help="independent sequences decoded per launch (2..8: the batched kernel; each sequence "
-                         "gets a seeded random KV length in [256, 4096] unless --prefill is given)")
+                    help="independent sequences decoded per launch (2..8: the batched kernel; 9..64: its tcgen05 "
+                         "build; each sequence gets a seeded random KV length in [256, 4096] unless --prefill is given)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -453,7 +453,8 @@ def check_parity_batched(gen, schedule, model, cfg, lens, tokens, step, device):
     globs = schedule.globs
     torch.cuda.synchronize()
     pos = [n + step for n in lens]
-    caches = [tuple(c[:, b : b + 1, : pos[b] + 2].cpu().clone() for c in model.stacked_kv_cache) for b in range(len(lens))]
+    caches = {b: tuple(c[:, b : b + 1, : pos[b] + 2].cpu().clone() for c in model.stacked_kv_cache)
+              for b in range(len(lens))}
     out = gen.run(tokens.view(-1, 1).to(device), pos_id=pos)
     gen.check()
     logits = globs.logits.cpu()
@@ -461,7 +462,9 @@ def check_parity_batched(gen, schedule, model, cfg, lens, tokens, step, device):
     worst = {"max_rel": 0.0, "cosine": 1.0}
     floor_worst = {"max_rel": 0.0, "cosine": 1.0}
     ok = literal = True
-    for b in range(len(lens)):
+    # every sequence up to 8; beyond that a spread of 8 (each costs two full-depth oracle runs)
+    checked = list(range(len(lens))) if len(lens) <= 8 else sorted({round(i * (len(lens) - 1) / 7) for i in range(8)})
+    for b in checked:
         ref.k_cache, ref.v_cache = caches[b]
         exact = ref.decode_token_exact(int(tokens[b]), pos[b])
         want = ref.decode_token(int(tokens[b]), pos[b])
@@ -476,8 +479,8 @@ def check_parity_batched(gen, schedule, model, cfg, lens, tokens, step, device):
         floor_worst = {"max_rel": max(floor_worst["max_rel"], floor["max_rel"]),
                        "cosine": min(floor_worst["cosine"], floor["cosine"])}
     return {
-        "checked": f"logits of all {len(lens)} sequences at the first timed step, each against its own "
-                   "single-sequence run of the CPU oracle",
+        "checked": f"logits of {len(checked)} of {len(lens)} sequences at the first timed step, each against its "
+                   "own single-sequence run of the CPU oracle",
         "ok": bool(ok), "meets_stated_tolerance": bool(literal),
         "max_rel": worst["max_rel"], "cosine": worst["cosine"], "oracle_vs_float32": floor_worst,
         "tolerance": f"stated: max_rel <= {MAX_REL_TOL}, cosine >= {COSINE_TOL}; ok uses twice the bf16 oracle's own "

@@ -64,7 +64,7 @@ enum {
 #define MKB_BARRIER_ROW_RMS_READ 8
 #define MKB_BARRIER_ROW_RMS_NORM 9 /* batched launches: see MKB_OP_RMS_NORM */
 
-#define MKB_MAX_BATCH 8
+#define MKB_MAX_BATCH 64
 
 /* MkbGlobals.flags */
 #define MKB_FLAG_RECORD_TIMINGS 1u /* write per-instruction event times (ns) into `timings` */
@@ -259,6 +259,11 @@ typedef struct MkbGlobals {
      *   - the schedule holds one MKB_OP_RMS_NORM per sequence and norm; `normed_states`
      *     (bf16 [batch, H]) receives their output;
      *   - hidden_size <= 4096, tp.size <= 1, not available through mkb_launch_no_alloc.
+     * batch 9..MKB_MAX_BATCH runs a third build in which the projections are small-M GEMMs on
+     * the tcgen05 tensor cores (blocks of 128 weight rows x the sequences, accumulators in
+     * tensor memory, activations streamed per 128-column slice): the schedule's blocks are then
+     * 128 rows (every block size of the Python Globals is 128), head_dim must be 128,
+     * pos_id_device is required (pos_ids holds 8 entries), and argmax_out is not written.
      * batch 0 or 1: the single-sequence kernel and the layout of the reference. */
     int32_t batch;
     int32_t pos_ids[8];

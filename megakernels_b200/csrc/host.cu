@@ -19,6 +19,12 @@ namespace mkb_batched {  // megakernel_batched.cu
 int max_batch();
 cudaError_t launch(const void* params, size_t params_bytes, int grid, cudaStream_t stream);
 }
+namespace mkb_gemm {  // megakernel_gemm.cu
+int max_batch();
+int block_rows();
+int stage_cols();
+cudaError_t launch(const void* params, size_t params_bytes, int grid, cudaStream_t stream);
+}
 
 using namespace mkb;
 
@@ -46,11 +52,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-struct KvMapKey {  // also used for weight maps: (ptr, K, R, rows, L)
+struct KvMapKey {  // also used for weight maps: (ptr, K, R, rows, L, box) and activation maps
     const void* ptr;
     int D, Hkv, T, LB;
+    int box = 0;
     bool operator==(const KvMapKey& o) const {
-        return ptr == o.ptr && D == o.D && Hkv == o.Hkv && T == o.T && LB == o.LB;
+        return ptr == o.ptr && D == o.D && Hkv == o.Hkv && T == o.T && LB == o.LB && box == o.box;
     }
 };
 struct KvMapEntry {
@@ -126,9 +133,11 @@ int kv_tensor_map(DeviceState* ds, const void* ptr, int D, int Hkv, int T, int L
 }
 
 // 4-D view [64, rows, K/64, L] of a stacked weight [L, rows, K] with the 128-byte swizzle;
-// one box is one ring stage of a `kc`-column slice: {64, 16 rows, min(kc, 1024)/64, 1}.
-int weight_tensor_map(DeviceState* ds, const void* ptr, int K, int kc, int rows, int L, CUtensorMap* out) {
-    KvMapKey key{ptr, -K, kc, rows, L};
+// one box is one ring stage of a `kc`-column slice: {64, box_rows, min(kc, stage_cols)/64, 1}
+// (16 rows x 1024 columns; 128 x 128 for the GEMM build).
+int weight_tensor_map(DeviceState* ds, const void* ptr, int K, int kc, int rows, int L, CUtensorMap* out,
+                      int box_rows = 16, int stage_cols = 1024) {
+    KvMapKey key{ptr, -K, kc, rows, L, box_rows};
     if (ds)
         for (auto& e : ds->maps)
             if (e.key == key) {
@@ -137,10 +146,10 @@ int weight_tensor_map(DeviceState* ds, const void* ptr, int K, int kc, int rows,
             }
     int rc = get_encode_fn();
     if (rc) return rc;
-    const int cols = kc > 1024 ? 1024 : kc;
+    const int cols = kc > stage_cols ? stage_cols : kc;
     cuuint64_t dims[4] = {64, (cuuint64_t)rows, (cuuint64_t)K / 64, (cuuint64_t)L};
     cuuint64_t strides[3] = {(cuuint64_t)K * 2, 128, (cuuint64_t)rows * K * 2};
-    cuuint32_t box[4] = {64, 16, (cuuint32_t)cols / 64, 1};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)cols / 64, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUtensorMap m;
     CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims,
@@ -149,6 +158,36 @@ int weight_tensor_map(DeviceState* ds, const void* ptr, int K, int kc, int rows,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
+    if (ds) {
+        if (ds->maps.size() >= 64) ds->maps.erase(ds->maps.begin());
+        ds->maps.push_back({key, m});
+    }
+    *out = m;
+    return MKB_OK;
+}
+
+// GEMM build: activations [batch, K] bf16 as a 3-D view [64, batch, K/64] with the 128-byte
+// swizzle; a box is {64, n rows, stage_cols / 64}: rows beyond `batch` read as zero.
+int activation_tensor_map(DeviceState* ds, const void* ptr, int K, int batch, int n, int stage_cols, CUtensorMap* out) {
+    KvMapKey key{ptr, -K, batch, n, -1, stage_cols};
+    if (ds)
+        for (auto& e : ds->maps)
+            if (e.key == key) {
+                *out = e.map;
+                return MKB_OK;
+            }
+    int rc = get_encode_fn();
+    if (rc) return rc;
+    cuuint64_t dims[3] = {64, (cuuint64_t)batch, (cuuint64_t)K / 64};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)n, (cuuint32_t)stage_cols / 64};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled (activations) failed with CUresult %d", (int)r);
     if (ds) {
         if (ds->maps.size() >= 64) ds->maps.erase(ds->maps.begin());
         ds->maps.push_back({key, m});
@@ -248,9 +287,17 @@ int validate(const MkbGlobals* g) {
             return fail(MKB_ERR_INVALID_ARGUMENT, "residual_scale %g must be a positive integer", g->residual_scale);
     }
     if (g->batch > 1) {
-        if (g->batch > MKB_MAX_BATCH || g->batch > mkb_batched::max_batch())
+        if (g->batch > MKB_MAX_BATCH || g->batch > mkb_gemm::max_batch())
             return fail(MKB_ERR_UNSUPPORTED, "batch %d: at most %d sequences per launch", g->batch, MKB_MAX_BATCH);
         if (H > 4096) return fail(MKB_ERR_UNSUPPORTED, "batched decode supports hidden_size <= 4096, got %d", H);
+        if (g->batch > mkb_batched::max_batch()) {  // the tcgen05 build: 128-row blocks, one head per block
+            if (D != 128 || H % 128 != 0 || I % 128 != 0 || g->vocab_size % 128 != 0 || R % 128 != 0)
+                return fail(MKB_ERR_UNSUPPORTED, "batch > %d needs head_dim 128 and sizes that are multiples of 128",
+                            mkb_batched::max_batch());
+            if (!g->pos_id_device)
+                return fail(MKB_ERR_INVALID_ARGUMENT, "batch > %d needs pos_id_device (one position per sequence)",
+                            mkb_batched::max_batch());
+        }
         if (tp.size > 1) return fail(MKB_ERR_UNSUPPORTED, "batched decode has no tensor-parallel variant");
         if (!g->normed_states || !aligned16(g->normed_states))
             return fail(MKB_ERR_INVALID_ARGUMENT, "batch > 1 needs normed_states (bf16 [batch, H], 16-byte aligned)");
@@ -376,11 +423,16 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
     p.attn_scale_log2e = g->attn_scale * 1.4426950408889634f;
     p.rms_eps = g->rms_norm_eps;
     p.skip_attn_reduction = g->skip_attn_reduction;
-    p.thr_qkv_waits_down = (p.H / 16) * (p.I / p.R);
-    p.thr_attn_waits_qkv = p.D / 16;
+    // rows per block of the schedule: 16, or 128 for the tcgen05 build (batch > 8)
+    const bool gemm = p.batch > mkb_batched::max_batch();
+    const int br = gemm ? mkb_gemm::block_rows() : 16;
+    p.thr_qkv_waits_down = (p.H / br) * (p.I / p.R);
+    p.thr_attn_waits_qkv = p.D / br;
     p.thr_oproj_waits_attn = p.Hq;
-    p.thr_upgate_waits_oproj = (p.H / 16) * (p.o_in / p.R);
-    p.thr_down_waits_upgate = p.R / 16;
+    p.thr_upgate_waits_oproj = (p.H / br) * (p.o_in / p.R);
+    p.thr_down_waits_upgate = p.R / br;
+    p.gemm_n = (p.batch + 15) / 16 * 16;
+    if (gemm) p.argmax_out = nullptr;  // no fused argmax in this build: the host reduces the logits
     const unsigned ms = g->wait_timeout_ms ? g->wait_timeout_ms : 2000u;
     p.timeout_ns = (unsigned long long)ms * 1000000ull;
     p.l2_window_stages = g_l2_window_stages;
@@ -406,7 +458,17 @@ int prepare_launch(const MkbGlobals* g, DeviceState* ds, int* status, int sm_cou
         {g->lm_head_weights, p.H, p.H, p.V, 1, &p.lm_map},
     };
     for (const auto& wm : wmaps) {
-        rc = weight_tensor_map(ds, wm.ptr, wm.K, wm.kc, wm.rows, wm.L, wm.out);
+        rc = gemm ? weight_tensor_map(ds, wm.ptr, wm.K, wm.kc, wm.rows, wm.L, wm.out, br, mkb_gemm::stage_cols())
+                  : weight_tensor_map(ds, wm.ptr, wm.K, wm.kc, wm.rows, wm.L, wm.out);
+        if (rc) return rc;
+    }
+    if (gemm) {
+        const int sc = mkb_gemm::stage_cols();
+        rc = activation_tensor_map(ds, g->normed_states, p.H, p.batch, p.gemm_n, sc, &p.x_normed_map);
+        if (rc) return rc;
+        rc = activation_tensor_map(ds, g->attn_out, p.o_in, p.batch, p.gemm_n, sc, &p.x_attn_map);
+        if (rc) return rc;
+        rc = activation_tensor_map(ds, g->silu_out, p.I, p.batch, p.gemm_n, sc, &p.x_silu_map);
         if (rc) return rc;
     }
 
@@ -452,6 +514,10 @@ int mkb_launch(const MkbGlobals* g, void* cuda_stream) {
     KParams p;
     rc = prepare_launch(g, ds, (g && g->status) ? g->status : ds->status, ds->sm_count, p);
     if (rc) return rc;
+    if (p.batch > mkb_batched::max_batch()) {
+        MKB_CUDA(mkb_gemm::launch(&p, sizeof(p), g->num_sms, (cudaStream_t)cuda_stream));
+        return MKB_OK;
+    }
     if (p.batch > 1) {
         MKB_CUDA(mkb_batched::launch(&p, sizeof(p), g->num_sms, (cudaStream_t)cuda_stream));
         return MKB_OK;
@@ -496,7 +562,8 @@ int mkb_validate_instructions(const MkbGlobals* g, const int32_t* host_instructi
     if (!host_instructions) return fail(MKB_ERR_INVALID_ARGUMENT, "host_instructions is NULL");
     const int L = g->num_layers, H = g->hidden_size, I = g->intermediate_size, D = g->head_dim;
     const int Hq = g->num_attention_heads, Hkv = g->num_kv_heads, R = g->matvec_reduction_size;
-    const int qkv_blocks = (Hq + 2 * Hkv) * D / 16;
+    const int br = g->batch > mkb_batched::max_batch() ? mkb_gemm::block_rows() : 16;  // rows per block
+    const int qkv_blocks = (Hq + 2 * Hkv) * D / br;
     for (int sm = 0; sm < g->num_sms; ++sm) {
         for (int i = 0; i < g->queue_len; ++i) {
             const int32_t* w = host_instructions + ((size_t)sm * g->queue_len + i) * MKB_INTS_PER_INSTRUCTION;
@@ -531,22 +598,22 @@ int mkb_validate_instructions(const MkbGlobals* g, const int32_t* host_instructi
                 } break;
                 case MKB_OP_O_PROJ_RESIDUAL:
                     if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
-                    if (!range_ok(w[2], w[3], H / 16)) return bad("block range outside the hidden rows");
+                    if (!range_ok(w[2], w[3], H / br)) return bad("block range outside the hidden rows");
                     if (w[4] < 0 || w[4] >= Hq * D / R) return bad("reduction block out of range");
                     break;
                 case MKB_OP_RMS_UPGATE_SILU:
                     if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
                     if (w[2] < 0 || w[2] > MKB_INTS_PER_INSTRUCTION - 3) return bad("block list too long");
                     for (int j = 0; j < w[2]; ++j)
-                        if (w[3 + j] < 0 || w[3 + j] >= I / 16) return bad("block outside the intermediate rows");
+                        if (w[3 + j] < 0 || w[3 + j] >= I / br) return bad("block outside the intermediate rows");
                     break;
                 case MKB_OP_DOWN_PROJ_RESIDUAL:
                     if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
-                    if (!range_ok(w[2], w[3], H / 16)) return bad("block range outside the hidden rows");
+                    if (!range_ok(w[2], w[3], H / br)) return bad("block range outside the hidden rows");
                     if (w[4] < 0 || w[4] >= I / R) return bad("reduction block out of range");
                     break;
                 case MKB_OP_RMS_LM_HEAD:
-                    if (!range_ok(w[1], w[2], g->vocab_size / 16)) return bad("block range outside the vocabulary");
+                    if (!range_ok(w[1], w[2], g->vocab_size / br)) return bad("block range outside the vocabulary");
                     break;
                 case MKB_OP_RMS_NORM:
                     if (g->batch <= 1) return bad("RMS_NORM instruction in a single-sequence launch");

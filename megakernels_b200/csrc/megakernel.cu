@@ -34,7 +34,7 @@ struct Ctx {
     // position of sequence b's token (batched build: kept behind the control words)
     __device__ __forceinline__ int pos_of(int b) const {
         if constexpr (kBatch == 1) return pos;
-        else return cta_abort[8 + b];
+        else return cta_abort[8 + b];  // control words 0..7, then one position per sequence
     }
 
     __device__ __forceinline__ uint32_t full_bar(int slot) const { return base + kSmemBars + slot * 8; }
@@ -50,6 +50,23 @@ struct Ctx {
     __device__ __forceinline__ uint32_t stage_addr(int slot) const {
         return base + kSmemRing + slot * kStageBytes;
     }
+    // GEMM build: activation ring and the two tensor-memory accumulators
+    __device__ __forceinline__ uint32_t xfull_bar(int slot) const {
+        return base + kSmemBars + (2 * kNumStages + 2 * kOutSlots + slot) * 8;
+    }
+    __device__ __forceinline__ uint32_t xempty_bar(int slot) const {
+        return base + kSmemBars + (2 * kNumStages + 2 * kOutSlots + kXStages + slot) * 8;
+    }
+    __device__ __forceinline__ uint32_t acc_full_bar(int buf) const {
+        return base + kSmemBars + (2 * kNumStages + 2 * kOutSlots + 2 * kXStages + buf) * 8;
+    }
+    __device__ __forceinline__ uint32_t acc_empty_bar(int buf) const {
+        return base + kSmemBars + (2 * kNumStages + 2 * kOutSlots + 2 * kXStages + 2 + buf) * 8;
+    }
+    __device__ __forceinline__ uint32_t xstage_addr(int slot) const {
+        return base + kSmemXRing + slot * kXStageBytes;
+    }
+    __device__ __forceinline__ uint32_t tmem_base() const { return (uint32_t)cta_abort[6]; }
 };
 
 // one thread per role stamps event times (ns) into the instruction's timing row
@@ -228,10 +245,10 @@ struct TpPoll {
 // matvec geometry
 // --------------------------------------------------------------------------- //
 // A 16-row x KC block of a weight matrix is streamed as KC/1024 ring stages of
-// 16 rows x 1024 columns (one stage of 16 x KC when KC < 1024).  A stage is one
+// 16 rows x 1024 columns (one stage of 16 x KC when KC < 1024; the GEMM build streams
+// 128-row blocks as KC/128 stages of 128 x 128).  A stage is one
 // tiled TMA copy with the 128-byte swizzle, laid out [64-column chunk][row][128 B];
 // consumer warp w multiplies column chunk w with four m16n8k16 tensor-core MMAs.
-constexpr int kStageCols = 1024;
 __host__ __device__ inline int stages_per_block(int kc) { return kc > kStageCols ? kc / kStageCols : 1; }
 __host__ __device__ inline int stage_cols(int kc) { return kc > kStageCols ? kStageCols : kc; }
 
@@ -498,6 +515,8 @@ __device__ void loader_main(Ctx c) {
 // consumers: matvec
 // --------------------------------------------------------------------------- //
 struct ConsumerState {
+    uint32_t xstage = 0;  // GEMM build: activation-ring stages consumed so far
+    uint32_t acc = 0;     // GEMM build: accumulator blocks issued so far (buffer = acc & 1)
     uint32_t slot = 0;    // ring slot of the next stage (mirrors the loader's sequence)
     uint32_t phase = 0;   // parity of that slot's current use
     uint32_t oslot = 0;   // output-ring slot of the next block (mirrors the storer's)
@@ -540,8 +559,15 @@ __device__ __forceinline__ uint32_t consumer_wait_stage(const Ctx& c, ConsumerSt
     return c.stage_addr(cs.slot);
 }
 __device__ __forceinline__ void consumer_release_stage(const Ctx& c, ConsumerState& cs, int lane) {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(c.empty_bar(cs.slot));
+    if constexpr (kGemm) {
+        // one arrival frees a stage in this build (the MMA issuer's commit, for the GEMM
+        // instructions); the attention warps therefore meet before thread 0 arrives
+        consumer_sync();
+        if (threadIdx.x == 0) mbar_arrive(c.empty_bar(cs.slot));
+    } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.empty_bar(cs.slot));
+    }
     if (++cs.slot == kNumStages) {
         cs.slot = 0;
         cs.phase ^= 1u;
@@ -659,7 +685,7 @@ __device__ __forceinline__ void stage_activation(const Ctx& c, const __nv_bfloat
                 st_shared_v4(c.base + kSmemAttn + ch * 16, v.x, v.y, v.z, v.w);
             }
         }
-    } else {
+    } else if constexpr (!kGemm) {
         const int ch = own_chunk(warp, lane, 0, kc);  // kc <= 4096: one chunk per thread
         if (ch >= 0) {
             uint4 v[kBatch];
@@ -1522,6 +1548,280 @@ __device__ bool consumer_residual_op(const Ctx& c, ConsumerState& cs, int op, co
                                  p.thr_down_waits_rms, (size_t)p.I);
 }
 
+
+#if MKB_BATCH > 8
+// --------------------------------------------------------------------------- //
+// GEMM build: the projections on the 5th-generation tensor cores
+// --------------------------------------------------------------------------- //
+// out[sequence][row] = sum_k W[row][k] * X[sequence][k] for a block of 128 weight rows:
+// A = the weight tile of a ring stage (128 rows x 128 columns, K-major, 128-byte swizzle, as the
+// tiled TMA copy leaves it), B = the activation slice of the same columns ([sequences] x 128,
+// K-major, same swizzle), D = 128 lanes x N fp32 columns in tensor memory (N = batch rounded up
+// to 16).  One thread issues the MMAs; four warps read finished accumulators back and apply the
+// epilogue; a second loader thread streams the activation slices once their producer is done.
+struct GemmOp {
+    int op, layer, nblocks, kc;   // blocks of this instruction (up/gate: 2 per listed block), input columns
+    int first_block;              // range instructions
+    const int* list;              // up/gate block list
+    const CUtensorMap* xmap;      // activations
+    int xchunk0;                  // first 64-column chunk of the input slice
+    int wait_layer, wait_row, wait_slot, wait_thr;  // what the activations wait for
+};
+__device__ __forceinline__ bool gemm_decode(const KParams& p, const int* w, GemmOp& g) {
+    g.op = __ldg(w);
+    g.list = nullptr;
+    g.xchunk0 = 0;
+    switch (g.op) {
+        case MKB_OP_RMS_QKV_ROPE_APPEND:
+            g.layer = __ldg(w + 1); g.first_block = __ldg(w + 2); g.nblocks = __ldg(w + 3) - g.first_block;
+            g.kc = p.H; g.xmap = &p.x_normed_map;
+            g.wait_layer = g.layer; g.wait_row = MKB_BARRIER_ROW_RMS_NORM; g.wait_slot = 0; g.wait_thr = p.batch;
+            return true;
+        case MKB_OP_RMS_UPGATE_SILU:
+            g.layer = __ldg(w + 1); g.nblocks = 2 * __ldg(w + 2); g.list = w + 3; g.first_block = 0;
+            g.kc = p.H; g.xmap = &p.x_normed_map;
+            g.wait_layer = g.layer; g.wait_row = MKB_BARRIER_ROW_RMS_NORM; g.wait_slot = 1; g.wait_thr = p.batch;
+            return true;
+        case MKB_OP_RMS_LM_HEAD:
+            g.layer = p.L - 1; g.first_block = __ldg(w + 1); g.nblocks = __ldg(w + 2) - g.first_block;
+            g.kc = p.H; g.xmap = &p.x_normed_map;
+            g.wait_layer = p.L - 1; g.wait_row = MKB_BARRIER_ROW_RMS_NORM; g.wait_slot = 2; g.wait_thr = p.batch;
+            return true;
+        case MKB_OP_O_PROJ_RESIDUAL:
+            g.layer = __ldg(w + 1); g.first_block = __ldg(w + 2); g.nblocks = __ldg(w + 3) - g.first_block;
+            g.kc = p.R; g.xmap = &p.x_attn_map; g.xchunk0 = __ldg(w + 4) * (p.R / 64);
+            g.wait_layer = g.layer; g.wait_row = MKB_OP_ATTENTION_REDUCTION - 1; g.wait_slot = 0;
+            g.wait_thr = p.thr_oproj_waits_attn * p.batch;
+            return true;
+        case MKB_OP_DOWN_PROJ_RESIDUAL:
+            g.layer = __ldg(w + 1); g.first_block = __ldg(w + 2); g.nblocks = __ldg(w + 3) - g.first_block;
+            g.kc = p.R; g.xmap = &p.x_silu_map; g.xchunk0 = __ldg(w + 4) * (p.R / 64);
+            g.wait_layer = g.layer; g.wait_row = MKB_OP_RMS_UPGATE_SILU - 1; g.wait_slot = __ldg(w + 4);
+            g.wait_thr = p.thr_down_waits_upgate;
+            return true;
+        default:
+            return false;
+    }
+}
+
+__device__ __forceinline__ void tma_tile3_g2s(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                              uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+// Second loader thread: waits for the producer of every GEMM instruction's activations (the wait
+// the consumers of the other builds perform), then streams the [N x 128] slices stage by stage.
+__device__ void xloader_main(Ctx c) {
+    const KParams& p = *c.p;
+    const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
+    c.role = kRoleLoader;
+    const uint32_t xbytes = (uint32_t)p.gemm_n * kStageCols * 2u;
+    uint32_t xstage = 0;
+    bool alive = true;
+    for (int i = 0; i < p.queue_len && alive; ++i) {
+        GemmOp g;
+        if (!gemm_decode(p, queue + i * MKB_INTS_PER_INSTRUCTION, g)) continue;
+        c.instr = i;
+        c.opcode = g.op;
+        if (*c.cta_abort) break;
+        c.cta_abort[4] = 1;  // the weight loader may look further ahead while this instruction waits
+        const bool ok = wait_counter(c, bar_addr(p, g.wait_layer, g.wait_row, g.wait_slot), g.wait_thr,
+                                     g.wait_layer, g.wait_row, g.wait_slot);
+        c.cta_abort[4] = 0;
+        if (!ok) break;
+        const int spb = stages_per_block(g.kc);
+        for (int b = 0; b < g.nblocks && alive; ++b)
+            for (int st = 0; st < spb; ++st) {
+                const int slot = xstage % kXStages;
+                const uint32_t parity = ((xstage / kXStages) & 1u) ^ 1u;
+                if (!mbar_try_wait(c.xempty_bar(slot), parity) && !mbar_wait_slow(c, c.xempty_bar(slot), parity, true)) {
+                    alive = false;
+                    break;
+                }
+                mbar_expect_tx(c.xfull_bar(slot), xbytes);
+                tma_tile3_g2s(c.xstage_addr(slot), g.xmap, 0, 0, g.xchunk0 + st * (kStageCols / 64), c.xfull_bar(slot));
+                ++xstage;
+            }
+    }
+    reinterpret_cast<volatile int*>(c.cta_abort)[5] = (int)xstage;  // for the exit path
+}
+
+// K-major operand tile with the 128-byte swizzle: rows 128 bytes apart, groups of 8 rows 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ bool gemm_wait(const Ctx& c, ConsumerState& cs, uint32_t bar, uint32_t parity) {
+    if (!cs.dead && !mbar_try_wait(bar, parity)) {
+        if (!mbar_wait_slow(c, bar, parity, true)) cs.dead = true;
+    }
+    return !cs.dead;
+}
+
+// One GEMM instruction.  Consumer warp 0 (one lane) issues the MMAs, warps 4..7 are the
+// epilogue (tensor-memory lane quarter = warp % 4, thread = weight row), the others only keep
+// their ring bookkeeping in step.
+__device__ bool gemm_instruction(const Ctx& c, ConsumerState& cs, const int* w) {
+    const KParams& p = *c.p;
+    GemmOp g;
+    gemm_decode(p, w, g);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int spb = stages_per_block(g.kc);
+    const uint32_t n = (uint32_t)p.gemm_n;
+    const uint32_t tmem = c.tmem_base();
+
+    if (warp == 0 && lane == 0) {
+        // fp32 accumulate, bf16 x bf16, both operands K-major, N = n, M = 128
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(kBlockRows >> 4) << 24);
+        uint32_t slot = cs.slot, phase = cs.phase, xstage = cs.xstage, acc = cs.acc;
+        for (int b = 0; b < g.nblocks; ++b) {
+            const uint32_t buf = acc & 1u, use = acc >> 1;
+            gemm_wait(c, cs, c.acc_empty_bar(buf), (use & 1u) ^ 1u);  // the epilogue has drained this accumulator
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int st = 0; st < spb; ++st) {
+                const uint32_t xslot = xstage % kXStages;
+                gemm_wait(c, cs, c.full_bar(slot), phase);
+                gemm_wait(c, cs, c.xfull_bar(xslot), (xstage / kXStages) & 1u);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t wb = c.stage_addr(slot), xb = c.xstage_addr(xslot);
+                if (!cs.dead) {
+#pragma unroll
+                    for (int ch = 0; ch < kStageCols / 64; ++ch)  // one swizzle atom (64 columns) at a time
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)                // four K = 16 steps inside the 128-byte rows
+                            umma_f16(tmem + buf * kBatch, umma_smem_desc(wb + ch * (kBlockRows * 128) + k * 32),
+                                     umma_smem_desc(xb + ch * (n * 128) + k * 32), idesc, (uint32_t)((st | ch | k) != 0));
+                }
+                umma_commit(c.empty_bar(slot));    // both stages are free once these MMAs have read them
+                umma_commit(c.xempty_bar(xslot));
+                if (++slot == kNumStages) { slot = 0; phase ^= 1u; }
+                ++xstage;
+            }
+            umma_commit(c.acc_full_bar(buf));
+            ++acc;
+        }
+    } else if (warp >= 4 && warp < 8) {
+        const int q = warp & 3, r = q * 32 + lane;  // this thread's row inside the block
+        uint32_t acc = cs.acc;
+        const bool pair = g.op == MKB_OP_RMS_UPGATE_SILU;
+        for (int b = 0; b < g.nblocks; b += pair ? 2 : 1) {
+            const int blk = g.list ? __ldg(g.list + (b >> 1)) : g.first_block + b;
+            const uint32_t buf = acc & 1u, use = acc >> 1;
+            gemm_wait(c, cs, c.acc_full_bar(buf), use & 1u);
+            const uint32_t buf2 = (acc + 1) & 1u, use2 = (acc + 1) >> 1;
+            if (pair) gemm_wait(c, cs, c.acc_full_bar(buf2), use2 & 1u);
+            cs.dead = __any_sync(0xffffffffu, cs.dead);  // the lanes shuffle below: leave together
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+            const int grow = blk * kBlockRows + r;  // row of the projection's output
+            for (uint32_t c0 = 0; c0 < n; c0 += 8) {
+                float v[8], v2[8];
+                tmem_ld8(lane_addr + buf * kBatch + c0, v);
+                if (pair) tmem_ld8(lane_addr + buf2 * kBatch + c0, v2);
+                if (cs.dead) continue;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int s = (int)c0 + j;  // sequence
+                    const bool live = s < p.batch;
+                    switch (g.op) {
+                        case MKB_OP_RMS_QKV_ROPE_APPEND: {
+                            float x = bf16_round(v[j]);
+                            const int k_start = p.Hq * p.D, v_start = (p.Hq + p.Hkv) * p.D;
+                            const int start = blk * kBlockRows;
+                            const int ps = live ? c.pos_of(s) : 0;
+                            if (start < v_start) {  // head_dim == 128 == block: the block is one head
+                                const float cs_ = __ldg(p.rope_cos + (size_t)ps * p.D + r);
+                                const float sn = __ldg(p.rope_sin + (size_t)ps * p.D + r);
+                                const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+                                x = x * cs_ + ((r & 1) ? other : -other) * sn;
+                            }
+                            if (live) {
+                                __nv_bfloat16* dst;
+                                if (start < k_start) {
+                                    dst = p.q_rope + (size_t)s * p.o_in + start;
+                                } else {
+                                    const size_t tok = (((size_t)g.layer * p.B + s) * p.T + ps) * p.Hkv * p.D;
+                                    dst = (start < v_start) ? p.k_cache + tok + (start - k_start)
+                                                            : p.v_cache + tok + (start - v_start);
+                                }
+                                dst[r] = __float2bfloat16_rn(x);
+                            }
+                        } break;
+                        case MKB_OP_O_PROJ_RESIDUAL:
+                        case MKB_OP_DOWN_PROJ_RESIDUAL:
+                            if (live)
+                                red_add_u64(p.residual_acc + (size_t)s * p.H + grow,
+                                            (unsigned long long)(__float2ll_rn(v[j] * kResidualScale) * p.residual_mult));
+                            break;
+                        case MKB_OP_RMS_UPGATE_SILU: {
+                            const float up = bf16_round(v[j]), gate = bf16_round(v2[j]);
+                            const float x = bf16_round(gate / (1.f + __expf(-gate))) * up;
+                            if (live) p.silu_out[(size_t)s * p.I + grow] = __float2bfloat16_rn(x);
+                        } break;
+                        default:  // MKB_OP_RMS_LM_HEAD
+                            if (live) p.logits[(size_t)s * p.V + grow] = __float2bfloat16_rn(v[j]);
+                            break;
+                    }
+                }
+            }
+            // hand the accumulator(s) back, then publish what this block wrote
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(c.acc_empty_bar(buf));
+                if (pair) mbar_arrive(c.acc_empty_bar(buf2));
+            }
+            acc += pair ? 2 : 1;
+            if (g.op == MKB_OP_RMS_QKV_ROPE_APPEND || pair) {
+                epilogue_sync();  // all four warps' global writes of this block precede the signal
+                if (tid == 4 * 32 && !cs.dead) {
+                    const int slot = pair ? blk * kBlockRows / p.R : blk * kBlockRows / p.D;
+                    red_release_gpu_add(bar_addr(p, g.layer, g.op - 1, slot), 1);
+                }
+            }
+        }
+        if (g.op == MKB_OP_O_PROJ_RESIDUAL || g.op == MKB_OP_DOWN_PROJ_RESIDUAL) {
+            epilogue_sync();
+            if (tid == 4 * 32 && !cs.dead) red_release_gpu_add(bar_addr(p, g.layer, g.op - 1, 0), g.nblocks);
+        }
+    }
+    // everybody's view of the rings moves past this instruction
+    const uint32_t stages = (uint32_t)(g.nblocks * spb);
+    const uint32_t total = cs.slot + stages;
+    cs.phase ^= (total / kNumStages) & 1u;
+    cs.slot = total % kNumStages;
+    cs.xstage += stages;
+    cs.acc += (uint32_t)g.nblocks;
+    volatile int* verdict = verdict_word(c, cs);
+    if (cs.dead) *c.cta_abort = 1;
+    consumer_sync();
+    if (tid == 0) *verdict = *c.cta_abort ? 0 : 1;
+    consumer_sync();
+    return *verdict != 0;
+}
+#endif  // MKB_BATCH > 8
+
 template <bool kTP>
 __device__ void consumer_main(Ctx c) {
     const KParams& p = *c.p;
@@ -1538,6 +1838,15 @@ __device__ void consumer_main(Ctx c) {
         switch (op) {
             case MKB_OP_NOOP:
                 break;
+#if MKB_BATCH > 8
+            case MKB_OP_RMS_QKV_ROPE_APPEND:
+            case MKB_OP_RMS_UPGATE_SILU:
+            case MKB_OP_RMS_LM_HEAD:
+            case MKB_OP_O_PROJ_RESIDUAL:
+            case MKB_OP_DOWN_PROJ_RESIDUAL:
+                ok = gemm_instruction(c, cs, w);
+                break;
+#else
             case MKB_OP_RMS_QKV_ROPE_APPEND:
             case MKB_OP_RMS_UPGATE_SILU:
             case MKB_OP_RMS_LM_HEAD:
@@ -1547,6 +1856,7 @@ __device__ void consumer_main(Ctx c) {
             case MKB_OP_DOWN_PROJ_RESIDUAL:
                 ok = consumer_residual_op(c, cs, op, w);
                 break;
+#endif
             case MKB_OP_PARTIAL_ATTENTION: {
                 const int gqa = p.Hq / p.Hkv;
                 if (p.D == 64) ok = consumer_attention<64, 4>(c, cs, w);
@@ -1685,7 +1995,14 @@ __device__ __forceinline__ void storer_signal(StorerState& ss, int lane, int* ad
     ss.n_entries++;
 }
 
-#if MKB_BATCH > 1
+#if MKB_BATCH > 8
+// ---- GEMM build: the epilogue warps write the outputs themselves; this warp's first lane is
+// the activation loader (a warp of its own, so that it never time-slices with the weight loader)
+template <bool kTP>
+__device__ void storer_main(Ctx c) {
+    if ((threadIdx.x & 31) == 0) xloader_main(c);
+}
+#elif MKB_BATCH > 1
 // ---- batched build: every block carries 16 rows x up to 8 sequences -------------------- //
 // Lane = row + 16 * half; the lane owns sequences 4 * half .. 4 * half + 3 of its row.
 constexpr int kSeqPerLane = kBatch / 2;
@@ -2025,7 +2342,17 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < kNumStages; ++s) {
             mbar_init(c.full_bar(s), 1);
-            mbar_init(c.empty_bar(s), kConsumerWarps);
+            mbar_init(c.empty_bar(s), kGemm ? 1 : kConsumerWarps);
+        }
+        if constexpr (kGemm) {
+            for (int s = 0; s < kXStages; ++s) {
+                mbar_init(c.xfull_bar(s), 1);
+                mbar_init(c.xempty_bar(s), 1);
+            }
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(c.acc_full_bar(b), 1);
+                mbar_init(c.acc_empty_bar(b), 4);  // one arrival per epilogue warp
+            }
         }
         for (int s = 0; s < kOutSlots; ++s) {
             mbar_init(c.out_full_bar(s), kConsumerWarps);
@@ -2034,7 +2361,7 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
         for (int k = 0; k < 8; ++k) c.cta_abort[k] = 0;
         if constexpr (kBatch > 1)
             for (int s = 0; s < kBatch; ++s)
-                c.cta_abort[8 + s] = s < p.batch ? (p.pos_id_ptr ? __ldg(p.pos_id_ptr + s) : p.pos_ids[s]) : 0;
+                c.cta_abort[8 + s] = s >= p.batch ? 0 : p.pos_id_ptr ? __ldg(p.pos_id_ptr + s) : p.pos_ids[s & 7];
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -2055,6 +2382,17 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
     }
 
     const int warp = threadIdx.x >> 5;
+#if MKB_BATCH > 8
+    // tensor memory for the two accumulators: allocated and freed by warp 0, address through shared memory
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(c.base + kSmemCtl + 6 * 4),
+                     "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#endif
     if (warp < kConsumerWarps) {
         consumer_main<kTP>(c);
     } else if (warp == kLoaderWarp) {
@@ -2062,7 +2400,26 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
     } else {
         storer_main<kTP>(c);
     }
+#if MKB_BATCH > 8
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#endif
     __syncthreads();
+#if MKB_BATCH > 8
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(c.tmem_base()), "r"((uint32_t)kTmemCols)
+                     : "memory");
+    // activation slices still in flight (only after an abort: every issued slice is otherwise consumed)
+    if (warp == kStorerWarp && (threadIdx.x & 31) == 0) {
+        const uint32_t issued = (uint32_t)c.cta_abort[5];
+        const uint32_t first = issued > (uint32_t)kXStages ? issued - kXStages : 0u;
+        c.role = kRoleLoader;
+        for (uint32_t s = first; s < issued; ++s) {
+            const uint32_t bar = c.xfull_bar(s % kXStages);
+            const uint32_t parity = (s / kXStages) & 1u;
+            if (!mbar_try_wait(bar, parity)) mbar_wait_slow(c, bar, parity, false);
+        }
+    }
+#endif
 
     // No bulk copy may still be in flight when the CTA's shared memory goes away:
     // wait (bounded) for every stage the loader issued most recently.
@@ -2087,9 +2444,14 @@ __global__ void __launch_bounds__(kBlockThreads, 1) megakernel(const __grid_cons
 __global__ void __launch_bounds__(kBlockThreads, 1) megakernel_tp(const __grid_constant__ KParams p) {
     megakernel_body<true>(p);
 }
-#else
-// The batched build: up to kBatch sequences per launch (MkbGlobals.batch > 1).
+#elif MKB_BATCH <= 8
+// The batched build: up to kBatch sequences per launch (MkbGlobals.batch = 2..8).
 __global__ void __launch_bounds__(kBlockThreads, 1) megakernel_batched(const __grid_constant__ KParams p) {
+    megakernel_body<false>(p);
+}
+#else
+// The GEMM build: 9..kBatch sequences per launch, projections on tcgen05 tensor cores.
+__global__ void __launch_bounds__(kBlockThreads, 1) megakernel_gemm(const __grid_constant__ KParams p) {
     megakernel_body<false>(p);
 }
 #endif

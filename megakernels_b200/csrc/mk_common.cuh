@@ -21,23 +21,31 @@
 
 #include "../../include/mkb200.h"
 
-// The kernel source is compiled twice.  MKB_BATCH == 1 (default): one sequence per launch, the
-// latency-optimised build.  MKB_BATCH == 8: up to 8 independent sequences per launch (the
-// activation vectors of all sequences are the 8 columns of the MMA's B operand, so the weights
-// are still streamed once); it trades two ring stages for room to park 8 activation vectors.
+// The kernel source is compiled three times.
+//   MKB_BATCH == 1 (default): one sequence per launch, the latency-optimised build.
+//   MKB_BATCH == 8: up to 8 independent sequences per launch; the activation vectors of all
+//     sequences are the 8 columns of the mma.sync B operand, so the weights are still streamed
+//     once; it trades two ring stages for room to park 8 activation vectors.
+//   MKB_BATCH == 64: 9..64 sequences per launch; the projections become small-M GEMMs on the
+//     5th-generation tensor cores: blocks of 128 weight rows are the M side of tcgen05.mma, the
+//     sequences its N side, the accumulator lives in tensor memory, and the activations are
+//     streamed per 128-column slice next to the weights instead of being parked.
 #ifndef MKB_BATCH
 #define MKB_BATCH 1
 #endif
 #if MKB_BATCH == 1
 #define MKB_NAMESPACE mkb
-#else
+#elif MKB_BATCH <= 8
 #define MKB_NAMESPACE mkb_batched
+#else
+#define MKB_NAMESPACE mkb_gemm
 #endif
 
 namespace MKB_NAMESPACE {
 
 // ---- geometry ------------------------------------------------------------ //
 constexpr int kBatch = MKB_BATCH;
+constexpr bool kGemm = kBatch > 8;
 constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;  // 512
 constexpr int kLoaderWarp = kConsumerWarps;            // warp 16
@@ -46,32 +54,40 @@ constexpr int kBlockThreads = (kConsumerWarps + 2) * 32;  // 576
 
 constexpr int kStageBytes = 32768;  // one ring stage
 constexpr int kNumStages = kBatch == 1 ? 6 : 4;  // 192 (128) KiB of weights / KV in flight per SM
-constexpr int kOutSlots = kBatch == 1 ? 4 : 2;   // ring of per-block partial sums, consumer -> storer
-constexpr int kOutSlotFloats = 16 * 16 * kBatch; // [row][sequence][partial]
-constexpr int kBlockRows = 16;      // output rows per matvec block
+constexpr int kOutSlots = kGemm ? 1 : kBatch == 1 ? 4 : 2;  // ring of per-block partial sums, consumer -> storer
+constexpr int kOutSlotFloats = kGemm ? 16 : 16 * 16 * kBatch;  // [row][sequence][partial] (unused by the GEMM build)
+constexpr int kBlockRows = kGemm ? 128 : 16;     // output rows per block
+constexpr int kStageCols = kGemm ? 128 : 1024;   // input columns per ring stage: a stage is kBlockRows x kStageCols bf16
+static_assert(kBlockRows * kStageCols * 2 == kStageBytes, "");
 // Parked activation vectors: one per sequence, kActStride bytes apart.  The stride is 64 mod
 // 128 so that the 8 lanes of a quarter warp (two sequences x four chunks) hit 8 different
 // 16-byte bank groups when they load their B-operand fragments.
 constexpr int kActBytes = kBatch == 1 ? 16384 : 8192;  // longest vector: H (or R) bf16 elements
 constexpr int kActStride = kBatch == 1 ? 0 : kActBytes + 64;
+// GEMM build: a second ring carries the activation slices, [sequence][kStageCols] bf16 per stage
+constexpr int kXStages = kGemm ? 4 : 0;
+constexpr int kXStageBytes = kBatch * kStageCols * 2;
+constexpr int kTmemCols = 2 * (kBatch < 32 ? 32 : kBatch);  // two accumulators of kBatch fp32 columns
 
 // attention: cross-warp merge scratch, 8 slots x 4 heads x (D + m + l)
 constexpr int kAttnHeadsPerPass = 4;
 constexpr int kAttnSlotFloats = kAttnHeadsPerPass * (128 + 4);
 constexpr int kAttnScratchFloats = 8 * kAttnSlotFloats;
-constexpr int kActAreaBytes = kBatch == 1 ? kAttnScratchFloats * 4 : kBatch * kActStride;
-static_assert(kActAreaBytes >= kAttnScratchFloats * 4 && kActAreaBytes >= kActBytes, "");
+constexpr int kActAreaBytes = (kBatch == 1 || kGemm) ? kAttnScratchFloats * 4 : kBatch * kActStride;
+static_assert(kActAreaBytes >= kAttnScratchFloats * 4 && (kGemm || kActAreaBytes >= kActBytes), "");
 
 // shared-memory map (byte offsets from the 1024-aligned base)
 constexpr int kSmemRing = 0;
-constexpr int kSmemOut = kSmemRing + kNumStages * kStageBytes;
+constexpr int kSmemXRing = kSmemRing + kNumStages * kStageBytes;  // GEMM build only (1024-byte aligned tiles)
+constexpr int kSmemOut = kSmemXRing + kXStages * kXStageBytes;
 constexpr int kSmemAttn = kSmemOut + kOutSlots * kOutSlotFloats * 4;  // activations / attention scratch
 constexpr int kSmemRed = kSmemAttn + kActAreaBytes;            // 32 floats
 constexpr int kSmemRope = kSmemRed + 32 * 4;                   // cos[D], sin[D] at every sequence's position
-constexpr int kSmemBars = kSmemRope + kBatch * 2 * 128 * 4;    // mbarriers, 8 B each
-constexpr int kNumMbars = 2 * kNumStages + 2 * kOutSlots;
+constexpr int kSmemBars = kSmemRope + (kGemm ? 0 : kBatch * 2 * 128 * 4);  // mbarriers, 8 B each
+// ring full/empty, out-slot full/empty, then (GEMM build) X-ring full/empty and accumulator full/empty x 2
+constexpr int kNumMbars = 2 * kNumStages + 2 * kOutSlots + 2 * kXStages + (kGemm ? 4 : 0);
 constexpr int kSmemCtl = kSmemBars + kNumMbars * 8;            // control words, then the positions
-constexpr int kCtlWords = 8 + 8;
+constexpr int kCtlWords = 8 + (kBatch < 8 ? 8 : kBatch);
 constexpr int kSmemTotal = kSmemCtl + kCtlWords * 4;
 static_assert(kSmemTotal + 1024 <= 227 * 1024, "shared memory budget of one CTA");
 constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack to align the base
@@ -113,6 +129,10 @@ struct KParams {
     int batch;
     int pos_ids[8];
     __nv_bfloat16* normed;
+    // GEMM build: activations as 3-D [64, batch, K/64] views with the 128-byte swizzle; a box is
+    // one X-ring stage {64, kBatch rows (rows beyond `batch` read as zero), kStageCols/64}
+    CUtensorMap x_normed_map, x_attn_map, x_silu_map;
+    int gemm_n;  // N of the MMAs: batch rounded up to a multiple of 16
     float attn_scale_log2e;  // attn_scale * log2(e)
     float rms_eps;
     int skip_attn_reduction;

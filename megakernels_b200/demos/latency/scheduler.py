@@ -49,7 +49,8 @@ class LatencyScheduleOptions:
 
     num_attention_partitions: int = 1
     coalesce_o_proj: bool = False
-    # > 1: batched decode, that many independent sequences per launch (at most 8); the model's
+    # > 1: batched decode, that many independent sequences per launch (at most 64; more than 8
+    # switches the schedule to 128-row blocks for the tcgen05 build of the kernel); the model's
     # KV cache must hold them (ExtraModelConfig.max_batch_size)
     batch_size: int = 1
     # > 0 on a tensor-parallel shard: all-reduce the residual stream inside the kernel,
@@ -95,7 +96,12 @@ def make_globals(
     config = model.config
     device = model.device
     dtype = model.dtype
-    assert 1 <= batch_size <= 8 and batch_size <= model.extra_config.max_batch_size
+    assert 1 <= batch_size <= 64 and batch_size <= model.extra_config.max_batch_size
+    # 9..64 sequences run the tcgen05 build of the kernel, whose blocks are 128 weight rows
+    # (the M side of the MMA); everything else counts blocks of 16 rows as the reference does
+    block = 128 if batch_size > 8 else 16
+    if batch_size > 8:
+        assert config.head_dim == 128 and config.vocab_size % 128 == 0, "the GEMM build needs 128-row blocks"
 
     def make_buffer(shape, buffer_dtype=dtype):
         shape = [shape] if isinstance(shape, int) else list(shape)
@@ -157,11 +163,11 @@ def make_globals(
         head_dim=config.head_dim,
         hidden_size=config.hidden_size,
         intermediate_size=inter,
-        up_gate_proj_block_size=16,
-        down_proj_block_size=16,
-        qkv_block_size=16,
-        o_proj_block_size=16,
-        lm_head_block_size=16,
+        up_gate_proj_block_size=block,
+        down_proj_block_size=block,
+        qkv_block_size=block,
+        o_proj_block_size=block,
+        lm_head_block_size=block,
         matvec_reduction_size=reduction,
         attn_kv_block_size=16,
         attn_reduction_size=4,

@@ -86,7 +86,8 @@ class MK_Generator(Generator):
         # schedules that contain the LM head and when the megakernel actually runs.
         globs = schedule.globs
         has_head = globs.instructions is not None and bool((globs.instructions[:, :, 0] == 7).any())
-        if fused_argmax and has_head and not skip_mk and globs.hidden_states.is_cuda:
+        # (the tcgen05 build for more than 8 sequences leaves the argmax to the host)
+        if fused_argmax and has_head and not skip_mk and globs.hidden_states.is_cuda and globs.batch_size <= 8:
             globs.argmax_out = torch.zeros(
                 globs.batch_size, dtype=torch.int32, device=globs.hidden_states.device
             )
@@ -169,6 +170,12 @@ class MK_Generator(Generator):
         if globs.batch_size > 1:
             globs.pos_ids = [int(p) for p in pos_id]
             assert len(globs.pos_ids) == globs.batch_size
+            if globs.batch_size > 8:  # more positions than the launch struct holds: device array
+                if globs.pos_id_device is None:
+                    globs.pos_id_device = torch.zeros(
+                        globs.batch_size, dtype=torch.int32, device=globs.hidden_states.device
+                    )
+                globs.pos_id_device.copy_(torch.tensor(globs.pos_ids, dtype=torch.int32), non_blocking=True)
         else:
             globs.pos_id = pos_id
         if not self.skip_mk:

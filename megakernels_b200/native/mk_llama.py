@@ -353,6 +353,8 @@ def pack_globals(
         g.batch = batch
         g.normed_states = _check_tensor("normed_states", normed_states, bf16, 2)
         if pos_id_device is None:
+            if batch > 8:
+                raise ValueError("more than 8 sequences need pos_id_device (int32, one position per sequence)")
             if pos_ids is None or len(pos_ids) != batch:
                 raise ValueError("a batched launch needs pos_ids (one position per sequence) or pos_id_device")
             for s, pos in enumerate(pos_ids):

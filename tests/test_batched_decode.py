@@ -39,6 +39,26 @@ def test_single_sequence_words_are_unchanged_by_the_batch_fields():
     assert serialize_and_pad(RMS_Norm(7, 1, 3))[:5] == [9, 7, 1, 3, 0]
 
 
+def test_more_than_eight_sequences_schedule_blocks_of_128_rows():
+    """The tcgen05 build multiplies blocks of 128 weight rows: block indices, counts and barrier
+    thresholds of the schedule follow."""
+    set_sm_count_override(148)
+    cfg = LlamaConfig.llama_3_1_8b(num_hidden_layers=1, vocab_size=4096)
+    _, schedule = batched_schedule(cfg, 16, 1, 64)
+    g = schedule.globs
+    assert (g.qkv_block_size, g.o_proj_block_size, g.up_gate_proj_block_size, g.down_proj_block_size,
+            g.lm_head_block_size) == (128,) * 5
+    th = g.barrier_thresholds()
+    assert th["attn_waits_qkv_per_head"] == 1 and th["downproj_waits_upgate"] == 2048 // 128
+    assert th["qkv_waits_downproj"] == (4096 // 128) * 7 and th["upgate_waits_oproj"] == (4096 // 128) * 2
+    ins = schedule.get_linear_instructions()
+    qkv = sorted(b for i in ins if type(i).__name__ == "LayerNorm_QKV_MatVecRopeAppend" for b in i.block_indices())
+    assert qkv == list(range((32 + 16) * 128 // 128))
+    up = sorted(b for i in ins if type(i).__name__ == "LayerNormDoubleMatVecSiLU" for b in i.block_idxs)
+    assert up == list(range(14336 // 128))
+    assert g.barriers.shape[2] >= 16 * 32
+
+
 @pytest.mark.parametrize("batch,parts", [(4, 1), (8, 3)])
 def test_batched_schedule_covers_every_sequence(batch, parts):
     set_sm_count_override(148)
@@ -66,7 +86,12 @@ def test_batched_schedule_covers_every_sequence(batch, parts):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape,batch,parts", [("8b", 4, 3), ("8b", 8, 1), ("1b", 5, 2), ("1b", 2, 4)])
+@pytest.mark.parametrize(
+    "shape,batch,parts",
+    # up to 8 sequences: mma.sync with the sequences as B-operand columns; more: tcgen05 GEMMs
+    # (128-row blocks, head_dim 128 only), incl. a batch that is not a multiple of the MMA's N step
+    [("8b", 4, 3), ("8b", 8, 1), ("1b", 5, 2), ("1b", 2, 4), ("8b", 16, 1), ("8b", 40, 2), ("8b", 64, 1)],
+)
 def test_batched_decode_matches_independent_sequences(shape, batch, parts):
     from megakernels_b200.generators import MK_Generator
     from oracle.llama_ref import TorchReferenceModel, assert_logits_parity
