@@ -659,11 +659,13 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
 // act[chunk]; warp w only ever reads chunks {st * 128 + w * 8 + j}, so each warp
 // loads, normalises and writes exactly its own chunks and a __syncwarp suffices.
 // Lane l of warp w owns chunk (st, j) = (l / 8 + 4 * k, l % 8) for k = 0, 1.
+// (The partition is in 1024-element groups whatever the ring-stage geometry of the build is.)
 __device__ __forceinline__ int own_chunk(int warp, int lane, int k, int kc) {
+    constexpr int kGroup = 1024;
     const int st = (lane >> 3) + 4 * k;
-    const int col_chunk = warp * 8 + (lane & 7);  // within the stage
-    if (st >= stages_per_block(kc) || col_chunk * 8 >= stage_cols(kc)) return -1;
-    return st * (kStageCols / 8) + col_chunk;
+    const int col_chunk = warp * 8 + (lane & 7);  // within the group
+    if (st >= (kc > kGroup ? kc / kGroup : 1) || col_chunk * 8 >= (kc > kGroup ? kGroup : kc)) return -1;
+    return st * (kGroup / 8) + col_chunk;
 }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c2, uint32_t d) {
@@ -1631,6 +1633,9 @@ __device__ void xloader_main(Ctx c) {
                                      g.wait_layer, g.wait_row, g.wait_slot);
         c.cta_abort[4] = 0;
         if (!ok) break;
+        // the activations were written with ordinary stores by other SMs and are read here by
+        // the TMA engine: order the two proxies after the acquiring poll
+        asm volatile("fence.proxy.async.global;" ::: "memory");
         const int spb = stages_per_block(g.kc);
         for (int b = 0; b < g.nblocks && alive; ++b)
             for (int st = 0; st < spb; ++st) {
