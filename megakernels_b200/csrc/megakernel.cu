@@ -601,7 +601,9 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
     const uint32_t act0 = c.base + kSmemAttn + (uint32_t)(warp * 64 + t * 8) * 2u + (uint32_t)(g * kActStride);
 
     for (int b = 0; b < nblocks; ++b) {
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        // two accumulators: the four MMAs of a stage form two chains of two instead of one of four
+        // (the latency of a dependent mma.sync, not its issue rate, bounds a warp's time per stage)
+        float d[4] = {0.f, 0.f, 0.f, 0.f}, d2[4] = {0.f, 0.f, 0.f, 0.f};
         for (int st = 0; st < spb; ++st) {
             const uint32_t sbase = consumer_wait_stage(c, cs);
             if (st == 0 && b == 0 && tid == 0) rec(c, MKB_T_CONSUMER_FIRST_STAGE);
@@ -616,12 +618,14 @@ __device__ __forceinline__ void consume_blocks(const Ctx& c, ConsumerState& cs, 
                     x1 = lds_v4(act0 + (uint32_t)st * (kStageCols * 2) + 64);
                 }
                 mma_16816(d, w0.x, w1.x, w0.y, w1.y, x0.x, x0.y);
-                mma_16816(d, w0.z, w1.z, w0.w, w1.w, x0.z, x0.w);
+                mma_16816(d2, w0.z, w1.z, w0.w, w1.w, x0.z, x0.w);
                 mma_16816(d, w2.x, w3.x, w2.y, w3.y, x1.x, x1.y);
-                mma_16816(d, w2.z, w3.z, w2.w, w3.w, x1.z, x1.w);
+                mma_16816(d2, w2.z, w3.z, w2.w, w3.w, x1.z, x1.w);
             }
             consumer_release_stage(c, cs, lane);
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) d[e] += d2[e];
         const uint32_t obar = c.out_empty_bar(cs.oslot);
         if (!cs.dead && !mbar_try_wait(obar, cs.ophase ^ 1u)) {
             if (!mbar_wait_slow(c, obar, cs.ophase ^ 1u, true)) cs.dead = true;
@@ -777,10 +781,8 @@ __device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& 
                 unpack8(hv, x[k]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const long long lo = (long long)(((unsigned long long)a[i].y << 32) | a[i].x);
-                    const long long hi = (long long)(((unsigned long long)a[i].w << 32) | a[i].z);
-                    x[k][2 * i] += __ll2float_rn(lo) * kResidualInvScale;
-                    x[k][2 * i + 1] += __ll2float_rn(hi) * kResidualInvScale;
+                    x[k][2 * i] += q32_to_float(a[i].x, a[i].y);
+                    x[k][2 * i + 1] += q32_to_float(a[i].z, a[i].w);
                 }
             } else {
                 unpack8(hv, x[k]);
@@ -854,15 +856,122 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     return *verdict != 0;
 }
 
+// What rms_activation_plain needs, in shared memory (written once by thread 0 at kernel start;
+// `trow` = the timing row of the consumers' current instruction, or null, by consumer thread 0).
+struct HotConsts {
+    const __nv_bfloat16* hidden;
+    const long long* acc;
+    __nv_bfloat16* normed;
+    int* trow;
+    int H;
+    float inv_H;
+    float eps;
+    int pad;
+};
+static_assert(sizeof(HotConsts) <= 64, "");
+
+// RMSNorm of `hidden + acc * 2^-32` (see rms_activation for the arithmetic) for the single-GPU
+// and batched builds.  Out of line (inlined copies made the compiler spill state of the whole
+// consumer loop), and written so that nothing comes through the stack: a function that receives
+// the context by reference reads it back from local memory, and with 220 KB of the SM's 256 KB
+// given to shared memory those loads miss L1 three times out of four - measured here as 600 -
+// 700 cycles each, eight or so in a row, 3 - 3.8 us per activation on the critical path of every
+// layer where the loads of the vector itself take 0.3.  Arguments are three scalars; constants
+// come from shared memory; the norm weights are fetched together with the vector.
+template <int CHUNKS>
+__device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w, int* read_done, int seq) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint4 h0 = lds_v4(base + kSmemHot), h1 = lds_v4(base + kSmemHot + 16), h2 = lds_v4(base + kSmemHot + 32);
+    const __nv_bfloat16* hidden = reinterpret_cast<const __nv_bfloat16*>(((unsigned long long)h0.y << 32) | h0.x);
+    const long long* accp = reinterpret_cast<const long long*>(((unsigned long long)h0.w << 32) | h0.z);
+    __nv_bfloat16* normed = reinterpret_cast<__nv_bfloat16*>(((unsigned long long)h1.y << 32) | h1.x);
+    int* trow = reinterpret_cast<int*>(((unsigned long long)h1.w << 32) | h1.z);
+    const int H = (int)h2.x;
+    const float inv_H = __uint_as_float(h2.y), eps = __uint_as_float(h2.z);
+    const size_t seq_off = kBatch == 1 ? 0 : (size_t)seq * H;
+
+    // one chunk of 8 elements per thread up to H = 4096, a second one (loaded after the first has
+    // been converted: fewer live registers, one more round trip) beyond
+    int chs[CHUNKS];
+    uint4 wv[CHUNKS];
+    float x[CHUNKS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+        chs[k] = own_chunk(warp, lane, k, H);
+        if (chs[k] < 0) continue;
+        const uint4 hv = ld_cg_v4(hidden + seq_off + (size_t)chs[k] * 8);
+        const long long* acc = accp + seq_off + (size_t)chs[k] * 8;
+        uint4 a[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
+        wv[k] = ld_nc_v4(norm_w + (size_t)chs[k] * 8);
+        unpack8(hv, x[k]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[k][2 * i] += q32_to_float(a[i].x, a[i].y);
+            x[k][2 * i + 1] += q32_to_float(a[i].z, a[i].w);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(x[k][e], x[k][e], ss);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(base + kSmemRed + warp * 4), "f"(ss) : "memory");
+    if (tid == 0 && trow != nullptr) trow[MKB_T_RMS_LOADED] = (int)(uint32_t)globaltimer_ns();
+    consumer_sync();
+    // every thread's loads of the residual stream have returned (their values went into
+    // the sums above), so later writers may now be let in.  A relaxed add is enough: a
+    // load that has delivered its value cannot observe a store issued afterwards, and a
+    // releasing add would stall this thread (and with it warp 0 and the whole ring) on a fence.
+    if (tid == 0 && read_done != nullptr) atomicAdd(read_done, 1);
+    if (tid == 0 && trow != nullptr) trow[MKB_T_RMS_SUMMED] = (int)(uint32_t)globaltimer_ns();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < kConsumerWarps; k += 4) {
+        const uint4 r = lds_v4(base + kSmemRed + k * 4);
+        tot += __uint_as_float(r.x) + __uint_as_float(r.y) + __uint_as_float(r.z) + __uint_as_float(r.w);
+    }
+    const float rstd = rsqrtf(tot * inv_H + eps);
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+        if (chs[k] >= 0) {
+            float wgt[8];
+            unpack8(wv[k], wgt);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                o[e] = pack_bf16x2(wgt[2 * e] * bf16_round(x[k][2 * e] * rstd),
+                                   wgt[2 * e + 1] * bf16_round(x[k][2 * e + 1] * rstd));
+            if constexpr (kBatch == 1)
+                st_shared_v4(base + kSmemAttn + chs[k] * 16, o[0], o[1], o[2], o[3]);
+            else
+                *reinterpret_cast<uint4*>(normed + seq_off + (size_t)chs[k] * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    __syncwarp();
+}
+
+// Up to 4096 elements a thread holds one chunk and the code is light enough to be inlined (an
+// out-of-line copy pays for its callee-saved registers with 2 x 48 KB of local-memory traffic per
+// call, over a microsecond); wider models (two chunks per thread) take the out-of-line copy, whose
+// inlining would make the compiler spill state of the whole consumer loop.
+__device__ __noinline__ void rms_activation_wide(const __nv_bfloat16* norm_w, int* read_done, int seq) {
+    rms_activation_body<2>(norm_w, read_done, seq);
+}
+__device__ __forceinline__ void rms_activation_plain(int H, const __nv_bfloat16* norm_w, int* read_done, int seq) {
+    if (H <= 4096) rms_activation_body<1>(norm_w, read_done, seq);
+    else rms_activation_wide(norm_w, read_done, seq);
+}
+
 // Out of line: the polling loops would otherwise be inlined three times into the consumer loop.
 __device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefetch pf, int wait_layer,
                                                    int which) {
     return rms_activation<true, false>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
 }
 
-__device__ __noinline__ void rms_activation_plain(const Ctx& c, const RmsPrefetch pf, int* read_done, int seq = 0) {
-    rms_activation<false, true>(c, pf, 0u, 0, 0, read_done, seq);
-}
 
 // kTP selects the tensor-parallel build of the kernel.  It is a compile-time switch and the two
 // builds are separate kernels: merely having the exchange code in the same kernel cost the
@@ -883,23 +992,26 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
         consume_blocks(c, cs, nblocks, c.p->H);
         return true;
     }
-    RmsPrefetch pf;
-    rms_prefetch(c, norm_w, pf);
     bool tagged = false;
     if constexpr (kTP) {
         // the residual stream arrives as tagged values from the chunk owners
-        if (needed && c.p->tp_size > 1) {
-            const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
-            if (!rms_activation_tagged(c, pf, wait_layer, which)) return false;
+        if (c.p->tp_size > 1) {
+            RmsPrefetch pf;
+            rms_prefetch(c, norm_w, pf);
+            if (needed) {
+                const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
+                if (!rms_activation_tagged(c, pf, wait_layer, which)) return false;
+            } else {
+                // the tensor-parallel exchange keeps the running residual stream in its tagged
+                // buffer; the only plain read there is the token embedding before the first all-reduce
+                rms_activation<false, false>(c, pf);
+            }
             tagged = true;
         }
     }
     if (!tagged) {
         if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
-        // the tensor-parallel exchange keeps the running residual stream in its tagged buffer;
-        // the only plain read there is the token embedding before the first all-reduce
-        if (kTP && c.p->tp_size > 1) rms_activation<false, false>(c, pf);
-        else rms_activation_plain(c, pf, read_done);
+        rms_activation_plain(c.p->H, norm_w, read_done, 0);
     }
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->H);
@@ -1521,14 +1633,12 @@ __device__ bool consumer_rms_norm(const Ctx& c, ConsumerState& cs, const int* w)
     const __nv_bfloat16* norm_w = which == 0 ? p.attn_ln_w + (size_t)layer * p.H
                                   : which == 1 ? p.mlp_ln_w + (size_t)layer * p.H
                                                : p.lm_norm_w;
-    RmsPrefetch pf;
-    rms_prefetch(c, norm_w, pf);
     const bool needed = !(which == 0 && layer == 0);
     const int wait_layer = which == 0 ? layer - 1 : layer;
     const int wait_row = (which == 1 ? MKB_OP_O_PROJ_RESIDUAL : MKB_OP_DOWN_PROJ_RESIDUAL) - 1;
     const int thr = which == 1 ? p.thr_upgate_waits_oproj : p.thr_qkv_waits_down;
     if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, thr, needed)) return false;
-    rms_activation_plain(c, pf, nullptr, seq);
+    rms_activation_plain(p.H, norm_w, nullptr, seq);
     consumer_sync();  // every thread's part of the vector is written
     if (threadIdx.x == 0) red_release_gpu_add(bar_addr(p, layer, MKB_BARRIER_ROW_RMS_NORM, which), 1);
     return true;
@@ -1839,7 +1949,13 @@ __device__ void consumer_main(Ctx c) {
         c.instr = i;
         c.opcode = op;
         bool ok = true;
-        if (threadIdx.x == 0 && op != MKB_OP_NOOP) rec(c, MKB_T_CONSUMER_START);
+        if (threadIdx.x == 0 && op != MKB_OP_NOOP) {
+            rec(c, MKB_T_CONSUMER_START);
+            if (p.timings != nullptr) {  // where rms_activation_plain stamps its phases
+                int* trow = p.timings + ((size_t)blockIdx.x * p.queue_len + i) * MKB_TIMING_SLOTS;
+                asm volatile("st.shared.u64 [%0], %1;" ::"r"(c.base + kSmemHot + 24), "l"(trow) : "memory");
+            }
+        }
         switch (op) {
             case MKB_OP_NOOP:
                 break;
@@ -2364,6 +2480,14 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
             mbar_init(c.out_empty_bar(s), 1);
         }
         for (int k = 0; k < 8; ++k) c.cta_abort[k] = 0;
+        HotConsts* hot = reinterpret_cast<HotConsts*>(gbase + kSmemHot);
+        hot->hidden = p.hidden;
+        hot->acc = p.residual_acc;
+        hot->normed = p.normed;
+        hot->trow = nullptr;
+        hot->H = p.H;
+        hot->inv_H = 1.f / (float)p.H;
+        hot->eps = p.rms_eps;
         if constexpr (kBatch > 1)
             for (int s = 0; s < kBatch; ++s)
                 c.cta_abort[8 + s] = s >= p.batch ? 0 : p.pos_id_ptr ? __ldg(p.pos_id_ptr + s) : p.pos_ids[s & 7];

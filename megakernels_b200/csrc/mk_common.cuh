@@ -88,7 +88,10 @@ constexpr int kSmemBars = kSmemRope + (kGemm ? 0 : kBatch * 2 * 128 * 4);  // mb
 constexpr int kNumMbars = 2 * kNumStages + 2 * kOutSlots + 2 * kXStages + (kGemm ? 4 : 0);
 constexpr int kSmemCtl = kSmemBars + kNumMbars * 8;            // control words, then the positions
 constexpr int kCtlWords = 8 + (kBatch < 8 ? 8 : kBatch);
-constexpr int kSmemTotal = kSmemCtl + kCtlWords * 4;
+// A few launch constants that out-of-line code on the critical path reads from shared memory
+// (HotConsts, 16-byte aligned) instead of chasing pointers through local and parameter memory.
+constexpr int kSmemHot = (kSmemCtl + kCtlWords * 4 + 15) & ~15;
+constexpr int kSmemTotal = kSmemHot + 64;
 static_assert(kSmemTotal + 1024 <= 227 * 1024, "shared memory budget of one CTA");
 constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack to align the base
 
@@ -322,6 +325,13 @@ __device__ __forceinline__ void red_add_u64(void* p, unsigned long long v) {
 // fixed-point format of the residual accumulators: value * 2^32 in a signed 64-bit integer
 constexpr float kResidualScale = 4294967296.f;
 constexpr float kResidualInvScale = 1.f / 4294967296.f;
+// A Q31.32 accumulator (low word, high word) as fp32: integer part and fraction are converted
+// separately (two 32-bit conversions and an FMA instead of a 64-bit conversion, which costs a
+// dozen instructions on the critical path of every RMSNorm).  The result is within one fp32 ulp of
+// the exactly rounded value and, like it, a function of the accumulator's bits alone.
+__device__ __forceinline__ float q32_to_float(uint32_t lo, uint32_t hi) {
+    return fmaf(__uint2float_rn(lo), kResidualInvScale, __int2float_rn((int)hi));
+}
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
