@@ -72,6 +72,8 @@ def parse_args():
     ap.add_argument("--sched", default="rr")
     ap.add_argument("--attn-partitions", type=int, default=0, help="0 = pick from the length")
     ap.add_argument("--no-coalesce-o-proj", action="store_true")
+    ap.add_argument("--separate-reduction", action="store_true",
+                    help="AttentionReduction instructions instead of the last partial of a KV head merging the rows")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="replay one captured decode step per token instead of launching eagerly")
     ap.add_argument("--replicas", action="store_true",
@@ -337,6 +339,7 @@ def build_engine(args, device, tp_size=1, tp_rank=0, group=None, layers=0, steps
     peer = tp_size > 1 and args.tp_exchange == "peer"
     options = LatencyScheduleOptions(
         num_attention_partitions=n_part, coalesce_o_proj=not args.no_coalesce_o_proj,
+        merge_in_last_partial=not args.separate_reduction,
         # chunks of 1024 elements: one pair per consumer thread, a multiple of the TP degree
         tp_all_reduce_chunks=(args.tp_chunks or max(tp_size, cfg.hidden_size // 1024)) if peer else 0,
         batch_size=args.batch,

@@ -223,7 +223,11 @@ typedef struct MkbGlobals {
     int32_t pos_id;
     float attn_scale;
     float rms_norm_eps;
-    int32_t skip_attn_reduction;
+    int32_t skip_attn_reduction; /* 1: one partition per KV head, PartialAttention writes attn_out (the
+                                    reference's only mode); 0: split-KV partials merged by
+                                    AttentionReduction instructions; 2: split-KV without reduction
+                                    instructions - the PartialAttention of a KV head that arrives last
+                                    merges the partial rows itself and signals the o-proj */
 
     /* ---- extensions without a counterpart in the reference call ---- */
     const int32_t *pos_id_device; /* if not NULL the position is read from this device word at

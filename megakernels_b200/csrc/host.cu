@@ -112,15 +112,20 @@ int kv_tensor_map(DeviceState* ds, const void* ptr, int D, int Hkv, int T, int L
             }
     int rc = get_encode_fn();
     if (rc) return rc;
+    // 5-D view [64, T, D/64, Hkv, L*B] with the 128-byte swizzle: a box is `ts` positions of one
+    // head and lands as D/64 sub-tiles of [ts][128 bytes], so that the 8 positions a warp reads
+    // side by side (16 bytes each, same column) fall into 8 different bank groups.  With whole
+    // 256-byte rows in shared memory they all hit the same banks (8-way conflicts, the attention
+    // stages then cost 1.7 us each).
     const int ts = (kStageBytes / 4) / D;
-    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)T, (cuuint64_t)LB};
-    cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)Hkv * D * 2, (cuuint64_t)T * Hkv * D * 2};
-    cuuint32_t box[4] = {(cuuint32_t)D, 1, (cuuint32_t)ts, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    cuuint64_t dims[5] = {64, (cuuint64_t)T, (cuuint64_t)D / 64, (cuuint64_t)Hkv, (cuuint64_t)LB};
+    cuuint64_t strides[4] = {(cuuint64_t)Hkv * D * 2, 128, (cuuint64_t)D * 2, (cuuint64_t)T * Hkv * D * 2};
+    cuuint32_t box[5] = {64, (cuuint32_t)ts, (cuuint32_t)D / 64, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUtensorMap m;
-    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims,
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(ptr), dims,
                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MKB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -263,6 +268,8 @@ int validate(const MkbGlobals* g) {
     if (g->batch <= 1 && !g->pos_id_device && (g->pos_id < 0 || g->pos_id >= g->kv_max_len))
         return fail(MKB_ERR_INVALID_ARGUMENT, "pos_id %d outside the KV cache length %d", g->pos_id, g->kv_max_len);
     if (g->max_partials < 1) return fail(MKB_ERR_INVALID_ARGUMENT, "max_partials must be >= 1");
+    if (g->skip_attn_reduction < 0 || g->skip_attn_reduction > 2)
+        return fail(MKB_ERR_INVALID_ARGUMENT, "skip_attn_reduction must be 0, 1 or 2");
     const MkbTensorParallel& tp = g->tp;
     if (tp.size > 1) {
         if (tp.size > MKB_MAX_TP || tp.rank < 0 || tp.rank >= tp.size)
@@ -582,11 +589,13 @@ int mkb_validate_instructions(const MkbGlobals* g, const int32_t* host_instructi
                     if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
                     if (w[2] < 0 || w[2] >= Hkv) return bad("KV head out of range");
                     if (w[3] < 1 || w[4] < 0 || w[4] >= w[3]) return bad("partial index outside num_partials");
-                    if (!g->skip_attn_reduction && w[4] >= g->max_partials) return bad("partial index beyond max_partials");
-                    if (g->skip_attn_reduction && w[3] != 1) return bad("skip_attn_reduction needs num_partials == 1");
+                    if (g->skip_attn_reduction != 1 && w[4] >= g->max_partials) return bad("partial index beyond max_partials");
+                    if (g->skip_attn_reduction == 1 && w[3] != 1) return bad("skip_attn_reduction = 1 needs num_partials == 1");
+                    if (g->skip_attn_reduction == 2 && w[3] > 24) return bad("at most 24 partials can be merged by the last one");
                     if (w[5] < 0 || w[5] >= (g->batch > 1 ? g->batch : 1)) return bad("sequence outside the batch");
                     break;
                 case MKB_OP_ATTENTION_REDUCTION: {
+                    if (g->skip_attn_reduction == 2) return bad("AttentionReduction instruction although the last partial merges (skip_attn_reduction = 2)");
                     if (w[1] < 0 || w[1] >= L) return bad("layer out of range");
                     if (w[2] < 0 || w[2] + 4 > Hq) return bad("head range outside the Q heads");
                     const int n = w[5];

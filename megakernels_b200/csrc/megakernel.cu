@@ -498,8 +498,8 @@ __device__ void loader_main(Ctx c) {
         const uint32_t dst = c.stage_addr(slot);
         mbar_expect_tx(bar, d.bytes);
         if (d.map == nullptr) {
-            tma_tile4_g2s(dst, &p.k_map, 0, d.kvh, d.t, d.lb, bar, policy);
-            tma_tile4_g2s(dst + kStageBytes / 2, &p.v_map, 0, d.kvh, d.t, d.lb, bar, policy);
+            tma_tile5_g2s(dst, &p.k_map, 0, d.t, 0, d.kvh, d.lb, bar, policy);
+            tma_tile5_g2s(dst + kStageBytes / 2, &p.v_map, 0, d.t, 0, d.kvh, d.lb, bar, policy);
         } else {
             tma_tile4_g2s(dst, d.map, 0, d.c1, d.c2, d.c3, bar, policy);
         }
@@ -1127,6 +1127,73 @@ __device__ __forceinline__ void attn_fold(AttnAcc<GQA, DPL>& a, const float (&s)
     }
 }
 
+// skip_attn_reduction == 2: no AttentionReduction instructions.  Every partial-attention
+// instruction, once its (O, LSE) rows are stored, bumps the counters of its heads; the bump of the
+// first head returns the previous count, and the instruction that finds np - 1 there is the last of
+// its KV head to arrive: it merges the np partial rows of the GQA heads (all visible to it: each
+// writer's bump was a release, this one is an acquire) with the arithmetic of the terminal
+// reduction, writes attn_out and signals the o-proj's counter.  Compared with a separate
+// instruction this takes the poll for the partials, an instruction boundary and the reduction
+// instruction's own start-up off the critical path of every layer.
+template <int D, int GQA>
+__device__ __forceinline__ void attn_arrive_and_merge(const Ctx& c, ConsumerState& cs, int layer, int kvh,
+                                                      int np, int part_slot0, const float* attn_o,
+                                                      const float* attn_lse, __nv_bfloat16* attn_out) {
+    const KParams& p = *c.p;
+    const int tid = threadIdx.x, lane = tid & 31;
+    volatile int* verdict = verdict_word(c, cs);
+    if (tid < 32) {
+        int last = 0;
+        if (lane < GQA && !cs.dead) {
+            int* addr = bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, part_slot0 + kvh * GQA + lane);
+            if (lane == 0) {
+                int old;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(addr) : "memory");
+                last = old == np - 1;
+            } else {
+                red_release_gpu_add(addr, 1);
+            }
+        }
+        if (lane == 0) *verdict = last;
+    }
+    consumer_sync();
+    if (*verdict == 0) return;
+    for (int idx = tid; idx < GQA * D; idx += kConsumerThreads) {  // whole warps: a warp stays inside one head
+        const int head = kvh * GQA + idx / D, dim = idx % D;
+        float lse = -INFINITY;
+        if (lane < np) lse = ld_cg_f32(attn_lse + (size_t)head * p.max_partials + lane);
+        constexpr int NB = 12;
+        const float* base = attn_o + (size_t)head * p.max_partials * D + dim;
+        float acc = 0.f, wgt = 0.f, denom = 0.f;
+        for (int j0 = 0; j0 < np; j0 += NB) {
+            float part[NB];
+#pragma unroll
+            for (int jj = 0; jj < NB; ++jj) part[jj] = ld_cg_f32(base + (size_t)(j0 + jj < np ? j0 + jj : 0) * D);
+            if (j0 == 0) {
+                float mx = lse;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                const float ms = (mx == -INFINITY) ? 0.f : mx;
+                wgt = exp2f(lse - ms);
+                denom = wgt;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+            }
+#pragma unroll
+            for (int jj = 0; jj < NB; ++jj) {
+                const int j = j0 + jj;
+                const float wj = (j < np) ? __shfl_sync(0xffffffffu, wgt, j & 31) : 0.f;
+                acc = fmaf(wj, part[jj], acc);
+            }
+        }
+        const float val = acc * (denom > 0.f ? 1.f / denom : 0.f);
+        const float hi = __shfl_down_sync(0xffffffffu, val, 1);
+        if ((dim & 1) == 0) *reinterpret_cast<uint32_t*>(attn_out + (size_t)head * D + dim) = pack_bf16x2(val, hi);
+    }
+    consumer_sync();  // every thread's stores precede the signal
+    if (tid == 0) red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);
+}
+
 template <int D, int GQA>
 __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w) {
     constexpr int DPL = D / 32;
@@ -1236,10 +1303,12 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-                const uint32_t krow = kbase + (uint32_t)(unit * 16 + nt * 8 + g) * (D * 2) + t * 16;
+                // position (unit * 16 + nt * 8 + g) is line g of its 1024-byte swizzle block; the
+                // 16-byte chunk at byte (t * 16 + j * 64) of the row lives in sub-tile j / 2
+                const uint32_t krow = kbase + (uint32_t)(unit * 16 + nt * 8 + g) * 128u;
 #pragma unroll
                 for (int j = 0; j < KP; ++j) {
-                    const uint4 kk = lds_v4(krow + j * 64);
+                    const uint4 kk = lds_v4(krow + (uint32_t)(j >> 1) * (TS * 128) + (uint32_t)(((t + 4 * (j & 1)) ^ g) << 4));
                     mma_16816(sc[nt], qa[j].x, 0u, qa[j].y, 0u, kk.x, kk.y);
                     mma_16816(sc[nt], qa[j].z, 0u, qa[j].w, 0u, kk.z, kk.w);
                 }
@@ -1279,14 +1348,17 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
             }
             // O += P V: V rows (positions) x 8-dim column tiles through ldmatrix.trans
             const int mat = lane >> 3, rr = lane & 7;
-            const uint32_t vrow = vbase + (uint32_t)(unit * 16 + (mat & 1) * 8 + rr) * (D * 2) +
-                                  (uint32_t)(slice * 32 + (mat >> 1) * 8) * 2;
+            // row (position) rr of a swizzle block; byte column slice * 64 + (mat >> 1) * 16 + h2 * 32
+            // of the 2 D-byte row: sub-tile slice / 2, chunk (slice & 1) * 4 + (mat >> 1) + 2 * h2
+            const uint32_t vrow = vbase + (uint32_t)(slice >> 1) * (TS * 128) +
+                                  (uint32_t)(unit * 16 + (mat & 1) * 8 + rr) * 128u;
+            const uint32_t vchunk = (uint32_t)((slice & 1) * 4 + (mat >> 1));
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {  // two pairs of n-tiles
                 uint32_t b0, b1, b2, b3;
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
-                             : "r"(vrow + h2 * 32));
+                             : "r"(vrow + (((vchunk + 2 * h2) ^ (uint32_t)rr) << 4)));
                 mma_16816(o[2 * h2], pa[0], 0u, pa[1], 0u, b0, b1);
                 mma_16816(o[2 * h2 + 1], pa[0], 0u, pa[1], 0u, b2, b3);
             }
@@ -1303,7 +1375,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
             for (int h = 0; h < GQA; ++h) {
                 const int head = kvh * GQA + h;
                 const float wgt = r.has_cur ? 1.f : 0.f;
-                if (p.skip_attn_reduction) {
+                if (p.skip_attn_reduction == 1) {
                     __nv_bfloat16* dst = attn_out + (size_t)head * D + lane * DPL;
                     if constexpr (DPL == 4) {
                         uint2 v;
@@ -1322,13 +1394,17 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
                 }
             }
             __syncwarp();
-            if (p.skip_attn_reduction) {
+            if (p.skip_attn_reduction == 1) {
                 if (lane == 0)
                     red_release_gpu_add(bar_addr(p, layer, MKB_OP_ATTENTION_REDUCTION - 1, 0), GQA);
-            } else {
+            } else if (p.skip_attn_reduction == 0) {
                 if (lane < GQA)
                     red_release_gpu_add(bar_addr(p, layer, MKB_OP_PARTIAL_ATTENTION - 1, part_slot0 + kvh * GQA + lane), 1);
             }
+        }
+        if (p.skip_attn_reduction == 2) {
+            consumer_sync();  // warp 0's rows are stored
+            attn_arrive_and_merge<D, GQA>(c, cs, layer, kvh, np, part_slot0, attn_o, attn_lse, attn_out);
         }
         return true;
     }
@@ -1377,7 +1453,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
         }
         const float val = den > 0.f ? num / den : 0.f;
         const int head = kvh * GQA + hh;
-        if (p.skip_attn_reduction) {
+        if (p.skip_attn_reduction == 1) {
             const float hi = __shfl_down_sync(0xffffffffu, val, 1);
             if ((d & 1) == 0 && !cs.dead)
                 *reinterpret_cast<uint32_t*>(attn_out + (size_t)head * D + d) = pack_bf16x2(val, hi);
@@ -1389,6 +1465,10 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
     }
     consumer_sync();  // scratch reads and global stores of all threads are done
     consumer_release_stage(c, cs, lane);
+    if (p.skip_attn_reduction == 2) {
+        attn_arrive_and_merge<D, GQA>(c, cs, layer, kvh, np, part_slot0, attn_o, attn_lse, attn_out);
+        return true;
+    }
     if (warp == 0 && !cs.dead) {
         if (p.skip_attn_reduction) {
             if (lane == 0)

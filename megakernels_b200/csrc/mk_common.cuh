@@ -216,6 +216,15 @@ __device__ __forceinline__ void tma_tile4_g2s(uint32_t dst, const CUtensorMap* m
         "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "l"(policy)
         : "memory");
 }
+// 5-D tiled tensor copy global -> shared (K/V tiles)
+__device__ __forceinline__ void tma_tile5_g2s(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                              int c3, int c4, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        ".L2::cache_hint [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_l1(const void* p) {
     asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }

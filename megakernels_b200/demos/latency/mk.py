@@ -48,7 +48,7 @@ def interpret_with_mk(globs: Globals, mk_func, stream=None, **kwargs):
         globs.pos_id,
         globs.attn_scale,
         globs.rms_norm_eps,
-        globs.skip_attn_reduction,
+        2 if globs.merge_in_last_partial else globs.skip_attn_reduction,
         stream=stream if stream is not None else torch.cuda.current_stream(),
         matvec_reduction_size=globs.matvec_reduction_size,
         residual_scale=globs.residual_scale,

@@ -11,6 +11,8 @@ word.  Differences are generalisations the reference does not have:
   (the reference asserts ``skip_attn_reduction``, latency/scheduler.py:276-277);
 * ``coalesce_o_proj`` emits one block-range O-proj instruction per SM instead
   of one per 16-row block (latency/scheduler.py:344-354);
+* ``merge_in_last_partial`` drops the terminal reductions: the partial-attention
+  instruction of a KV head that arrives last merges the partial rows itself;
 * ``tp_all_reduce_chunks`` (tensor-parallel shards only) emits ``TP_AllReduce``
   instructions after every o-proj and down-proj group, so that the ranks
   exchange their partial sums inside the kernel and a token stays one launch.
@@ -49,6 +51,10 @@ class LatencyScheduleOptions:
 
     num_attention_partitions: int = 1
     coalesce_o_proj: bool = False
+    # with more than one attention partition: no AttentionReduction instructions; the partial of a
+    # KV head that arrives last merges the partial rows itself and signals the o-proj (one barrier
+    # hop and one instruction less on the critical path of a layer)
+    merge_in_last_partial: bool = False
     # > 1: batched decode, that many independent sequences per launch (at most 64; more than 8
     # switches the schedule to 128-row blocks for the tcgen05 build of the kernel); the model's
     # KV cache must hold them (ExtraModelConfig.max_batch_size)
@@ -325,7 +331,7 @@ def make_dag_layer(
         return new_nodes, partial_nodes
 
     attn_outputs = partial_nodes
-    if not globs.skip_attn_reduction:
+    if not globs.skip_attn_reduction and not globs.merge_in_last_partial:
         gqa = assert_div(globs.num_attention_heads, globs.num_kv_heads)
         red_nodes: list[DAG_Node] = []
         for head_start in range(0, globs.num_attention_heads, globs.attn_reduction_size):
@@ -469,6 +475,7 @@ class LatencyScheduleBuilder(ScheduleBuilder):
     def make_globals(self, model):  # type: ignore[override]
         skip = self.options.num_attention_partitions == 1
         globs = make_globals(model, skip_attn_reduction=skip, batch_size=self.options.batch_size)
+        globs.merge_in_last_partial = bool(self.options.merge_in_last_partial) and not skip
         extra = model.extra_config
         if self.options.tp_all_reduce_chunks and extra.tp_size > 1:
             globs.tp = TensorParallelState(extra.tp_size, extra.tp_rank, self.options.tp_all_reduce_chunks)

@@ -98,6 +98,9 @@ class BaseGlobals:
         self.pos_id_device: Tensor | None = None  # int32[1]; overrides pos_id when set
         self.tp: TensorParallelState | None = None  # in-kernel tensor-parallel all-reduce
         self.argmax_out: Tensor | None = None  # int32[1]: the kernel's own argmax over the logits
+        # split-KV schedules without AttentionReduction instructions: the last partial of a KV head
+        # to arrive merges the partial rows itself (launched as skip_attn_reduction = 2)
+        self.merge_in_last_partial: bool = False
         # int64 [H]: the token's o-proj / down-proj outputs summed in Q31.32 fixed point by the
         # kernel (integer atomics: the same bits whatever order the SMs arrive in).  The kernel
         # never writes ``hidden_states``; the residual stream is ``residual_stream()``.

@@ -322,7 +322,8 @@ def pack_globals(
     g.pos_id = int(pos_id)
     g.attn_scale = float(attn_scale)
     g.rms_norm_eps = float(rms_norm_eps)
-    g.skip_attn_reduction = int(bool(skip_attn_reduction))
+    # 0: AttentionReduction instructions, 1: one partition writes attn_out, 2: the last partial merges
+    g.skip_attn_reduction = 2 if (skip_attn_reduction is not True and skip_attn_reduction == 2) else int(bool(skip_attn_reduction))
     g.residual_scale = float(residual_scale)
     if tp is not None:
         # megakernels_b200.instructions.TensorParallelState with its buffers attached

@@ -64,6 +64,7 @@ class ScriptConfig:
     memory_fraction: float = 0.0
     attn_partitions: int = 0
     coalesce_o_proj: bool = False
+    merge_in_last_partial: bool = False
 
     def finalize(self):
         if self.mode != "mk":
@@ -143,7 +144,8 @@ def main(config: ScriptConfig):
         prompt_len, config.ntok, model.device, model.num_kv_heads()
     )
     options = LatencyScheduleOptions(
-        num_attention_partitions=n_part, coalesce_o_proj=config.coalesce_o_proj
+        num_attention_partitions=n_part, coalesce_o_proj=config.coalesce_o_proj,
+        merge_in_last_partial=config.merge_in_last_partial,
     )
     schedule = make_schedule_builder(config.setting, options).build(model)
     queues = assign_to_sms(

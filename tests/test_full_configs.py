@@ -51,7 +51,8 @@ def device_model(cfg, max_len, prefill, poison=True, seed_kv=2):
 
 
 def engine(model, partitions, sched="rr"):
-    opts = LatencyScheduleOptions(num_attention_partitions=partitions, coalesce_o_proj=True)
+    opts = LatencyScheduleOptions(num_attention_partitions=partitions, coalesce_o_proj=True,
+                                  merge_in_last_partial=True)
     schedule = build_schedule(model, opts)
     tensorize_instructions(schedule.globs, assign_to_sms(sched, schedule=schedule))
     return schedule, MK_Generator(model, interpreter(), schedule)

@@ -135,13 +135,18 @@ def test_golden_8b_widths(golden_dir):
 
 
 @pytest.mark.parametrize(
-    "shape,prefill,partitions",
-    [("1b", 5, 1), ("1b", 300, 4), ("1b", 1000, 18), ("8b", 130, 3), ("8b", 700, 16), ("1b", 17, 6)],
+    "shape,prefill,partitions,merge",
+    [("1b", 5, 1, False), ("1b", 300, 4, False), ("1b", 1000, 18, False), ("8b", 130, 3, False),
+     ("8b", 700, 16, False), ("1b", 17, 6, False),
+     ("1b", 300, 4, True), ("1b", 1000, 18, True), ("8b", 130, 3, True), ("8b", 700, 16, True),
+     ("1b", 17, 6, True), ("8b", 1500, 24, True)],
 )
-def test_split_kv_attention_and_reduction(shape, prefill, partitions):
-    """Multi-partition schedules (partials + reduction) and empty partitions."""
+def test_split_kv_attention_and_reduction(shape, prefill, partitions, merge):
+    """Multi-partition schedules (partials + reduction instructions, or the last partial of a KV
+    head merging the rows) and empty partitions."""
     cfg = small_1b(num_hidden_layers=1) if shape == "1b" else small_8b(num_hidden_layers=1)
-    opts = LatencyScheduleOptions(num_attention_partitions=partitions, coalesce_o_proj=True)
+    opts = LatencyScheduleOptions(num_attention_partitions=partitions, coalesce_o_proj=True,
+                                  merge_in_last_partial=merge)
     cpu_model, cpu_sched, gpu_model, gpu_sched = make_pair(cfg, prefill + 8, prefill, options=opts)
     embed = cpu_model.model.embed_tokens.embed_tokens.weight
     # the multi-partition VM solvers are this repository's generalisation; the torch path

@@ -78,3 +78,31 @@ def test_two_level_reduction_tree_equals_full_attention():
     assert err <= 1e-2, err
     lse = g.attn_lse_intermediates[:, 6]
     assert bool(torch.isfinite(lse).all()) and not math.isnan(float(lse.sum()))
+
+
+@pytest.mark.parametrize("shape,partitions,prefill", [("1b", 4, 90), ("8b", 3, 70)])
+def test_merge_in_last_partial_equals_separate_reduction(shape, partitions, prefill):
+    """Schedules without AttentionReduction instructions (`merge_in_last_partial`: the partial of a
+    KV head that arrives last merges the rows) leave the same logits, bit for bit, as partials +
+    terminal reductions, and the same o-proj barrier count."""
+    from oracle.python_vm import PyVM_Interpreter
+
+    cfg = (LlamaConfig.llama_3_2_1b if shape == "1b" else LlamaConfig.llama_3_1_8b)(
+        num_hidden_layers=2, vocab_size=4096
+    )
+    logits = []
+    for merge in (False, True):
+        model = build_model(cfg, prefill + 4)
+        fill_kv(model, prefill, poison=True)
+        opts = LatencyScheduleOptions(num_attention_partitions=partitions, coalesce_o_proj=True,
+                                      merge_in_last_partial=merge)
+        sched = build_schedule(model, opts)
+        g = sched.globs
+        ops = [type(i).__name__ for i in sched.get_linear_instructions()]
+        assert ("AttentionReduction" in ops) != merge
+        g.hidden_states[:] = model.model.embed_tokens.embed_tokens.weight[11]
+        g.pos_id = prefill
+        PyVM_Interpreter().interpret(g, sched.get_linear_instructions())
+        assert int(g.barriers[:, 2, 0].sum()) == 2 * g.num_attention_heads
+        logits.append(g.logits.clone())
+    assert torch.equal(logits[0], logits[1])
