@@ -429,7 +429,15 @@ __device__ __forceinline__ void prefetch_l2_tile4(const CUtensorMap* map, int c0
                  : "memory");
 }
 
-__device__ void loader_main(Ctx c) {
+// The loader: one thread in each of `kLoaders` warps, each a complete copy of the loop below.
+// Every loader walks the whole stage sequence and copies the stages dealt to it round-robin
+// (stage % kLoaders == which); the L2 look-ahead is dealt the same way.  (The issue of a tiled
+// 32 KiB copy occupies its thread for about 0.5 us: one thread feeds the ring at no more than
+// 61 GB/s; two lanes of one warp would reconverge after every stage and issue one after the
+// other, hence separate warps.)
+__device__ __forceinline__ int loader_index(int warp) { return warp == kLoaderWarp ? 0 : warp - kStorerWarp; }
+
+__device__ void loader_main(Ctx c, const int which) {
     const KParams& p = *c.p;
     const uint64_t policy = l2_policy_evict_first();
     const int* queue = p.instructions + (size_t)blockIdx.x * p.queue_len * MKB_INTS_PER_INSTRUCTION;
@@ -438,7 +446,7 @@ __device__ void loader_main(Ctx c) {
     // Norm weights are tiny but sit on the critical path right after every barrier; a miss
     // to HBM under full streaming load costs microseconds.  Pin them in L2 up front: CTA b
     // takes rows b, b + gridDim.x, ... of the 2 L + 1 norm vectors.
-    {
+    if (which == 0) {
         uint64_t keep;
         asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
         for (int row = blockIdx.x; row < 2 * p.L + 1; row += gridDim.x) {
@@ -453,62 +461,66 @@ __device__ void loader_main(Ctx c) {
     StreamCursor issue, ahead;  // `ahead` is never behind `issue`
     issue.ctx = ahead.ctx = &c;
     StageDesc d, da;
-    uint32_t stage = 0;       // stages copied into the ring so far
+    uint32_t stage = 0;       // stages of the sequence walked so far (all loaders' stages)
     uint32_t ahead_stage = 0; // stages the look-ahead cursor has passed
+    uint32_t own_issued = 0;  // one past the last stage this loader copied into the ring
     bool ahead_more = true;
+    bool stop = false;
     int last_instr = -1;
     bool have = issue.next(p, queue, d);
-    while (have) {
+    while (have && !stop) {
         if (issue.i != last_instr) {
-            if (last_instr >= 0) rec(c, MKB_T_LOADER_DONE);
+            if (which == 0 && last_instr >= 0) rec(c, MKB_T_LOADER_DONE);
             last_instr = issue.i;
             c.instr = issue.i;
             c.opcode = issue.op;
-            rec(c, MKB_T_LOADER_START);
-            if (issue.i + 2 < p.queue_len) prefetch_l1(queue + (issue.i + 2) * MKB_INTS_PER_INSTRUCTION);
+            if (which == 0) {
+                rec(c, MKB_T_LOADER_START);
+                if (issue.i + 2 < p.queue_len) prefetch_l1(queue + (issue.i + 2) * MKB_INTS_PER_INSTRUCTION);
+            }
             if (*c.cta_abort) break;
         }
-        const int slot = stage % kNumStages;
-        const uint32_t parity = ((stage / kNumStages) & 1u) ^ 1u;
-        if (!mbar_try_wait(c.empty_bar(slot), parity)) {
-            // ring full: use the time to pull upcoming weights into L2, where the
-            // stalls of this SM's consumers cannot stop HBM from streaming
-            // while the consumers sit in a barrier wait the ring cannot drain, so the
-            // look-ahead may run deeper than in steady state
-            const int window = c.cta_abort[4] ? p.l2_stall_window_stages : p.l2_window_stages;
-            if (ahead_more && (int)(ahead_stage - stage) < window) {
-                if (ahead_stage < stage + kNumStages) {
-                    // skip what the ring already holds or is about to receive
+        if ((int)(stage % kLoaders) == which) {
+            const int slot = stage % kNumStages;
+            const uint32_t parity = ((stage / kNumStages) & 1u) ^ 1u;
+            while (!mbar_try_wait(c.empty_bar(slot), parity)) {
+                // ring full: use the time to pull upcoming weights into L2, where the
+                // stalls of this SM's consumers cannot stop HBM from streaming
+                // while the consumers sit in a barrier wait the ring cannot drain, so the
+                // look-ahead may run deeper than in steady state
+                const int window = c.cta_abort[4] ? p.l2_stall_window_stages : p.l2_window_stages;
+                if (ahead_more && (int)(ahead_stage - stage) < window) {
                     ahead_more = ahead.next(p, queue, da);
+                    // skip what the ring already holds or is about to receive, and the other loaders'
+                    // share.  Weights only: K/V tiles in the look-ahead measured no gain (batched and
+                    // 64k-context runs alike)
+                    if (ahead_more && ahead_stage >= stage + kNumStages &&
+                        (int)(ahead_stage % kLoaders) == which && da.map)
+                        prefetch_l2_tile4(da.map, 0, da.c1, da.c2, da.c3);
                     ++ahead_stage;
                     continue;
                 }
-                ahead_more = ahead.next(p, queue, da);
-                if (ahead_more) {
-                    ++ahead_stage;
-                    // weights only: K/V tiles in the look-ahead measured no gain (batched and
-                    // 64k-context runs alike), their stages are bound by the strided tile copy
-                    if (da.map) prefetch_l2_tile4(da.map, 0, da.c1, da.c2, da.c3);
-                }
-                continue;
+                if (!mbar_wait_slow(c, c.empty_bar(slot), parity, true)) stop = true;
+                break;
             }
-            if (!mbar_wait_slow(c, c.empty_bar(slot), parity, true)) break;
-        }
-        const uint32_t bar = c.full_bar(slot);
-        const uint32_t dst = c.stage_addr(slot);
-        mbar_expect_tx(bar, d.bytes);
-        if (d.map == nullptr) {
-            tma_tile5_g2s(dst, &p.k_map, 0, d.t, 0, d.kvh, d.lb, bar, policy);
-            tma_tile5_g2s(dst + kStageBytes / 2, &p.v_map, 0, d.t, 0, d.kvh, d.lb, bar, policy);
-        } else {
-            tma_tile4_g2s(dst, d.map, 0, d.c1, d.c2, d.c3, bar, policy);
+            if (stop) break;
+            const uint32_t bar = c.full_bar(slot);
+            const uint32_t dst = c.stage_addr(slot);
+            mbar_expect_tx(bar, d.bytes);
+            if (d.map == nullptr) {
+                tma_tile5_g2s(dst, &p.k_map, 0, d.t, 0, d.kvh, d.lb, bar, policy);
+                tma_tile5_g2s(dst + kStageBytes / 2, &p.v_map, 0, d.t, 0, d.kvh, d.lb, bar, policy);
+            } else {
+                tma_tile4_g2s(dst, d.map, 0, d.c1, d.c2, d.c3, bar, policy);
+            }
+            own_issued = stage + 1;
         }
         ++stage;
         have = issue.next(p, queue, d);
     }
-    if (last_instr >= 0) rec(c, MKB_T_LOADER_DONE);
-    // hand the number of issued stages to the exit path
-    reinterpret_cast<volatile int*>(c.cta_abort)[1] = (int)stage;
+    if (which == 0 && last_instr >= 0) rec(c, MKB_T_LOADER_DONE);
+    // hand the extent of this loader's copies to the exit path (spare words of the HotConsts block)
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(c.base + kSmemHot + 48 + 4 * which), "r"(own_issued) : "memory");
 }
 
 // --------------------------------------------------------------------------- //
@@ -878,8 +890,10 @@ static_assert(sizeof(HotConsts) <= 64, "");
 // 700 cycles each, eight or so in a row, 3 - 3.8 us per activation on the critical path of every
 // layer where the loads of the vector itself take 0.3.  Arguments are three scalars; constants
 // come from shared memory; the norm weights are fetched together with the vector.
+// `w0` (one-chunk path only): this thread's norm weights, fetched by the caller before its barrier wait.
 template <int CHUNKS>
-__device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w, int* read_done, int seq) {
+__device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w, int* read_done, int seq,
+                                                    const uint4 w0 = make_uint4(0, 0, 0, 0)) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -907,7 +921,8 @@ __device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w,
         uint4 a[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
-        wv[k] = ld_nc_v4(norm_w + (size_t)chs[k] * 8);
+        if constexpr (CHUNKS == 1) wv[k] = w0;
+        else wv[k] = ld_nc_v4(norm_w + (size_t)chs[k] * 8);
         unpack8(hv, x[k]);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -961,9 +976,17 @@ __device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w,
 __device__ __noinline__ void rms_activation_wide(const __nv_bfloat16* norm_w, int* read_done, int seq) {
     rms_activation_body<2>(norm_w, read_done, seq);
 }
-__device__ __forceinline__ void rms_activation_plain(int H, const __nv_bfloat16* norm_w, int* read_done, int seq) {
-    if (H <= 4096) rms_activation_body<1>(norm_w, read_done, seq);
+__device__ __forceinline__ void rms_activation_plain(int H, const __nv_bfloat16* norm_w, int* read_done, int seq,
+                                                     const uint4 w0) {
+    if (H <= 4096) rms_activation_body<1>(norm_w, read_done, seq, w0);
     else rms_activation_wide(norm_w, read_done, seq);
+}
+// The norm weights do not depend on the barrier: the one-chunk path fetches them before waiting
+// (the 48 KB an activation reads go through the SM's load pipe at 64 bytes per cycle; 8 KB less
+// after the barrier is 0.1 us less on the critical path).
+__device__ __forceinline__ uint4 rms_weights_early(int H, const __nv_bfloat16* norm_w) {
+    const int ch = own_chunk(threadIdx.x >> 5, threadIdx.x & 31, 0, H);
+    return (H <= 4096 && ch >= 0) ? ld_nc_v4(norm_w + (size_t)ch * 8) : make_uint4(0, 0, 0, 0);
 }
 
 // Out of line: the polling loops would otherwise be inlined three times into the consumer loop.
@@ -1010,8 +1033,9 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
         }
     }
     if (!tagged) {
+        const uint4 w0 = rms_weights_early(c.p->H, norm_w);
         if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
-        rms_activation_plain(c.p->H, norm_w, read_done, 0);
+        rms_activation_plain(c.p->H, norm_w, read_done, 0, w0);
     }
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->H);
@@ -1717,8 +1741,9 @@ __device__ bool consumer_rms_norm(const Ctx& c, ConsumerState& cs, const int* w)
     const int wait_layer = which == 0 ? layer - 1 : layer;
     const int wait_row = (which == 1 ? MKB_OP_O_PROJ_RESIDUAL : MKB_OP_DOWN_PROJ_RESIDUAL) - 1;
     const int thr = which == 1 ? p.thr_upgate_waits_oproj : p.thr_qkv_waits_down;
+    const uint4 w0 = rms_weights_early(p.H, norm_w);
     if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, thr, needed)) return false;
-    rms_activation_plain(p.H, norm_w, nullptr, seq);
+    rms_activation_plain(p.H, norm_w, nullptr, seq, w0);
     consumer_sync();  // every thread's part of the vector is written
     if (threadIdx.x == 0) red_release_gpu_add(bar_addr(p, layer, MKB_BARRIER_ROW_RMS_NORM, which), 1);
     return true;
@@ -2568,6 +2593,7 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
         hot->H = p.H;
         hot->inv_H = 1.f / (float)p.H;
         hot->eps = p.rms_eps;
+        for (int k = 0; k < 4; ++k) reinterpret_cast<int*>(gbase + kSmemHot + 48)[k] = 0;  // loaders' issued counts
         if constexpr (kBatch > 1)
             for (int s = 0; s < kBatch; ++s)
                 c.cta_abort[8 + s] = s >= p.batch ? 0 : p.pos_id_ptr ? __ldg(p.pos_id_ptr + s) : p.pos_ids[s & 7];
@@ -2604,10 +2630,10 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
 #endif
     if (warp < kConsumerWarps) {
         consumer_main<kTP>(c);
-    } else if (warp == kLoaderWarp) {
-        if ((threadIdx.x & 31) == 0) loader_main(c);
-    } else {
+    } else if (warp == kStorerWarp) {
         storer_main<kTP>(c);
+    } else {
+        if ((threadIdx.x & 31) == 0) loader_main(c, loader_index(warp));
     }
 #if MKB_BATCH > 8
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -2631,12 +2657,15 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
 #endif
 
     // No bulk copy may still be in flight when the CTA's shared memory goes away:
-    // wait (bounded) for every stage the loader issued most recently.
-    if (warp == kLoaderWarp && (threadIdx.x & 31) == 0) {
-        const uint32_t issued = (uint32_t)c.cta_abort[1];
+    // every loader waits (bounded) for the stages it issued most recently.
+    if (warp >= kLoaderWarp && warp != kStorerWarp && (threadIdx.x & 31) == 0) {
+        const uint32_t which = (uint32_t)loader_index(warp);
+        uint32_t issued;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(issued) : "r"(c.base + kSmemHot + 48 + 4 * which) : "memory");
         const uint32_t first = issued > (uint32_t)kNumStages ? issued - kNumStages : 0u;
         c.role = kRoleLoader;
         for (uint32_t s = first; s < issued; ++s) {
+            if (s % kLoaders != which) continue;
             const uint32_t bar = c.full_bar(s % kNumStages);
             const uint32_t parity = (s / kNumStages) & 1u;
             if (!mbar_try_wait(bar, parity)) mbar_wait_slow(c, bar, parity, false);

@@ -50,7 +50,12 @@ constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;  // 512
 constexpr int kLoaderWarp = kConsumerWarps;            // warp 16
 constexpr int kStorerWarp = kConsumerWarps + 1;        // warp 17
-constexpr int kBlockThreads = (kConsumerWarps + 2) * 32;  // 576
+// Loader warps (one issuing thread each): warp 16 and, if more than one, the warps after the storer.
+#ifndef MKB_LOADERS
+#define MKB_LOADERS 1
+#endif
+constexpr int kLoaders = MKB_LOADERS;
+constexpr int kBlockThreads = (kConsumerWarps + 1 + kLoaders) * 32;  // 576 with one loader
 
 constexpr int kStageBytes = 32768;  // one ring stage
 constexpr int kNumStages = kBatch == 1 ? 6 : 4;  // 192 (128) KiB of weights / KV in flight per SM
