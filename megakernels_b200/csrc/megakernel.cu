@@ -520,7 +520,7 @@ __device__ void loader_main(Ctx c, const int which) {
     }
     if (which == 0 && last_instr >= 0) rec(c, MKB_T_LOADER_DONE);
     // hand the extent of this loader's copies to the exit path (spare words of the HotConsts block)
-    asm volatile("st.shared.u32 [%0], %1;" ::"r"(c.base + kSmemHot + 48 + 4 * which), "r"(own_issued) : "memory");
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(c.base + kSmemHot + 56 + 4 * which), "r"(own_issued) : "memory");
 }
 
 // --------------------------------------------------------------------------- //
@@ -720,133 +720,9 @@ __device__ __forceinline__ void stage_activation(const Ctx& c, const __nv_bfloat
     __syncwarp();
 }
 
-// RMSNorm of the hidden state into shared memory (bf16).  Mirrors the
-// reference's arithmetic: fp32 statistics, bf16 round of x * rstd, then times
-// the bf16 weight, rounded to bf16 (python_vm.py:50-56).
-struct RmsPrefetch {
-    uint4 wv[2];
-    int chs[2];
-};
-// The norm weights do not depend on the barrier: fetch them before waiting.
-__device__ __forceinline__ void rms_prefetch(const Ctx& c, const __nv_bfloat16* norm_w, RmsPrefetch& pf) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        pf.chs[k] = own_chunk(warp, lane, k, c.p->H);
-        if (pf.chs[k] >= 0) pf.wv[k] = ld_nc_v4(norm_w + (size_t)pf.chs[k] * 8);
-    }
-}
-// LL: the residual stream is read from this rank's tagged buffer (tensor parallelism), each
-// thread polling its own chunks until they carry `tag`; returns false if the wait was abandoned.
-// Otherwise the residual stream is the token embedding in `hidden` plus, with ACC, the Q31.32
-// accumulators the row-split projections add into; `read_done` (may be null) is a counter
-// bumped once every thread's loads have completed, for producers that must not add to the
-// accumulators before this instruction has read them.
-// Batched build: `seq` selects the sequence whose residual stream is normalised, and the result
-// goes to the global `normed` buffer (one RMS_NORM instruction per sequence) instead of shared memory.
-template <bool LL, bool ACC>
-__device__ __forceinline__ bool rms_activation(const Ctx& c, const RmsPrefetch& pf, uint32_t tag = 0,
-                                               int layer = 0, int which = 0, int* read_done = nullptr,
-                                               int seq = 0) {
-    const KParams& p = *c.p;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const size_t seq_off = kBatch == 1 ? 0 : (size_t)seq * p.H;
-    float x[2][8];
-    float ss = 0.f;
-    bool ok = true;
-    if constexpr (LL) {
-        uint4 xv[2];
-        // 8 bf16 = four {bf16x2, tag} words = two 16-byte loads
-        const uint4* ll = reinterpret_cast<const uint4*>(p.tp_hidden_ll[p.tp_rank]);
-        TpPoll poll;
-        if (tid == 0) c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            if (pf.chs[k] < 0) continue;
-            uint4 a, b;
-            while (true) {
-                a = ld_volatile_v4(ll + (size_t)pf.chs[k] * 2);
-                b = ld_volatile_v4(ll + (size_t)pf.chs[k] * 2 + 1);
-                if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
-                if (!poll.tick(c, layer, 100 + which, pf.chs[k], (int)a.y)) {
-                    ok = false;
-                    break;
-                }
-            }
-            xv[k] = make_uint4(a.x, a.z, b.x, b.z);
-            unpack8(xv[k], x[k]);
-        }
-        if (tid == 0) {
-            c.cta_abort[4] = 0;
-            rec(c, MKB_T_CONSUMER_WAIT_DONE);
-        }
-    } else {
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            if (pf.chs[k] < 0) continue;
-            const uint4 hv = ld_cg_v4(p.hidden + seq_off + (size_t)pf.chs[k] * 8);
-            if constexpr (ACC) {
-                const long long* acc = p.residual_acc + seq_off + (size_t)pf.chs[k] * 8;
-                uint4 a[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
-                unpack8(hv, x[k]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    x[k][2 * i] += q32_to_float(a[i].x, a[i].y);
-                    x[k][2 * i + 1] += q32_to_float(a[i].z, a[i].w);
-                }
-            } else {
-                unpack8(hv, x[k]);
-            }
-        }
-    }
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        if (pf.chs[k] >= 0) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) ss = fmaf(x[k][e], x[k][e], ss);
-        }
-    }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    float* red = reinterpret_cast<float*>(__cvta_shared_to_generic(c.base + kSmemRed));
-    if (lane == 0) red[warp] = ss;
-    if (tid == 0) rec(c, MKB_T_RMS_LOADED);
-    if constexpr (LL) {
-        if (!consumer_all(ok)) return false;
-    } else {
-        consumer_sync();
-        // every thread's loads of the residual stream have returned (their values went into
-        // the sums above), so later writers may now be let in.  A relaxed add is enough: a
-        // load that has delivered its value cannot observe a store issued afterwards, and a
-        // releasing add would stall this thread (and with it warp 0 and the whole ring) on a fence.
-        if (tid == 0 && read_done != nullptr) atomicAdd(read_done, 1);
-    }
-    if (tid == 0) rec(c, MKB_T_RMS_SUMMED);
-    float tot = 0.f;
-#pragma unroll
-    for (int k = 0; k < kConsumerWarps; ++k) tot += red[k];
-    const float rstd = rsqrtf(tot / (float)p.H + p.rms_eps);
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        if (pf.chs[k] >= 0) {
-            float wgt[8];
-            unpack8(pf.wv[k], wgt);
-            uint32_t o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                o[e] = pack_bf16x2(wgt[2 * e] * bf16_round(x[k][2 * e] * rstd),
-                                   wgt[2 * e + 1] * bf16_round(x[k][2 * e + 1] * rstd));
-            if constexpr (kBatch == 1)
-                st_shared_v4(c.base + kSmemAttn + pf.chs[k] * 16, o[0], o[1], o[2], o[3]);
-            else
-                *reinterpret_cast<uint4*>(p.normed + seq_off + (size_t)pf.chs[k] * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-    }
-    __syncwarp();
-    return true;
-}
+// RMSNorm of the residual stream into shared memory (bf16).  Mirrors the reference's
+// arithmetic: fp32 statistics, bf16 round of x * rstd, then times the bf16 weight, rounded to bf16
+// (python_vm.py:50-56).  The code is rms_activation_body further down.
 
 // Consumer thread 0 waits for a counter; the verdict reaches all 512 consumer
 // threads through shared memory so that they leave the instruction together.
@@ -868,42 +744,53 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
     return *verdict != 0;
 }
 
-// What rms_activation_plain needs, in shared memory (written once by thread 0 at kernel start;
+// What rms_activation_body needs, in shared memory (written once by thread 0 at kernel start;
 // `trow` = the timing row of the consumers' current instruction, or null, by consumer thread 0).
 struct HotConsts {
     const __nv_bfloat16* hidden;
     const long long* acc;
     __nv_bfloat16* normed;
     int* trow;
+    const uint4* ll;  // tensor parallelism: this rank's tagged residual stream
     int H;
     float inv_H;
     float eps;
     int pad;
 };
-static_assert(sizeof(HotConsts) <= 64, "");
+static_assert(sizeof(HotConsts) == 56, "two loader words follow at byte 56");
 
-// RMSNorm of `hidden + acc * 2^-32` (see rms_activation for the arithmetic) for the single-GPU
-// and batched builds.  Out of line (inlined copies made the compiler spill state of the whole
-// consumer loop), and written so that nothing comes through the stack: a function that receives
-// the context by reference reads it back from local memory, and with 220 KB of the SM's 256 KB
-// given to shared memory those loads miss L1 three times out of four - measured here as 600 -
-// 700 cycles each, eight or so in a row, 3 - 3.8 us per activation on the critical path of every
-// layer where the loads of the vector itself take 0.3.  Arguments are three scalars; constants
-// come from shared memory; the norm weights are fetched together with the vector.
-// `w0` (one-chunk path only): this thread's norm weights, fetched by the caller before its barrier wait.
-template <int CHUNKS>
-__device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w, int* read_done, int seq,
-                                                    const uint4 w0 = make_uint4(0, 0, 0, 0)) {
+// The residual stream of an RMSNorm comes from one of three places:
+//   kRmsAcc    `hidden` (the token embedding) + the Q31.32 accumulators the row-split projections
+//              add into (single-GPU and batched builds); `read_done` (may be null) is a counter
+//              bumped once every thread's loads have returned, for producers that must not add to
+//              the accumulators before this instruction has read them;
+//   kRmsHidden `hidden` alone (tensor parallelism: the embedding, before the first all-reduce);
+//   kRmsTagged this rank's tagged buffer (tensor parallelism): every thread polls its own chunks
+//              until they carry `tag`; returns false if the wait was abandoned.
+// Batched build: `seq` selects the sequence, and the result goes to the global `normed` buffer
+// (one RMS_NORM instruction per sequence) instead of shared memory.
+//
+// Nothing on the hot path comes through the stack: a function that receives the context by
+// reference reads it back from local memory, and with 220 KB of the SM's 256 KB given to shared
+// memory those loads miss L1 three times out of four - measured as 600 - 700 cycles each, eight
+// or so in a row, 3 - 3.8 us per activation on the critical path of every layer where the loads
+// of the vector itself take 0.3.  Constants come from shared memory (HotConsts); `c` is only
+// touched when a tagged poll runs out of time.
+enum RmsSource { kRmsAcc = 0, kRmsHidden = 1, kRmsTagged = 2 };
+template <int CHUNKS, int SRC>
+__device__ __forceinline__ bool rms_activation_body(const Ctx& c, const __nv_bfloat16* norm_w, int* read_done,
+                                                    int seq, const uint4 w0, uint32_t tag, int layer, int which) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint4 h0 = lds_v4(base + kSmemHot), h1 = lds_v4(base + kSmemHot + 16), h2 = lds_v4(base + kSmemHot + 32);
     const __nv_bfloat16* hidden = reinterpret_cast<const __nv_bfloat16*>(((unsigned long long)h0.y << 32) | h0.x);
     const long long* accp = reinterpret_cast<const long long*>(((unsigned long long)h0.w << 32) | h0.z);
-    __nv_bfloat16* normed = reinterpret_cast<__nv_bfloat16*>(((unsigned long long)h1.y << 32) | h1.x);
+    [[maybe_unused]] __nv_bfloat16* normed = reinterpret_cast<__nv_bfloat16*>(((unsigned long long)h1.y << 32) | h1.x);
     int* trow = reinterpret_cast<int*>(((unsigned long long)h1.w << 32) | h1.z);
-    const int H = (int)h2.x;
-    const float inv_H = __uint_as_float(h2.y), eps = __uint_as_float(h2.z);
+    const uint4* ll = reinterpret_cast<const uint4*>(((unsigned long long)h2.y << 32) | h2.x);
+    const int H = (int)h2.z;
+    const float inv_H = __uint_as_float(h2.w), eps = __uint_as_float(lds_u32(base + kSmemHot + 48));
     const size_t seq_off = kBatch == 1 ? 0 : (size_t)seq * H;
 
     // one chunk of 8 elements per thread up to H = 4096, a second one (loaded after the first has
@@ -912,36 +799,71 @@ __device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w,
     uint4 wv[CHUNKS];
     float x[CHUNKS][8];
     float ss = 0.f;
+    bool ok = true;
+    if constexpr (SRC == kRmsTagged) {
+        // tells the loader that the ring is not being drained (control word 4)
+        if (tid == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(base + kSmemCtl + 16), "r"(1) : "memory");
+    }
 #pragma unroll
     for (int k = 0; k < CHUNKS; ++k) {
         chs[k] = own_chunk(warp, lane, k, H);
         if (chs[k] < 0) continue;
-        const uint4 hv = ld_cg_v4(hidden + seq_off + (size_t)chs[k] * 8);
-        const long long* acc = accp + seq_off + (size_t)chs[k] * 8;
-        uint4 a[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
         if constexpr (CHUNKS == 1) wv[k] = w0;
         else wv[k] = ld_nc_v4(norm_w + (size_t)chs[k] * 8);
-        unpack8(hv, x[k]);
+        if constexpr (SRC == kRmsTagged) {
+            // 8 bf16 = four {bf16x2, tag} words = two 16-byte loads
+            TpPoll poll;
+            uint4 a, b;
+            while (true) {
+                a = ld_volatile_v4(ll + (size_t)chs[k] * 2);
+                b = ld_volatile_v4(ll + (size_t)chs[k] * 2 + 1);
+                if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+                if (!poll.tick(c, layer, 100 + which, chs[k], (int)a.y)) {
+                    ok = false;
+                    break;
+                }
+            }
+            unpack8(make_uint4(a.x, a.z, b.x, b.z), x[k]);
+        } else {
+            const uint4 hv = ld_cg_v4(hidden + seq_off + (size_t)chs[k] * 8);
+            if constexpr (SRC == kRmsAcc) {
+                const long long* acc = accp + seq_off + (size_t)chs[k] * 8;
+                uint4 a[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            x[k][2 * i] += q32_to_float(a[i].x, a[i].y);
-            x[k][2 * i + 1] += q32_to_float(a[i].z, a[i].w);
+                for (int i = 0; i < 4; ++i) a[i] = ld_cg_v4(acc + 2 * i);
+                unpack8(hv, x[k]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    x[k][2 * i] += q32_to_float(a[i].x, a[i].y);
+                    x[k][2 * i + 1] += q32_to_float(a[i].z, a[i].w);
+                }
+            } else {
+                unpack8(hv, x[k]);
+            }
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(x[k][e], x[k][e], ss);
+    }
+    if constexpr (SRC == kRmsTagged) {
+        if (tid == 0) {
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(base + kSmemCtl + 16), "r"(0) : "memory");
+            if (trow != nullptr) trow[MKB_T_CONSUMER_WAIT_DONE] = (int)(uint32_t)globaltimer_ns();
+        }
     }
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (lane == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(base + kSmemRed + warp * 4), "f"(ss) : "memory");
     if (tid == 0 && trow != nullptr) trow[MKB_T_RMS_LOADED] = (int)(uint32_t)globaltimer_ns();
-    consumer_sync();
-    // every thread's loads of the residual stream have returned (their values went into
-    // the sums above), so later writers may now be let in.  A relaxed add is enough: a
-    // load that has delivered its value cannot observe a store issued afterwards, and a
-    // releasing add would stall this thread (and with it warp 0 and the whole ring) on a fence.
-    if (tid == 0 && read_done != nullptr) atomicAdd(read_done, 1);
+    if constexpr (SRC == kRmsTagged) {
+        if (!consumer_all(ok)) return false;
+    } else {
+        consumer_sync();
+        // every thread's loads of the residual stream have returned (their values went into
+        // the sums above), so later writers may now be let in.  A relaxed add is enough: a
+        // load that has delivered its value cannot observe a store issued afterwards, and a
+        // releasing add would stall this thread (and with it warp 0 and the whole ring) on a fence.
+        if (tid == 0 && read_done != nullptr) atomicAdd(read_done, 1);
+    }
     if (tid == 0 && trow != nullptr) trow[MKB_T_RMS_SUMMED] = (int)(uint32_t)globaltimer_ns();
     float tot = 0.f;
 #pragma unroll
@@ -967,19 +889,24 @@ __device__ __forceinline__ void rms_activation_body(const __nv_bfloat16* norm_w,
         }
     }
     __syncwarp();
+    return true;
 }
 
 // Up to 4096 elements a thread holds one chunk and the code is light enough to be inlined (an
 // out-of-line copy pays for its callee-saved registers with 2 x 48 KB of local-memory traffic per
-// call, over a microsecond); wider models (two chunks per thread) take the out-of-line copy, whose
+// call, over a microsecond); wider models (two chunks per thread) take an out-of-line copy, whose
 // inlining would make the compiler spill state of the whole consumer loop.
-__device__ __noinline__ void rms_activation_wide(const __nv_bfloat16* norm_w, int* read_done, int seq) {
-    rms_activation_body<2>(norm_w, read_done, seq);
+template <int SRC>
+__device__ __noinline__ bool rms_activation_wide(const Ctx& c, const __nv_bfloat16* norm_w, int* read_done, int seq,
+                                                 uint32_t tag, int layer, int which) {
+    return rms_activation_body<2, SRC>(c, norm_w, read_done, seq, make_uint4(0, 0, 0, 0), tag, layer, which);
 }
-__device__ __forceinline__ void rms_activation_plain(int H, const __nv_bfloat16* norm_w, int* read_done, int seq,
-                                                     const uint4 w0) {
-    if (H <= 4096) rms_activation_body<1>(norm_w, read_done, seq, w0);
-    else rms_activation_wide(norm_w, read_done, seq);
+template <int SRC>
+__device__ __forceinline__ bool rms_activation_from(const Ctx& c, int H, const __nv_bfloat16* norm_w, const uint4 w0,
+                                                    int* read_done = nullptr, int seq = 0, uint32_t tag = 0,
+                                                    int layer = 0, int which = 0) {
+    if (H <= 4096) return rms_activation_body<1, SRC>(c, norm_w, read_done, seq, w0, tag, layer, which);
+    return rms_activation_wide<SRC>(c, norm_w, read_done, seq, tag, layer, which);
 }
 // The norm weights do not depend on the barrier: the one-chunk path fetches them before waiting
 // (the 48 KB an activation reads go through the SM's load pipe at 64 bytes per cycle; 8 KB less
@@ -988,13 +915,6 @@ __device__ __forceinline__ uint4 rms_weights_early(int H, const __nv_bfloat16* n
     const int ch = own_chunk(threadIdx.x >> 5, threadIdx.x & 31, 0, H);
     return (H <= 4096 && ch >= 0) ? ld_nc_v4(norm_w + (size_t)ch * 8) : make_uint4(0, 0, 0, 0);
 }
-
-// Out of line: the polling loops would otherwise be inlined three times into the consumer loop.
-__device__ __noinline__ bool rms_activation_tagged(const Ctx& c, const RmsPrefetch pf, int wait_layer,
-                                                   int which) {
-    return rms_activation<true, false>(c, pf, tp_tag(c, wait_layer, which), wait_layer, which);
-}
-
 
 // kTP selects the tensor-parallel build of the kernel.  It is a compile-time switch and the two
 // builds are separate kernels: merely having the exchange code in the same kernel cost the
@@ -1015,27 +935,28 @@ __device__ __forceinline__ bool consumer_rms_matvec(const Ctx& c, ConsumerState&
         consume_blocks(c, cs, nblocks, c.p->H);
         return true;
     }
+    const int H = c.p->H;
+    const uint4 w0 = rms_weights_early(H, norm_w);
     bool tagged = false;
     if constexpr (kTP) {
-        // the residual stream arrives as tagged values from the chunk owners
         if (c.p->tp_size > 1) {
-            RmsPrefetch pf;
-            rms_prefetch(c, norm_w, pf);
             if (needed) {
+                // the residual stream arrives as tagged values from the chunk owners
                 const int which = wait_row == MKB_OP_O_PROJ_RESIDUAL - 1 ? 0 : 1;
-                if (!rms_activation_tagged(c, pf, wait_layer, which)) return false;
+                if (!rms_activation_from<kRmsTagged>(c, H, norm_w, w0, nullptr, 0, tp_tag(c, wait_layer, which),
+                                                     wait_layer, which))
+                    return false;
             } else {
                 // the tensor-parallel exchange keeps the running residual stream in its tagged
                 // buffer; the only plain read there is the token embedding before the first all-reduce
-                rms_activation<false, false>(c, pf);
+                rms_activation_from<kRmsHidden>(c, H, norm_w, w0);
             }
             tagged = true;
         }
     }
     if (!tagged) {
-        const uint4 w0 = rms_weights_early(c.p->H, norm_w);
         if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, threshold, needed)) return false;
-        rms_activation_plain(c.p->H, norm_w, read_done, 0, w0);
+        rms_activation_from<kRmsAcc>(c, H, norm_w, w0, read_done);
     }
     if (threadIdx.x == 0) rec(c, MKB_T_CONSUMER_ACT_READY);
     consume_blocks(c, cs, nblocks, c.p->H);
@@ -1743,7 +1664,7 @@ __device__ bool consumer_rms_norm(const Ctx& c, ConsumerState& cs, const int* w)
     const int thr = which == 1 ? p.thr_upgate_waits_oproj : p.thr_qkv_waits_down;
     const uint4 w0 = rms_weights_early(p.H, norm_w);
     if (!consumers_wait_counter(c, cs, wait_layer, wait_row, 0, thr, needed)) return false;
-    rms_activation_plain(p.H, norm_w, nullptr, seq, w0);
+    rms_activation_from<kRmsAcc>(c, p.H, norm_w, w0, nullptr, seq);
     consumer_sync();  // every thread's part of the vector is written
     if (threadIdx.x == 0) red_release_gpu_add(bar_addr(p, layer, MKB_BARRIER_ROW_RMS_NORM, which), 1);
     return true;
@@ -2056,7 +1977,7 @@ __device__ void consumer_main(Ctx c) {
         bool ok = true;
         if (threadIdx.x == 0 && op != MKB_OP_NOOP) {
             rec(c, MKB_T_CONSUMER_START);
-            if (p.timings != nullptr) {  // where rms_activation_plain stamps its phases
+            if (p.timings != nullptr) {  // where rms_activation_body stamps its phases
                 int* trow = p.timings + ((size_t)blockIdx.x * p.queue_len + i) * MKB_TIMING_SLOTS;
                 asm volatile("st.shared.u64 [%0], %1;" ::"r"(c.base + kSmemHot + 24), "l"(trow) : "memory");
             }
@@ -2593,7 +2514,8 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
         hot->H = p.H;
         hot->inv_H = 1.f / (float)p.H;
         hot->eps = p.rms_eps;
-        for (int k = 0; k < 4; ++k) reinterpret_cast<int*>(gbase + kSmemHot + 48)[k] = 0;  // loaders' issued counts
+        hot->ll = reinterpret_cast<const uint4*>(p.tp_size > 1 ? p.tp_hidden_ll[p.tp_rank] : nullptr);
+        for (int k = 0; k < 2; ++k) reinterpret_cast<int*>(gbase + kSmemHot + 56)[k] = 0;  // loaders' issued counts
         if constexpr (kBatch > 1)
             for (int s = 0; s < kBatch; ++s)
                 c.cta_abort[8 + s] = s >= p.batch ? 0 : p.pos_id_ptr ? __ldg(p.pos_id_ptr + s) : p.pos_ids[s & 7];
@@ -2661,7 +2583,7 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
     if (warp >= kLoaderWarp && warp != kStorerWarp && (threadIdx.x & 31) == 0) {
         const uint32_t which = (uint32_t)loader_index(warp);
         uint32_t issued;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(issued) : "r"(c.base + kSmemHot + 48 + 4 * which) : "memory");
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(issued) : "r"(c.base + kSmemHot + 56 + 4 * which) : "memory");
         const uint32_t first = issued > (uint32_t)kNumStages ? issued - kNumStages : 0u;
         c.role = kRoleLoader;
         for (uint32_t s = first; s < issued; ++s) {
