@@ -146,8 +146,10 @@ __device__ __forceinline__ bool warp_mbar_wait(const Ctx& c, uint32_t bar, uint3
 }
 
 // Bounded wait for `*addr >= threshold` with acquire semantics.
+// (`sleep_ns` travels in a register: the loop must not reach through `c`, which lives in local
+// memory, on every poll - that is an L1 miss of 600 cycles between two polls.)
 __device__ __noinline__ bool wait_counter(const Ctx& c, const int* addr, int threshold, int layer,
-                                          int row, int slot) {
+                                          int row, int slot, unsigned sleep_ns) {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
@@ -167,14 +169,14 @@ __device__ __noinline__ bool wait_counter(const Ctx& c, const int* addr, int thr
                 return false;
             }
         }
-        __nanosleep(c.p->poll_sleep_ns);
+        __nanosleep(sleep_ns);
     }
 }
 
 // Warp-collective bounded wait on up to 32 counters at once: lane i polls addr (nullptr =
 // nothing to wait for).  Sequential waits would cost one L2 round trip per counter.
 __device__ __noinline__ bool warp_wait_counters(const Ctx& c, const int* addr, int threshold,
-                                                int layer, int row, int slot) {
+                                                int layer, int row, int slot, unsigned sleep_ns) {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
@@ -201,7 +203,7 @@ __device__ __noinline__ bool warp_wait_counters(const Ctx& c, const int* addr, i
             }
             if (stop) return false;
         }
-        __nanosleep(c.p->poll_sleep_ns);
+        __nanosleep(sleep_ns);
     }
 }
 
@@ -734,7 +736,7 @@ __device__ __forceinline__ bool consumers_wait_counter(const Ctx& c, ConsumerSta
         bool ok = !*c.cta_abort;
         if (ok && needed) {
             c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
-            ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot);
+            ok = wait_counter(c, bar_addr(*c.p, layer, row, slot), threshold, layer, row, slot, (unsigned)c.p->poll_sleep_ns);
             c.cta_abort[4] = 0;
         }
         rec(c, MKB_T_CONSUMER_WAIT_DONE);
@@ -972,7 +974,7 @@ __device__ __forceinline__ bool consumers_wait_lanes(const Ctx& c, ConsumerState
         const int lane = threadIdx.x;
         bool ok = __shfl_sync(0xffffffffu, *c.cta_abort, 0) == 0;  // uniform over the warp
         if (lane == 0) c.cta_abort[4] = 1;  // tells the loader that the ring is not being drained
-        ok = ok && warp_wait_counters(c, addr, threshold, layer, row, slot);
+        ok = ok && warp_wait_counters(c, addr, threshold, layer, row, slot, (unsigned)c.p->poll_sleep_ns);
         if (lane == 0) {
             c.cta_abort[4] = 0;
             rec(c, MKB_T_CONSUMER_WAIT_DONE);
@@ -1168,7 +1170,7 @@ __device__ bool consumer_attention(const Ctx& c, ConsumerState& cs, const int* w
             else if (lane == GQA + 1) slot = p.Hq + p.Hkv + kvh;
             bool ok = __shfl_sync(0xffffffffu, *c.cta_abort, 0) == 0;  // uniform over the warp
             ok = ok && warp_wait_counters(c, slot >= 0 ? bar_addr(p, layer, row, slot) : nullptr,
-                                          p.thr_attn_waits_qkv, layer, row, slot);
+                                          p.thr_attn_waits_qkv, layer, row, slot, (unsigned)p.poll_sleep_ns);
             if (lane == 0) {
                 rec(c, MKB_T_CONSUMER_WAIT_DONE);
                 *verdict = ok ? 1 : 0;
@@ -1447,7 +1449,7 @@ __device__ bool consumer_attn_reduction(const Ctx& c, ConsumerState& cs, const i
         const int row = MKB_OP_PARTIAL_ATTENTION - 1;
         bool ok = __shfl_sync(0xffffffffu, *c.cta_abort, 0) == 0;  // uniform over the warp
         ok = ok && warp_wait_counters(c, lane < 4 ? bar_addr(p, layer, row, part_slot0 + h0 + lane) : nullptr,
-                                      num_partials, layer, row, h0 + lane);
+                                      num_partials, layer, row, h0 + lane, (unsigned)p.poll_sleep_ns);
         if (lane == 0) {
             rec(c, MKB_T_CONSUMER_WAIT_DONE);
             *verdict = ok ? 1 : 0;
@@ -1766,7 +1768,7 @@ __device__ void xloader_main(Ctx c) {
         if (*c.cta_abort) break;
         c.cta_abort[4] = 1;  // the weight loader may look further ahead while this instruction waits
         const bool ok = wait_counter(c, bar_addr(p, g.wait_layer, g.wait_row, g.wait_slot), g.wait_thr,
-                                     g.wait_layer, g.wait_row, g.wait_slot);
+                                     g.wait_layer, g.wait_row, g.wait_slot, (unsigned)p.poll_sleep_ns);
         c.cta_abort[4] = 0;
         if (!ok) break;
         // the activations were written with ordinary stores by other SMs and are read here by
