@@ -406,8 +406,8 @@ def make_batched_dag(globs: Globals, options: LatencyScheduleOptions, layer_limi
         for b in range(B):
             for kv in range(globs.num_kv_heads):
                 parts = emit([PartialAttention(layer, kv, n_part, p, b) for p in range(n_part)], qkv)
-                if globs.skip_attn_reduction:
-                    attn_out.extend(parts)
+                if globs.skip_attn_reduction or globs.merge_in_last_partial:
+                    attn_out.extend(parts)  # (the last partial to arrive merges the rows)
                     continue
                 for h0 in range(kv * gqa, (kv + 1) * gqa, globs.attn_reduction_size):
                     attn_out.extend(

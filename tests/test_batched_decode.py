@@ -87,12 +87,14 @@ def test_batched_schedule_covers_every_sequence(batch, parts):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize(
-    "shape,batch,parts",
+    "shape,batch,parts,merge",
     # up to 8 sequences: mma.sync with the sequences as B-operand columns; more: tcgen05 GEMMs
-    # (128-row blocks, head_dim 128 only), incl. a batch that is not a multiple of the MMA's N step
-    [("8b", 4, 3), ("8b", 8, 1), ("1b", 5, 2), ("1b", 2, 4), ("8b", 16, 1), ("8b", 40, 2), ("8b", 64, 1)],
+    # (128-row blocks, head_dim 128 only), incl. a batch that is not a multiple of the MMA's N step;
+    # merge: no reduction instructions, the last partial of a (sequence, KV head) merges the rows
+    [("8b", 4, 3, False), ("8b", 8, 1, False), ("1b", 5, 2, False), ("1b", 2, 4, False), ("8b", 16, 1, False),
+     ("8b", 40, 2, False), ("8b", 64, 1, False), ("8b", 4, 3, True), ("1b", 5, 2, True), ("8b", 40, 2, True)],
 )
-def test_batched_decode_matches_independent_sequences(shape, batch, parts):
+def test_batched_decode_matches_independent_sequences(shape, batch, parts, merge):
     from megakernels_b200.generators import MK_Generator
     from oracle.llama_ref import TorchReferenceModel, assert_logits_parity
     from tests.gpu_utils import interpreter
@@ -111,10 +113,12 @@ def test_batched_decode_matches_independent_sequences(shape, batch, parts):
     # one copy of the weights on the host, one KV cache per sequence swapped in for its run
     ref = TorchReferenceModel(model, kv_len=max_len)
     caches = [tuple(c[:, b : b + 1].cpu().clone() for c in model.stacked_kv_cache) for b in range(batch)]
-    opts = LatencyScheduleOptions(num_attention_partitions=parts, coalesce_o_proj=True, batch_size=batch)
+    opts = LatencyScheduleOptions(num_attention_partitions=parts, coalesce_o_proj=True, batch_size=batch,
+                                  merge_in_last_partial=merge)
     schedule = LatencyScheduleBuilder(opts).build(model)
     tensorize_instructions(schedule.globs, assign_to_sms("rr", schedule=schedule))
     g = schedule.globs
+    assert any(isinstance(i, AttentionReduction) for i in schedule.get_linear_instructions()) == (parts > 1 and not merge)
     mk = MK_Generator(model, interpreter(), schedule)
     ids = torch.randint(0, cfg.vocab_size, (3, batch), generator=torch.Generator().manual_seed(3))
     for step in range(3):
