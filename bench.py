@@ -49,7 +49,7 @@ FALLBACK_HBM_GBS = 6650.0  # used when no measured copy bandwidth is on file (ME
 # DRAM traffic of one megakernel launch relative to its algorithmic bytes, from an ncu capture
 # of a 4-layer case (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes);
 # traffic grows in proportion to the layers streamed, so the full launch is scaled by the ratio.
-NCU_TRAFFIC_RATIO = (2.8373e9 + 0.0202e9) / 2.8124e9
+NCU_TRAFFIC_RATIO = (2.8239e9 + 0.0368e9) / 2.8124e9
 
 WORKLOADS = {
     # tp: shard the model over the ranks when N > 1 (False: replicas only)
