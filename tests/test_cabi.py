@@ -128,3 +128,47 @@ def test_host_validation_of_all_reduce_instructions():
     g.tp.num_chunks = 3  # not a multiple of the group size
     rc, msg = check()
     assert rc == 1 and "num_chunks" in msg
+
+
+def test_host_validation_of_attention_reduction_modes():
+    """skip_attn_reduction: 0 / 1 / 2 are the only values; mode 2 (the last partial merges) has no
+    AttentionReduction instructions; mode 1 has exactly one partition (pure host code)."""
+    import sys
+
+    import torch
+
+    sys.path.insert(0, str(ROOT / "megakernels_b200" / "native"))
+    import mk_llama
+
+    lib = mk_llama.load_library()
+    lib.mkb_validate_instructions.argtypes = [ctypes.POINTER(mk_llama.MkbGlobals), ctypes.c_void_p]
+    lib.mkb_validate_instructions.restype = ctypes.c_int
+    g = mk_llama.MkbGlobals()
+    g.abi_version = mk_llama.MKB_ABI_VERSION
+    g.struct_bytes = ctypes.sizeof(mk_llama.MkbGlobals)
+    fake = 0x10000
+    for name, ctype in mk_llama.MkbGlobals._fields_:
+        if ctype is ctypes.c_void_p and name not in ("timings", "status", "pos_id_device", "argmax_out"):
+            setattr(g, name, fake)
+    g.num_sms, g.queue_len, g.barrier_ops, g.barrier_width = 1, 2, 10, 48
+    g.num_layers, g.hidden_size, g.intermediate_size, g.head_dim = 2, 2048, 8192, 64
+    g.num_attention_heads, g.num_kv_heads, g.vocab_size = 32, 8, 128256
+    g.kv_max_len, g.kv_batch, g.max_partials, g.matvec_reduction_size = 128, 1, 4, 2048
+    ins = torch.zeros(1, 2, 32, dtype=torch.int32)
+    ins[0, 0, :6] = torch.tensor([2, 0, 1, 3, 2, 0])  # partial 2 of 3, KV head 1
+    ins[0, 1, :9] = torch.tensor([3, 0, 4, 3, 1, 3, 0, 1, 2])  # terminal reduction of heads 4..7
+
+    def check(mode):
+        g.skip_attn_reduction = mode
+        rc = lib.mkb_validate_instructions(ctypes.byref(g), ctypes.c_void_p(ins.data_ptr()))
+        return rc, lib.mkb_last_error().decode()
+
+    assert check(0)[0] == 0
+    rc, msg = check(1)
+    assert rc == 1 and "num_partials == 1" in msg
+    rc, msg = check(2)
+    assert rc == 1 and "AttentionReduction instruction" in msg
+    rc, msg = check(3)
+    assert rc == 1 and "0, 1 or 2" in msg
+    ins[0, 1].zero_()  # without the reduction instruction mode 2 is a valid stream
+    assert check(2)[0] == 0
