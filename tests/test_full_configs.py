@@ -147,15 +147,17 @@ def test_longest_reduction_list():
     assert_logits_parity(schedule.globs.logits, ref.decode_token(tok, length), "24 partitions")
 
 
-@pytest.mark.parametrize("shape", ["8b", "70b"])
-def test_identical_runs_give_identical_bits(shape):
+@pytest.mark.parametrize("shape,merge", [("8b", False), ("70b", False), ("8b", True), ("70b", True)])
+def test_identical_runs_give_identical_bits(shape, merge):
     """The residual stream is summed with integer atomics, so nothing depends on the order in
-    which SMs arrive: 50 repetitions of one step must agree bit for bit (flip rate 0)."""
+    which SMs arrive: 50 repetitions of one step must agree bit for bit (flip rate 0).  With
+    `merge_in_last_partial` WHICH partial merges a KV head's rows changes from run to run; the merge
+    itself always walks the rows in index order, so the bits must not."""
     if shape == "8b":
         cfg = LlamaConfig.llama_3_1_8b(num_hidden_layers=2, vocab_size=4096)
     else:
         cfg = LlamaConfig.llama_3_1_70b(num_hidden_layers=1, vocab_size=4096)
-    opts = LatencyScheduleOptions(num_attention_partitions=3, coalesce_o_proj=True)
+    opts = LatencyScheduleOptions(num_attention_partitions=3, coalesce_o_proj=True, merge_in_last_partial=merge)
     cpu_model, _, _, gpu_sched = make_pair(cfg, 300, 280, options=opts, sched="wave")
     g = gpu_sched.globs
     hidden = cpu_model.model.embed_tokens.embed_tokens.weight[77]
