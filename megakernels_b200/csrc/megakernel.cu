@@ -1697,7 +1697,7 @@ __device__ bool consumer_residual_op(const Ctx& c, ConsumerState& cs, int op, co
 // A = the weight tile of a ring stage (128 rows x 128 columns, K-major, 128-byte swizzle, as the
 // tiled TMA copy leaves it), B = the activation slice of the same columns ([sequences] x 128,
 // K-major, same swizzle), D = 128 lanes x N fp32 columns in tensor memory (N = batch rounded up
-// to 16).  One thread issues the MMAs; four warps read finished accumulators back and apply the
+// to 16).  One thread issues the MMAs; twelve warps read finished accumulators back and apply the
 // epilogue; a second loader thread streams the activation slices once their producer is done.
 struct GemmOp {
     int op, layer, nblocks, kc;   // blocks of this instruction (up/gate: 2 per listed block), input columns
@@ -1771,6 +1771,7 @@ __device__ void xloader_main(Ctx c) {
                                      g.wait_layer, g.wait_row, g.wait_slot, (unsigned)p.poll_sleep_ns);
         c.cta_abort[4] = 0;
         if (!ok) break;
+        rec(c, MKB_T_CONSUMER_WAIT_DONE);
         // the activations were written with ordinary stores by other SMs and are read here by
         // the TMA engine: order the two proxies after the acquiring poll
         asm volatile("fence.proxy.async.global;" ::: "memory");
@@ -1814,7 +1815,7 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j]);
 }
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 384;" ::: "memory"); }  // warps 4..15
 __device__ __forceinline__ bool gemm_wait(const Ctx& c, ConsumerState& cs, uint32_t bar, uint32_t parity) {
     if (!cs.dead && !mbar_try_wait(bar, parity)) {
         if (!mbar_wait_slow(c, bar, parity, true)) cs.dead = true;
@@ -1822,9 +1823,9 @@ __device__ __forceinline__ bool gemm_wait(const Ctx& c, ConsumerState& cs, uint3
     return !cs.dead;
 }
 
-// One GEMM instruction.  Consumer warp 0 (one lane) issues the MMAs, warps 4..7 are the
-// epilogue (tensor-memory lane quarter = warp % 4, thread = weight row), the others only keep
-// their ring bookkeeping in step.
+// One GEMM instruction.  Consumer warp 0 (one lane) issues the MMAs, warps 4..15 are the
+// epilogue (tensor-memory lane quarter = warp % 4, thread = weight row; the three groups of four
+// warps split the sequences), the others only keep their ring bookkeeping in step.
 __device__ bool gemm_instruction(const Ctx& c, ConsumerState& cs, const int* w) {
     const KParams& p = *c.p;
     GemmOp g;
@@ -1846,6 +1847,7 @@ __device__ bool gemm_instruction(const Ctx& c, ConsumerState& cs, const int* w) 
                 const uint32_t xslot = xstage % kXStages;
                 gemm_wait(c, cs, c.full_bar(slot), phase);
                 gemm_wait(c, cs, c.xfull_bar(xslot), (xstage / kXStages) & 1u);
+                if (b == 0 && st == 0) rec(c, MKB_T_CONSUMER_FIRST_STAGE);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t wb = c.stage_addr(slot), xb = c.xstage_addr(xslot);
                 if (!cs.dead) {
@@ -1864,8 +1866,13 @@ __device__ bool gemm_instruction(const Ctx& c, ConsumerState& cs, const int* w) 
             umma_commit(c.acc_full_bar(buf));
             ++acc;
         }
-    } else if (warp >= 4 && warp < 8) {
+        rec(c, MKB_T_ATTN_STAGES_DONE);  // (GEMM instructions: every MMA of the instruction is issued)
+    } else if (warp >= 4) {
+        // Twelve epilogue warps: warp w reads the lane quarter w % 4 of tensor memory (its rows), and
+        // the three groups of four warps share the sequences (accumulator columns) of every block.
         const int q = warp & 3, r = q * 32 + lane;  // this thread's row inside the block
+        const uint32_t cols_per_group = ((n / 8 + 2) / 3) * 8;
+        const uint32_t c_lo = min(n, (uint32_t)((warp - 4) >> 2) * cols_per_group), c_hi = min(n, c_lo + cols_per_group);
         uint32_t acc = cs.acc;
         const bool pair = g.op == MKB_OP_RMS_UPGATE_SILU;
         for (int b = 0; b < g.nblocks; b += pair ? 2 : 1) {
@@ -1875,10 +1882,11 @@ __device__ bool gemm_instruction(const Ctx& c, ConsumerState& cs, const int* w) 
             const uint32_t buf2 = (acc + 1) & 1u, use2 = (acc + 1) >> 1;
             if (pair) gemm_wait(c, cs, c.acc_full_bar(buf2), use2 & 1u);
             cs.dead = __any_sync(0xffffffffu, cs.dead);  // the lanes shuffle below: leave together
+            if (b == 0 && tid == 4 * 32) rec(c, MKB_T_RMS_LOADED);  // (GEMM instructions: first accumulator complete)
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
             const int grow = blk * kBlockRows + r;  // row of the projection's output
-            for (uint32_t c0 = 0; c0 < n; c0 += 8) {
+            for (uint32_t c0 = c_lo; c0 < c_hi; c0 += 8) {
                 float v[8], v2[8];
                 tmem_ld8(lane_addr + buf * kBatch + c0, v);
                 if (pair) tmem_ld8(lane_addr + buf2 * kBatch + c0, v2);
@@ -1937,13 +1945,14 @@ __device__ bool gemm_instruction(const Ctx& c, ConsumerState& cs, const int* w) 
             }
             acc += pair ? 2 : 1;
             if (g.op == MKB_OP_RMS_QKV_ROPE_APPEND || pair) {
-                epilogue_sync();  // all four warps' global writes of this block precede the signal
+                epilogue_sync();  // all epilogue warps' global writes of this block precede the signal
                 if (tid == 4 * 32 && !cs.dead) {
                     const int slot = pair ? blk * kBlockRows / p.R : blk * kBlockRows / p.D;
                     red_release_gpu_add(bar_addr(p, g.layer, g.op - 1, slot), 1);
                 }
             }
         }
+        if (tid == 4 * 32) rec(c, MKB_T_RMS_SUMMED);  // (GEMM instructions: last epilogue done)
         if (g.op == MKB_OP_O_PROJ_RESIDUAL || g.op == MKB_OP_DOWN_PROJ_RESIDUAL) {
             epilogue_sync();
             if (tid == 4 * 32 && !cs.dead) red_release_gpu_add(bar_addr(p, g.layer, g.op - 1, 0), g.nblocks);
@@ -2500,7 +2509,7 @@ __device__ __forceinline__ void megakernel_body(const KParams& p) {
             }
             for (int b = 0; b < 2; ++b) {
                 mbar_init(c.acc_full_bar(b), 1);
-                mbar_init(c.acc_empty_bar(b), 4);  // one arrival per epilogue warp
+                mbar_init(c.acc_empty_bar(b), 12);  // one arrival per epilogue warp (warps 4..15)
             }
         }
         for (int s = 0; s < kOutSlots; ++s) {

@@ -52,7 +52,16 @@ def summarize(globs) -> dict:
             us = lambda slot: (int(t[slot]) - t0) / 1e3  # noqa: E731
             d = per_op[op]
             d["wait"].append(us(T_WAIT_DONE) - us(T_CONSUMER_START))
-            if op in (1, 4, 5, 6, 7):
+            if op in (1, 4, 5, 6, 7) and getattr(globs, "batch_size", 1) > 8:
+                # tcgen05 build: the second loader waits for the producer, one thread issues the MMAs
+                # (slot 5: all issued), four warps run the epilogues (slot 6: first accumulator
+                # complete, slot 7: last epilogue done)
+                d["first_stage"].append(us(T_FIRST_STAGE) - us(T_WAIT_DONE))
+                d["mma_issue"].append(us(5) - us(T_FIRST_STAGE))
+                d["first_accumulator"].append(us(6) - us(T_FIRST_STAGE))
+                d["epilogue_after_issue"].append(us(7) - us(5))
+                d["tail"].append(us(T_CONSUMER_DONE) - us(7))
+            elif op in (1, 4, 5, 6, 7):
                 d["activation"].append(us(T_ACT_READY) - us(T_WAIT_DONE))
                 if op in (1, 5, 7) and getattr(globs, "batch_size", 1) == 1:
                     d["act:load"].append(us(6) - us(T_WAIT_DONE))
