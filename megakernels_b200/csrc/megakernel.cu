@@ -759,7 +759,7 @@ struct HotConsts {
     float eps;
     int pad;
 };
-static_assert(sizeof(HotConsts) == 56, "two loader words follow at byte 56");
+static_assert(sizeof(HotConsts) == 56 && kLoaders <= 2, "two loader words follow at byte 56");
 
 // The residual stream of an RMSNorm comes from one of three places:
 //   kRmsAcc    `hidden` (the token embedding) + the Q31.32 accumulators the row-split projections
