@@ -26,9 +26,10 @@ def test_parse_cli_defaults_follow_the_reference_script():
 
 def test_parse_cli_types_and_presets():
     cfg = parse_cli(["l8", "once", "ntok=8", "layers=2", "tokens=false", "memory_fraction=0.25",
-                     "prompt_ids=1,2,3", "sched=wave", "coalesce_o_proj=true"])
+                     "prompt_ids=1,2,3", "sched=wave", "coalesce_o_proj=true", "merge_in_last_partial=true"])
     assert cfg.model == "llama-8b" and (cfg.num_warmup, cfg.num_iters) == (0, 1)
     assert cfg.ntok == 8 and cfg.layers == 2 and cfg.tokens is False and cfg.coalesce_o_proj is True
+    assert cfg.merge_in_last_partial is True and parse_cli([]).merge_in_last_partial is False
     assert cfg.memory_fraction == 0.25 and cfg.prompt_ids == "1,2,3" and cfg.sched == "wave"
     assert isinstance(cfg, ScriptConfig)
 
